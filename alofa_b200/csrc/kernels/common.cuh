@@ -1,0 +1,58 @@
+// Shared device helpers: element conversion, block reductions with a fixed
+// order, and the launch-error check used by every exported function.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define ALOFA_API extern "C" __attribute__((visibility("default")))
+
+// Return codes of the exported launch functions.
+#define ALOFA_OK 0
+#define ALOFA_ERR_ARGUMENT 1   // a size the kernel does not take
+#define ALOFA_ERR_LAUNCH 2     // the CUDA runtime refused the launch
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+// Sum over a warp in a fixed butterfly order; every lane gets the result.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum / max; `scratch` holds 32 floats.  All threads get the result.
+// The order of additions depends only on the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarp; ++w) total += scratch[w];
+  return total;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float m = scratch[0];
+  for (int w = 1; w < nwarp; ++w) m = fmaxf(m, scratch[w]);
+  return m;
+}
+
+static inline int launch_status() { return cudaGetLastError() == cudaSuccess ? ALOFA_OK : ALOFA_ERR_LAUNCH; }

@@ -1,0 +1,160 @@
+"""Python face of the CUDA kernels.
+
+Each function checks what the kernel cannot check for itself (device, dtype,
+contiguity, matching sizes), then launches on the current CUDA stream through
+the library's C entry point.  There is no fallback of any kind: tensors that
+are not on a CUDA device are refused, and a library that cannot be built or
+loaded raises when it is first needed."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..errors import AlofaError
+from .build import load_library
+
+EPI_STORE, EPI_RESIDUAL, EPI_GATED = 0, 1, 2
+
+_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_libs: dict = {}
+
+
+def _generic():
+    lib = _libs.get("generic")
+    if lib is None:
+        lib = load_library("alofa_generic", ["kernels/generic.cu"])
+        sigs = {
+            "alofa_embed_gather": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+            "alofa_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
+            "alofa_gemm_generic": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_rope_store": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+            "alofa_sample": [_P, _P, _P, _P, _I, _I, _P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype = _I
+            fn.argtypes = args
+        _libs["generic"] = lib
+    return lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
+    if not t.is_cuda:
+        raise AlofaError("unsupported", "kernels run on CUDA tensors only", f"{name} is on {t.device}")
+    if not t.is_contiguous():
+        raise AlofaError("invalid_argument", "kernel operand must be contiguous", name)
+    if dtype is not None and t.dtype != dtype:
+        raise AlofaError("invalid_argument", "kernel operand has the wrong dtype", f"{name} is {t.dtype}, want {dtype}")
+    return t.data_ptr()
+
+
+def _is_bf16(t: torch.Tensor, name: str) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise AlofaError("unsupported", "kernel operand must be float32 or bfloat16", f"{name} is {t.dtype}")
+
+
+def _done(rc: int, what: str, detail: str = "") -> None:
+    if rc == 0:
+        return
+    if rc == 1:
+        raise AlofaError("unsupported", f"{what}: the kernel does not take these sizes", detail)
+    raise AlofaError("state", f"{what}: the CUDA runtime refused the launch", detail + " " + str(torch.cuda.get_device_name()))
+
+
+def embed_gather(out, table, ids, status=None) -> None:
+    """out[t] = table[ids[t]] widened to fp32; out [T, H] fp32."""
+    n, hidden = out.shape
+    _done(
+        _generic().alofa_embed_gather(
+            _dev(out, "out", torch.float32), _dev(table, "table"), _dev(ids, "ids", torch.int32), n, hidden, table.shape[0],
+            _is_bf16(table, "table"), _dev(status, "status", torch.int32) if status is not None else None, _stream(),
+        ),
+        "embed_gather",
+    )
+
+
+def rmsnorm(out, x, weight, eps: float, rows=None) -> None:
+    """out[r] = rmsnorm(x[rows[r] or r]) * weight; x fp32, weight fp32."""
+    n, hidden = out.shape
+    if x.shape[-1] != hidden or weight.shape[0] != hidden:
+        raise AlofaError("invalid_argument", "rmsnorm sizes disagree", f"out={tuple(out.shape)} x={tuple(x.shape)} w={tuple(weight.shape)}")
+    _done(
+        _generic().alofa_rmsnorm(
+            _dev(out, "out"), _dev(x, "x", torch.float32), _dev(weight, "weight", torch.float32),
+            _dev(rows, "rows", torch.int32) if rows is not None else None, n, hidden, float(eps), _is_bf16(out, "out"), _stream(),
+        ),
+        "rmsnorm",
+    )
+
+
+def gemm_generic(out, x, w, bias, epi: int) -> None:
+    """out = x @ w.T (+bias) with the epilogue ``epi``; any sizes."""
+    m, k = x.shape
+    n = out.shape[1]
+    rows_w = 2 * n if epi == EPI_GATED else n
+    if w.shape != (rows_w, k) or out.shape[0] != m or (bias is not None and bias.shape[0] != rows_w):
+        raise AlofaError("invalid_argument", "gemm sizes disagree", f"out={tuple(out.shape)} x={tuple(x.shape)} w={tuple(w.shape)} epi={epi}")
+    _done(
+        _generic().alofa_gemm_generic(
+            _dev(out, "out"), _dev(x, "x"), _dev(w, "w"), _dev(bias, "bias", torch.float32) if bias is not None else None,
+            m, n, k, epi, _is_bf16(x, "x"), _is_bf16(w, "w"), _is_bf16(out, "out"), _stream(),
+        ),
+        "gemm_generic", f"M={m} N={n} K={k} epi={epi}",
+    )
+
+
+def rope_store(q_out, k_cache, v_cache, qkv, cos_sin, positions, slot_map, nh, nkv, hd, rot, write_cache=True) -> None:
+    """Rotate q and k, write k and v into the cache slots of ``slot_map``."""
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * hd or q_out.shape != (n, nh * hd):
+        raise AlofaError("invalid_argument", "rope_store sizes disagree", f"qkv={tuple(qkv.shape)} q_out={tuple(q_out.shape)}")
+    if rot and cos_sin.shape[1] * 2 != rot:
+        raise AlofaError("invalid_argument", "rotary table does not match rotary_dim", f"table={tuple(cos_sin.shape)} rot={rot}")
+    dt = qkv.dtype
+    _done(
+        _generic().alofa_rope_store(
+            _dev(q_out, "q_out", dt), _dev(k_cache, "k_cache", dt) if write_cache else None,
+            _dev(v_cache, "v_cache", dt) if write_cache else None, _dev(qkv, "qkv"),
+            _dev(cos_sin, "cos_sin", torch.float32) if rot else None, _dev(positions, "positions", torch.int32),
+            _dev(slot_map, "slot_map", torch.int32) if write_cache else None, n, nh, nkv, hd, rot, 1 if write_cache else 0,
+            _is_bf16(qkv, "qkv"), _stream(),
+        ),
+        "rope_store", f"hd={hd} rot={rot}",
+    )
+
+
+def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, block_table, page_size, nh, nkv, hd, window, scale) -> None:
+    """Causal GQA over the paged cache, any head size up to 256."""
+    n = q.shape[0]
+    dt = q.dtype
+    _done(
+        _generic().alofa_paged_attention_generic(
+            _dev(out, "out", dt), _dev(q, "q"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt),
+            _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+            _dev(block_table, "block_table", torch.int32), block_table.shape[1], page_size, n, nh, nkv, hd,
+            int(window or 0), float(scale), _is_bf16(q, "q"), _stream(),
+        ),
+        "paged_attention_generic", f"hd={hd} nh={nh} nkv={nkv}",
+    )
+
+
+def sample(tokens, logits, temperature, uniform) -> None:
+    """tokens[r] = argmax (temperature 0) or inverse-CDF draw of softmax(x/T)."""
+    n, vocab = logits.shape
+    _done(
+        _generic().alofa_sample(
+            _dev(tokens, "tokens", torch.int32), _dev(logits, "logits", torch.float32),
+            _dev(temperature, "temperature", torch.float32) if temperature is not None else None,
+            _dev(uniform, "uniform", torch.float32) if uniform is not None else None, n, vocab, _stream(),
+        ),
+        "sample",
+    )

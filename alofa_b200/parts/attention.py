@@ -1,0 +1,107 @@
+"""Grouped-query attention over a paged key/value cache.
+
+``q = x Wq^T + bq`` (and k, v), heads packed along the channel axis (channel
+``h * head_dim + d``); q and k are position-encoded, k and v are appended to
+the cache through the block table, query head ``h`` reads KV head
+``h // (heads / kv_heads)``, keys up to the query's own position are visible
+(all of them, or the last ``window``), scores are ``dot / sqrt(head_dim)``,
+softmax in fp32, and the output projection is added into the residual stream
+(src/alofa/kernels/cpu/scalar.mojo:132-193, 392-470;
+src/alofa/kernels/cpu/paged.mojo:208-336; src/alofa/engine/executor.mojo:745-795).
+
+At load the q, k and v weights are stacked into one matrix so that one product
+yields all three; the checkpoint's tensors are read under their own names."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..csrc import ops
+from ..errors import AlofaError
+from .base import PagedKV, Part, TensorSpec, as_float32_vector, build_part, register_part
+from .linear import RESIDUAL, STORE, Linear
+
+
+class GQAttention(Part):
+    family = "mixer"
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.param
+        self.hidden = int(p("hidden_size"))
+        self.nh = int(p("num_heads"))
+        self.nkv = int(p("num_kv_heads"))
+        self.hd = int(p("head_dim"))
+        self.qkv_bias = bool(p("qkv_bias", False))
+        self.out_bias = bool(p("out_bias", False))
+        self.window = self.params.get("window")
+        if self.nkv <= 0 or self.nh % self.nkv:
+            raise AlofaError("invalid_argument", "kv heads must divide heads", f"heads={self.nh} kv_heads={self.nkv}")
+        if self.hd <= 0 or self.hd % 2 or self.hd > 256:
+            raise AlofaError("unsupported", "head_dim must be even and at most 256", f"head_dim={self.hd}")
+        self.q_dim, self.kv_dim = self.nh * self.hd, self.nkv * self.hd
+        self.scale = 1.0 / math.sqrt(self.hd)
+        self.position = build_part("position", p("position"), rt)
+        self.qkv = self.q_only = self.out = None
+
+    def cache_spec(self):
+        return PagedKV(self.nkv, self.hd, self.window)
+
+    def tensors(self):
+        pre = self.prefix
+        t = {
+            pre + "q_proj.weight": TensorSpec((self.q_dim, self.hidden)),
+            pre + "k_proj.weight": TensorSpec((self.kv_dim, self.hidden)),
+            pre + "v_proj.weight": TensorSpec((self.kv_dim, self.hidden)),
+            pre + "o_proj.weight": TensorSpec((self.hidden, self.q_dim)),
+        }
+        if self.qkv_bias:
+            t[pre + "q_proj.bias"] = TensorSpec((self.q_dim,))
+            t[pre + "k_proj.bias"] = TensorSpec((self.kv_dim,))
+            t[pre + "v_proj.bias"] = TensorSpec((self.kv_dim,))
+        if self.out_bias:
+            t[pre + "o_proj.bias"] = TensorSpec((self.hidden,))
+        t.update(self.position.tensors())
+        return t
+
+    def load(self, state):
+        pre = self.prefix
+        w = torch.cat([state[pre + f"{n}_proj.weight"] for n in "qkv"], dim=0)
+        b = None
+        if self.qkv_bias:
+            b = as_float32_vector(torch.cat([state[pre + f"{n}_proj.bias"] for n in "qkv"], dim=0))
+        self.qkv = Linear(w, b, STORE)
+        # a run of this layer that reads another run's cache needs q only
+        self.q_only = Linear(w[: self.q_dim], b[: self.q_dim] if b is not None else None, STORE)
+        ob = as_float32_vector(state[pre + "o_proj.bias"]) if self.out_bias else None
+        self.out = Linear(state[pre + "o_proj.weight"], ob, RESIDUAL)
+        self.position.load(state)
+
+    def forward(self, ctx, x, h, cache, writes=True):
+        """h += Attention(x).  ``cache`` is the layer cache (k, v, group)."""
+        n = x.shape[0]
+        dt = self.rt.dtype
+        group = ctx.groups[cache.group]
+        nkv_in = self.nkv if writes else 0
+        qkv = ctx.buf((n, (self.nh + 2 * nkv_in) * self.hd), dt)
+        (self.qkv if writes else self.q_only)(qkv, x)
+        table, rot = self.position.rotary_table()
+        if getattr(self.position, "apply", None) is not None:
+            q_view = qkv[:, : self.q_dim].view(n, self.nh, self.hd)
+            k_view = qkv[:, self.q_dim : self.q_dim + nkv_in * self.hd].view(n, nkv_in, self.hd)
+            self.position.apply(ctx, q_view, k_view)
+        q = ctx.buf((n, self.q_dim), dt)
+        ops.rope_store(q, cache.k, cache.v, qkv, table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, rot, writes)
+        attn = ctx.buf((n, self.q_dim), dt)
+        self.attend(ctx, attn, q, cache, group)
+        self.out(h, attn)
+
+    def attend(self, ctx, out, q, cache, group):
+        ops.paged_attention_generic(
+            out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
+            self.nh, self.nkv, self.hd, self.window, self.scale,
+        )
+
+
+register_part("mixer", "gqa_attention", GQAttention)

@@ -1,0 +1,46 @@
+"""Dense gated feed-forward: ``h += (act(x Wg^T) * (x Wu^T)) Wd^T`` with
+``silu(z) = z / (1 + exp(-z))``, no biases
+(src/alofa/model/arch/qwen.mojo:1481-1510; src/alofa/kernels/cpu/scalar.mojo:208-231).
+The gate and up weights are stacked at load so that one product with a fused
+epilogue writes ``silu(gate) * up`` directly."""
+from __future__ import annotations
+
+import torch
+
+from ..errors import AlofaError
+from .base import Part, TensorSpec, register_part
+from .linear import GATED, RESIDUAL, Linear
+
+
+class GatedMLP(Part):
+    family = "feed_forward"
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        act = self.param("activation", "silu")
+        if act != "silu":
+            raise AlofaError("unsupported", "gated_mlp supports the silu activation only", f"activation={act}")
+        self.gate_up = self.down = None
+
+    def tensors(self):
+        pre = self.prefix
+        return {
+            pre + "gate_proj.weight": TensorSpec((self.inter, self.hidden)),
+            pre + "up_proj.weight": TensorSpec((self.inter, self.hidden)),
+            pre + "down_proj.weight": TensorSpec((self.hidden, self.inter)),
+        }
+
+    def load(self, state):
+        pre = self.prefix
+        self.gate_up = Linear(torch.cat([state[pre + "gate_proj.weight"], state[pre + "up_proj.weight"]], dim=0), None, GATED)
+        self.down = Linear(state[pre + "down_proj.weight"], None, RESIDUAL)
+
+    def forward(self, ctx, x, h):
+        act = ctx.buf((x.shape[0], self.inter), self.rt.dtype)
+        self.gate_up(act, x)
+        self.down(h, act)
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)
