@@ -29,13 +29,26 @@ GXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-shared", "-Wall"]
 
 _loaded: dict = {}
 _lock = threading.Lock()
+_load_lock = threading.RLock()
 
 
 def _say(text: str) -> None:
     print(f"[alofa_b200] {text}", file=sys.stderr, flush=True)
 
 
+_build_dir = None
+
+
 def build_dir() -> Path:
+    """Where compiled libraries are kept (decided once per process)."""
+    global _build_dir
+    with _lock:
+        if _build_dir is None:
+            _build_dir = _choose_build_dir()
+        return _build_dir
+
+
+def _choose_build_dir() -> Path:
     override = os.environ.get("ALOFA_BUILD_DIR")
     candidates = [Path(override)] if override else []
     candidates += [CSRC / "_build", Path(tempfile.gettempdir()) / f"alofa_b200_build_{os.getuid()}"]
@@ -124,7 +137,7 @@ def compile_library(name: str, sources: list, defines: dict | None = None, cuda:
 def load_library(name: str, sources: list, defines: dict | None = None, cuda: bool = True, extra_flags: list | None = None) -> ctypes.CDLL:
     """The loaded library, compiling it first when needed."""
     ident = (name, tuple(sources), tuple(sorted((defines or {}).items())), cuda, tuple(extra_flags or []))
-    with _lock:
+    with _load_lock:
         if ident in _loaded:
             return _loaded[ident]
         path = compile_library(name, sources, defines, cuda, extra_flags)

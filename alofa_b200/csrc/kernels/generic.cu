@@ -345,99 +345,3 @@ ALOFA_API int alofa_paged_attention_generic(void* out, const void* q, const void
         max_blocks, page_size, nh, nkv, hd, window, scale);
   return launch_status();
 }
-
-// ---------------------------------------------------------------------------
-// Sampling on fp32 logits [n, vocab], one block per row.
-//   temperature == 0: the largest logit, ties to the lowest index.
-//   else: softmax(x / temperature) in fp32 and the inverse CDF at u[row]: the
-//   first index whose running sum exceeds u * total.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits,
-                                                      const float* __restrict__ temperature,
-                                                      const float* __restrict__ uniform, int vocab) {
-  __shared__ float scratch[32];
-  __shared__ float sval[32];
-  __shared__ int sidx[32];
-  __shared__ float running;
-  __shared__ int chosen;
-  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
-  const float* x = logits + (size_t)r * vocab;
-  // argmax with ties to the lowest index
-  float best = -INFINITY;
-  int best_i = 0x7fffffff;
-  for (int i = tid; i < vocab; i += blockDim.x) {
-    const float v = x[i];
-    if (v > best || (v == best && i < best_i)) {
-      best = v;
-      best_i = i;
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-    if (ov > best || (ov == best && oi < best_i)) {
-      best = ov;
-      best_i = oi;
-    }
-  }
-  if (lane == 0) {
-    sval[warp] = best;
-    sidx[warp] = best_i;
-  }
-  __syncthreads();
-  if (tid == 0) {
-    for (int w = 1; w < nwarp; ++w)
-      if (sval[w] > sval[0] || (sval[w] == sval[0] && sidx[w] < sidx[0])) {
-        sval[0] = sval[w];
-        sidx[0] = sidx[w];
-      }
-    running = 0.f;
-    chosen = 0x7fffffff;
-  }
-  __syncthreads();
-  const float xmax = sval[0];
-  const float temp = temperature ? temperature[r] : 0.f;
-  if (!(temp > 0.f)) {
-    if (tid == 0) tokens[r] = sidx[0];
-    return;
-  }
-  const float inv_t = 1.0f / temp;
-  float part = 0.f;
-  for (int i = tid; i < vocab; i += blockDim.x) part += expf((x[i] - xmax) * inv_t);
-  const float total = block_sum(part, scratch);
-  const float target = uniform[r] * total;
-  // inverse CDF over consecutive chunks of blockDim.x entries
-  for (int c0 = 0; c0 < vocab; c0 += blockDim.x) {
-    const int i = c0 + tid;
-    const float p = i < vocab ? expf((x[i] - xmax) * inv_t) : 0.f;
-    float scan = p;  // inclusive scan inside the warp
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float n = __shfl_up_sync(0xffffffffu, scan, o);
-      if (lane >= o) scan += n;
-    }
-    if (lane == 31) scratch[warp] = scan;
-    __syncthreads();
-    float before = running;
-    for (int w = 0; w < warp; ++w) before += scratch[w];
-    const float cum = before + scan;
-    if (i < vocab && target < cum) atomicMin(&chosen, i);  // the lowest such index wins
-    __syncthreads();
-    if (chosen != 0x7fffffff) break;
-    if (tid == 0) {
-      float tot = running;
-      for (int w = 0; w < nwarp; ++w) tot += scratch[w];
-      running = tot;
-    }
-    __syncthreads();
-  }
-  if (tid == 0) tokens[r] = chosen != 0x7fffffff ? chosen : sidx[0];
-}
-
-ALOFA_API int alofa_sample(int* tokens, const float* logits, const float* temperature, const float* uniform, int n_rows,
-                           int vocab, cudaStream_t stream) {
-  if (n_rows <= 0) return ALOFA_OK;
-  sample_kernel<<<n_rows, 1024, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
-  return launch_status();
-}

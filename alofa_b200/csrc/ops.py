@@ -18,6 +18,17 @@ EPI_STORE, EPI_RESIDUAL, EPI_GATED = 0, 1, 2
 
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _libs: dict = {}
+_launches = 0  # kernels launched through this module (graph replays add their kernels)
+
+
+def launch_count() -> int:
+    """How many of this package's kernels have been launched so far."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
 
 
 def _generic():
@@ -30,13 +41,28 @@ def _generic():
             "alofa_gemm_generic": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_rope_store": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
-            "alofa_sample": [_P, _P, _P, _P, _I, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
             fn.restype = _I
             fn.argtypes = args
         _libs["generic"] = lib
+    return lib
+
+
+def _sampling():
+    lib = _libs.get("sampling")
+    if lib is None:
+        lib = load_library("alofa_sampling", ["kernels/sampling.cu"])
+        sigs = {
+            "alofa_sample": [_P, _P, _P, _P, _I, _I, _P],
+            "alofa_sample_chain": [_P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype = _I
+            fn.argtypes = args
+        _libs["sampling"] = lib
     return lib
 
 
@@ -63,7 +89,9 @@ def _is_bf16(t: torch.Tensor, name: str) -> int:
 
 
 def _done(rc: int, what: str, detail: str = "") -> None:
+    global _launches
     if rc == 0:
+        _launches += 1
         return
     if rc == 1:
         raise AlofaError("unsupported", f"{what}: the kernel does not take these sizes", detail)
@@ -151,10 +179,28 @@ def sample(tokens, logits, temperature, uniform) -> None:
     """tokens[r] = argmax (temperature 0) or inverse-CDF draw of softmax(x/T)."""
     n, vocab = logits.shape
     _done(
-        _generic().alofa_sample(
+        _sampling().alofa_sample(
             _dev(tokens, "tokens", torch.int32), _dev(logits, "logits", torch.float32),
             _dev(temperature, "temperature", torch.float32) if temperature is not None else None,
             _dev(uniform, "uniform", torch.float32) if uniform is not None else None, n, vocab, _stream(),
         ),
         "sample",
+    )
+
+
+def sample_chain(tokens, logits, work, fparams, iparams, bias_start, bias_index, bias_value, hist_start, hist_token, hist_count) -> None:
+    """The whole sampling chain per row (bias, penalties, temperature, top-k,
+    top-p, min-p, draw); ``work`` is fp32 scratch of the logits' shape."""
+    n, vocab = logits.shape
+    if work.shape != logits.shape or fparams.shape != (n, 8) or iparams.shape != (n, 4):
+        raise AlofaError("invalid_argument", "sample_chain sizes disagree", f"logits={tuple(logits.shape)} work={tuple(work.shape)}")
+    f32, i32 = torch.float32, torch.int32
+    _done(
+        _sampling().alofa_sample_chain(
+            _dev(tokens, "tokens", i32), _dev(logits, "logits", f32), _dev(work, "work", f32), n, vocab,
+            _dev(fparams, "fparams", f32), _dev(iparams, "iparams", i32), _dev(bias_start, "bias_start", i32),
+            _dev(bias_index, "bias_index", i32), _dev(bias_value, "bias_value", f32), _dev(hist_start, "hist_start", i32),
+            _dev(hist_token, "hist_token", i32), _dev(hist_count, "hist_count", i32), _stream(),
+        ),
+        "sample_chain", f"vocab={vocab}",
     )

@@ -19,7 +19,6 @@ import torch
 
 from ..cache.manager import CacheManager, GroupSpec
 from ..cache.storage import CacheStorage, group_windows
-from ..csrc import ops
 from ..errors import AlofaError
 from ..parts.base import PagedKV
 from ..parts.model import Model
@@ -175,17 +174,12 @@ class StepRunner:
         self.commit(ctx)
         return logits if ctx.n_out else None
 
-    def forward_and_sample(self, entries: Sequence[StepEntry]):
-        """Run one step and pick a token at every wanted place: (tokens int32
-        on the device, logits)."""
+    def forward_logits(self, entries: Sequence[StepEntry]):
+        """Run one step; (context, logits or None) for a sampler to use."""
         ctx = self.prepare(entries)
         logits = self.model.forward(ctx, self.storage.caches)
         self.commit(ctx)
-        if not ctx.n_out:
-            return None, None
-        tokens = torch.empty(ctx.n_out, dtype=torch.int32, device=self.rt.device)
-        ops.sample(tokens, logits, ctx.temperature, ctx.uniform)
-        return tokens, logits
+        return ctx, (logits if ctx.n_out else None)
 
     def check_status(self) -> None:
         """Raise if a kernel flagged bad input since the last check (reads the
