@@ -83,35 +83,48 @@ struct Out {
   int n_prefill = 0, n_decode = 0, n_preempt = 0, n_finished = 0;
 };
 
-// Preempt the newest running request that has progress; not `protect`.
+// Preempt the newest request that holds pages (latest admitted first); not
+// `protect`.  The reference only preempts running requests
+// (scheduler.mojo:569-594) so that a tight watermark cannot keep a prompt from
+// ever completing; here a prompt portion is only scheduled while it fits
+// under the watermark (try_prefill), and the oldest holder is never the victim
+// of a newer one, so the oldest live request always finishes.
 bool preempt_one(Sched& s, Out& out, int protect) {
   int victim = -1;
   for (size_t i = 0; i < s.slots.size(); ++i) {
     const Slot& sl = s.slots[i];
-    if ((int)i == protect || sl.state != ST_RUNNING || sl.cache_len() <= 0) continue;
+    if ((int)i == protect || sl.state == ST_FREE || sl.cache_len() <= 0) continue;
     if (victim < 0 || sl.seq > s.slots[victim].seq) victim = (int)i;
   }
   if (victim < 0) return false;
   Slot& v = s.slots[victim];
-  // A decode entry of this tick for the victim is withdrawn.  What comes back
-  // is what the cache manager holds for it now, plus the page this tick had
-  // set aside for the withdrawn token.
+  // Work of this tick for the victim is withdrawn.  What comes back is what
+  // the cache manager holds for it now, plus the pages this tick had set aside
+  // for the withdrawn tokens.
   const int len = v.cache_len();
-  bool withdrawn = false;
+  int before = len;  // tokens the cache manager holds for the victim right now
   for (int i = 0; i < out.n_decode; ++i) {
     if (out.d_id[i] == v.id) {
       for (int j = i + 1; j < out.n_decode; ++j) out.d_id[j - 1] = out.d_id[j];
       out.n_decode--;
-      withdrawn = true;
+      before = len - 1;
       break;
     }
   }
-  for (size_t g = 0; g < s.page_size.size(); ++g) {
-    if (withdrawn)
-      s.free_local[g] += held(s, (int)g, len - 1) + ceil_div(len, s.page_size[g]) - ceil_div(len - 1, s.page_size[g]);
-    else
-      s.free_local[g] += held(s, (int)g, len);
+  for (int i = 0; i < out.n_prefill; ++i) {
+    if (out.p_id[i] == v.id) {
+      before = out.p_start[i];
+      for (int j = i + 1; j < out.n_prefill; ++j) {
+        out.p_id[j - 1] = out.p_id[j];
+        out.p_start[j - 1] = out.p_start[j];
+        out.p_end[j - 1] = out.p_end[j];
+      }
+      out.n_prefill--;
+      break;
+    }
   }
+  for (size_t g = 0; g < s.page_size.size(); ++g)
+    s.free_local[g] += held(s, (int)g, before) + ceil_div(len, s.page_size[g]) - ceil_div(before, s.page_size[g]);
   out.x_id[out.n_preempt++] = v.id;
   v.done = 0;
   v.n_out = 0;
@@ -134,7 +147,8 @@ int try_prefill(Sched& s, Out& out, int i, int budget) {
   const int G = (int)s.page_size.size();
   for (int g = 0; g < G; ++g) {
     int need = ceil_div(sl.done + chunk, s.page_size[g]) - ceil_div(sl.done, s.page_size[g]);
-    if (need > s.free_local[g]) return budget;  // left for a later tick
+    // left for a later tick when it does not fit under the watermark
+    if (s.capacity[g] - s.free_local[g] + need > threshold(s, g)) return budget;
   }
   for (int g = 0; g < G; ++g)
     s.free_local[g] -= ceil_div(sl.done + chunk, s.page_size[g]) - ceil_div(sl.done, s.page_size[g]);

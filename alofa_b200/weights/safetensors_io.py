@@ -12,6 +12,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from dataclasses import dataclass
 from pathlib import Path
 
@@ -94,7 +95,9 @@ class SafeTensorFile:
         count = (e.end - e.begin) // width
         if count == 0:
             return torch.empty(e.shape, dtype=dtype)
-        flat = torch.frombuffer(self._map, dtype=dtype, count=count, offset=e.begin)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)  # the mapping is read-only; nothing writes through the view
+            flat = torch.frombuffer(self._map, dtype=dtype, count=count, offset=e.begin)
         return flat.view(e.shape)
 
     def close(self):

@@ -1,0 +1,254 @@
+"""Each kernel alone against its plain fp64 reference, at sizes other than the
+engine's test models: odd widths, head sizes in steps of 16, partial rotary,
+scattered pages, and inputs made so that a wrong key or a wrong edge shows."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+from gpu_util import assert_close, dev, paged_from_sequences, rounded
+
+pytestmark = pytest.mark.gpu
+
+F32, BF16 = torch.float32, torch.bfloat16
+# kernel-level bounds, times max(1, max|reference|): fp32 sums against fp64;
+# bf16 outputs are rounded once to 8 bits of mantissa (2^-9 relative)
+TOL = {F32: 1e-5, BF16: 6e-3}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from alofa_b200.csrc import ops
+
+    return ops
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_embed_gather(ops, dtype):
+    rng = np.random.default_rng(0)
+    table = rounded(rng.normal(size=(301, 72)), dtype)
+    ids = np.array([0, 300, 17, 17, 5], dtype=np.int32)
+    out = torch.empty(5, 72, dtype=F32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed_gather(out, dev(table, dtype), dev(ids), status)
+    assert np.array_equal(out.cpu().numpy(), table[ids].astype(np.float32)) and int(status.item()) == 0
+    ops.embed_gather(out, dev(table, dtype), dev(np.array([1, 301, -1, 2, 3], dtype=np.int32)), status)
+    assert int(status.item()) == 1 and float(out[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("out_dtype", [F32, BF16])
+@pytest.mark.parametrize("hidden", [100, 896, 1000])
+def test_rmsnorm(ops, out_dtype, hidden):
+    rng = np.random.default_rng(1)
+    x = rng.normal(size=(9, hidden)).astype(np.float32) * 3
+    w = (1 + 0.1 * rng.normal(size=hidden)).astype(np.float32)
+    out = torch.empty(9, hidden, dtype=out_dtype, device="cuda")
+    ops.rmsnorm(out, dev(x), dev(w), 1e-5)
+    assert_close(out.float().cpu(), plain.rmsnorm(x, w, 1e-5), TOL[out_dtype], "rmsnorm")
+    rows = np.array([8, 0, 3], dtype=np.int32)
+    out = torch.empty(3, hidden, dtype=out_dtype, device="cuda")
+    ops.rmsnorm(out, dev(x), dev(w), 1e-5, dev(rows))
+    assert_close(out.float().cpu(), plain.rmsnorm(x[rows], w, 1e-5), TOL[out_dtype], "rmsnorm rows")
+
+
+@pytest.mark.parametrize("dtypes", [(F32, F32, F32), (BF16, BF16, BF16), (BF16, BF16, F32), (BF16, F32, BF16)])
+@pytest.mark.parametrize("shape", [(37, 53, 71), (1, 130, 64), (70, 64, 200)])
+def test_gemm_generic_epilogues(ops, dtypes, shape):
+    xd, wd, od = dtypes
+    m, n, k = shape
+    rng = np.random.default_rng(2)
+    x = rounded(rng.normal(size=(m, k)), xd)
+    w = rounded(rng.normal(size=(2 * n, k)) / np.sqrt(k), wd)
+    bias = rng.normal(size=2 * n).astype(np.float32)
+    out = torch.empty(m, n, dtype=od, device="cuda")
+    ops.gemm_generic(out, dev(x, xd), dev(w[:n], wd), dev(bias[:n]), ops.EPI_STORE)
+    assert_close(out.float().cpu(), plain.linear(x, w[:n], bias[:n]), TOL[od], "store")
+    ops.gemm_generic(out, dev(x, xd), dev(w, wd), None, ops.EPI_GATED)
+    assert_close(out.float().cpu(), plain.silu(plain.linear(x, w[:n])) * plain.linear(x, w[n:]), TOL[od], "gated")
+    res = rng.normal(size=(m, n)).astype(np.float32)
+    acc = dev(res)
+    ops.gemm_generic(acc, dev(x, xd), dev(w[:n], wd), None, ops.EPI_RESIDUAL)
+    assert_close(acc.cpu(), res + plain.linear(x, w[:n]), TOL[F32], "residual")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("hd, rot", [(48, 48), (48, 32), (16, 16), (128, 64)])
+def test_rope_store(ops, dtype, hd, rot):
+    from alofa_b200.config.spec import PartSpec
+    from alofa_b200.parts.base import Runtime
+    from alofa_b200.parts.position import RotaryNeox
+
+    rng = np.random.default_rng(3)
+    n, nh, nkv = 11, 3, 1
+    part = RotaryNeox(PartSpec("rotary_neox", {"head_dim": hd, "rotary_dim": rot, "theta": 5e4, "max_position": 600}), Runtime(torch.device("cuda"), dtype))
+    table = part.build_table(600)
+    qkv = rounded(rng.normal(size=(n, (nh + 2 * nkv) * hd)), dtype)
+    positions = np.array([0, 1, 2, 599, 64, 63, 17, 300, 5, 5, 128], dtype=np.int32)
+    slots = np.array([4, 9, 0, 31, -1, 2, 7, 30, 12, 13, 1], dtype=np.int32)
+    k_cache = torch.full((32, nkv, hd), 3.0, dtype=dtype, device="cuda")
+    v_cache = torch.full((32, nkv, hd), 3.0, dtype=dtype, device="cuda")
+    q_out = torch.empty(n, nh * hd, dtype=dtype, device="cuda")
+    ops.rope_store(q_out, k_cache, v_cache, dev(qkv, dtype), table, dev(positions), dev(slots), nh, nkv, hd, rot)
+
+    def rotate(x, heads):
+        x = x.reshape(n, heads, hd)
+        out = x.copy()
+        out[..., :rot] = plain.rope(x[..., :rot].reshape(n, heads * rot), positions, heads, rot, 5e4).reshape(n, heads, rot)
+        return out.reshape(n, heads * hd)
+
+    q, k, v = qkv[:, : nh * hd], qkv[:, nh * hd : (nh + nkv) * hd], qkv[:, (nh + nkv) * hd :]
+    assert_close(q_out.float().cpu(), rotate(q, nh), TOL[dtype], "q")
+    want_k = np.full((32, nkv * hd), 3.0)
+    want_v = np.full((32, nkv * hd), 3.0)
+    rk = rotate(k, nkv)
+    for t, s in enumerate(slots):
+        if s >= 0:
+            want_k[s], want_v[s] = rk[t], v[t]
+    assert_close(k_cache.float().cpu().reshape(32, -1), want_k, TOL[dtype], "k cache")
+    assert_close(v_cache.float().cpu().reshape(32, -1), want_v, 0.0, "v cache")
+
+
+def attention_case(ops, dtype, hd, nh, nkv, lens, q_lens, page, window, rng, craft=None, given=None):
+    """Sequences of ``lens`` keys; the last ``q_lens[i]`` positions of each are
+    queries in this launch.  Returns (got, want) as float64 arrays."""
+    if given is not None:
+        qs, ks, vs = given
+    else:
+        ks = [rounded(rng.normal(size=(n, nkv * hd)), dtype) for n in lens]
+        vs = [rounded(rng.normal(size=(n, nkv * hd)), dtype) for n in lens]
+        qs = [rounded(rng.normal(size=(n, nh * hd)), dtype) for n in lens]
+    if craft:
+        craft(qs, ks, vs)
+        ks = [rounded(k, dtype) for k in ks]
+        qs = [rounded(q, dtype) for q in qs]
+    k_cache, v_cache, table = paged_from_sequences(ks, vs, page, nkv, hd, dtype, rng)
+    q_rows, positions, seq_of = [], [], []
+    want = []
+    for s, (n, ql) in enumerate(zip(lens, q_lens)):
+        full = plain.attention(qs[s], ks[s], vs[s], nh, nkv, hd, window)
+        for p in range(n - ql, n):
+            q_rows.append(qs[s][p])
+            positions.append(p)
+            seq_of.append(s)
+            want.append(full[p])
+    q = dev(np.stack(q_rows), dtype)
+    out = torch.empty_like(q)
+    ops.paged_attention_generic(out, q, k_cache, v_cache, dev(np.array(positions, dtype=np.int32)), dev(np.array(seq_of, dtype=np.int32)),
+                                table, page, nh, nkv, hd, window, 1.0 / np.sqrt(hd))
+    return out.float().cpu().numpy().astype(np.float64), np.stack(want)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("hd, nh, nkv", [(16, 4, 2), (48, 6, 2), (80, 5, 5), (128, 8, 1), (256, 2, 1)])
+def test_paged_attention_generic_sizes(ops, dtype, hd, nh, nkv):
+    rng = np.random.default_rng(hd)
+    got, want = attention_case(ops, dtype, hd, nh, nkv, lens=[1, 37, 300, 129], q_lens=[1, 37, 2, 1], page=16, window=None, rng=rng)
+    assert_close(got, want, TOL[dtype], f"hd={hd}")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    """One key far back is made to dominate the softmax: the output must be its
+    value.  A kernel that skips a page, a chunk edge or a block-table entry
+    misses it."""
+    hd, nh, nkv = 32, 2, 1
+    for far in (0, 15, 16, 127, 128, 255, 256, 400, 650):
+        rng = np.random.default_rng(far)
+
+        def craft(qs, ks, vs, far=far):
+            direction = rng.normal(size=hd)
+            direction /= np.linalg.norm(direction)
+            for h in range(nh):
+                qs[0][-1, h * hd : (h + 1) * hd] = 12.0 * direction
+            ks[0][far, :hd] = 12.0 * direction
+            vs[0][far, :hd] = 100.0
+
+        got, want = attention_case(ops, dtype, hd, nh, nkv, lens=[700], q_lens=[1], page=16, window=None, rng=rng, craft=craft)
+        assert np.abs(want[0]).min() > 90.0  # the plain output is that key's value
+        assert_close(got, want, TOL[dtype], f"far key at {far}")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("window", [1, 16, 24, 129])
+def test_attention_window_edge(ops, dtype, window):
+    """A dominating key exactly at the window's oldest place is seen; one
+    place older it is not."""
+    hd, nh, nkv, n = 16, 2, 2, 300
+    for offset, seen in ((window - 1, True), (window, False)):
+        rng = np.random.default_rng(window)
+
+        def craft(qs, ks, vs, offset=offset):
+            direction = np.ones(hd) / np.sqrt(hd)
+            qs[0][-1, :] = np.tile(14.0 * direction, nh)
+            ks[0][n - 1 - offset, :] = np.tile(14.0 * direction, nkv)
+            vs[0][n - 1 - offset, :] = 50.0
+
+        got, want = attention_case(ops, dtype, hd, nh, nkv, lens=[n], q_lens=[1], page=16, window=window, rng=rng, craft=craft)
+        assert (np.abs(want[0]).min() > 45.0) == seen
+        assert_close(got, want, TOL[dtype], f"window {window} offset {offset}")
+
+
+def test_attention_rows_do_not_depend_on_the_batch(ops):
+    """The same query gives the same bits alone or among other requests, and
+    whatever the page size and the pages are."""
+    rng = np.random.default_rng(5)
+    hd, nh, nkv, lens = 48, 6, 2, [200, 77, 301]
+    ks = [rounded(rng.normal(size=(n, nkv * hd)), F32) for n in lens]
+    vs = [rounded(rng.normal(size=(n, nkv * hd)), F32) for n in lens]
+    qs = [rounded(rng.normal(size=(n, nh * hd)), F32) for n in lens]
+    first = ([qs[0]], [ks[0]], [vs[0]])
+    alone16, want = attention_case(ops, F32, hd, nh, nkv, [200], [3], 16, None, np.random.default_rng(1), given=first)
+    alone64, _ = attention_case(ops, F32, hd, nh, nkv, [200], [3], 64, None, np.random.default_rng(2), given=first)
+    mixed, _ = attention_case(ops, F32, hd, nh, nkv, lens, [3, 77, 1], 16, None, np.random.default_rng(3), given=(qs, ks, vs))
+    assert_close(alone16, want, TOL[F32])
+    assert np.array_equal(alone16, alone64) and np.array_equal(alone16, mixed[:3])
+
+
+def test_sample_greedy_ties_and_temperature(ops):
+    rng = np.random.default_rng(6)
+    V = 1187
+    logits = rng.normal(size=(6, V)).astype(np.float32)
+    logits[0, [5, 900]] = 9.0  # a tie at the top goes to the lower index
+    logits[1, V - 1] = 8.0
+    tokens = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.sample(tokens, dev(logits), dev(np.zeros(6, dtype=np.float32)), dev(np.zeros(6, dtype=np.float32)))
+    assert tokens.cpu().tolist() == [int(np.argmax(r)) for r in logits] and tokens[0] == 5 and tokens[1] == V - 1
+    temps = np.array([0.01, 0.5, 1.0, 1.0, 2.0, 0.0], dtype=np.float32)
+    us = np.array([0.3, 0.3, 0.0, 0.999999, 0.5, 0.4], dtype=np.float32)  # row 0: two tied maxima, u below one half picks the first
+    ops.sample(tokens, dev(logits), dev(temps), dev(us))
+    got = tokens.cpu().tolist()
+    assert got[0] == 5 and got[5] == int(np.argmax(logits[5]))  # tiny temperature = greedy
+    for r in range(1, 5):
+        dist = plain.sample_distribution(logits[r], temperature=float(temps[r]))
+        cdf = np.cumsum(dist)
+        lo = cdf[got[r] - 1] if got[r] else 0.0
+        assert lo - 1e-5 <= us[r] < cdf[got[r]] + 1e-5, f"row {r}: {got[r]} is not where the CDF passes u"
+
+
+@pytest.mark.parametrize("vocab", [379, 5000])
+def test_sample_chain_against_plain(ops, vocab):
+    from alofa_b200.sampling.params import SamplingParams
+    from alofa_b200.sampling.sampler import sample_chain_rows
+
+    rng = np.random.default_rng(vocab)
+    rows, logits, want = [], [], []
+    for trial in range(64):
+        x = rng.normal(0, 2, size=vocab).astype(np.float32)
+        if trial % 4 == 0:
+            x[rng.integers(0, vocab, 40)] = x[0]  # ties
+        p = SamplingParams(
+            temperature=float(rng.choice([0.0, 0.5, 1.0, 1.7])), top_k=int(rng.choice([0, 1, 5, 50])), top_p=float(rng.choice([1.0, 0.9, 0.5, 0.1])),
+            min_p=float(rng.choice([0.0, 0.05, 0.3])), repetition_penalty=float(rng.choice([1.0, 1.3])), frequency_penalty=float(rng.choice([0.0, 0.2])),
+            presence_penalty=float(rng.choice([0.0, 0.4])), min_tokens_to_keep=int(rng.choice([1, 1, 3])), logit_bias={int(rng.integers(vocab)): 2.5} if trial % 3 == 0 else {},
+        )
+        hist = [int(t) for t in rng.integers(0, vocab, 30)]
+        u = float(rng.random())
+        dist = plain.sample_distribution(x, hist, p.temperature, p.top_k, p.top_p, p.min_p, p.repetition_penalty, p.frequency_penalty, p.presence_penalty, p.min_tokens_to_keep, list(p.logit_bias.items()))
+        rows.append((p, u, hist))
+        logits.append(x)
+        want.append((plain.pick_from(dist, u), dist, u))
+    got = sample_chain_rows(dev(np.stack(logits)), rows).cpu().tolist()
+    for g, (w, dist, u) in zip(got, want):
+        if g != w:  # allowed only when u sits within fp32 rounding of a CDF step
+            cdf = np.cumsum(dist)
+            assert dist[g] > 0 and min(abs(u - cdf[w]), abs(u - (cdf[w - 1] if w else 0.0))) < 1e-5, (g, w)
