@@ -1,0 +1,401 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (sm_100a):
+//   y[t, f] = sum_k x[t, k] * W[f, k]   (+ bias, fused epilogue)
+// W [N, K] and x [T, K] are row-major (K contiguous), accumulation is fp32.
+//
+// The weight is the M operand: one CTA owns 128 output features and BN tokens,
+// so the same kernel streams weights for a handful of decode tokens (BN = 16)
+// and computes prompt portions (BN up to 256).  Per 64-deep k-slice a producer
+// thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the
+// weight tile [128 x 64] and the token tile [BN x 64] into a ring of shared
+// memory stages; one thread issues tcgen05.mma (M = 128, N = BN, K = 16, four
+// per slice) accumulating in tensor memory; four epilogue warps read the
+// accumulator with tcgen05.ld (lane = feature) and write it out:
+//   EPI_STORE    out[t, f] = acc + bias[f]                (bf16 or fp32)
+//   EPI_RESIDUAL out[t, f] += acc + bias[f]               (fp32 residual stream)
+//   EPI_GATED    W = [gate; up]: out[t, f] = silu(g) * u  (two accumulators)
+//   EPI_PARTIAL  ws[z, t, f] = acc                        (split-K; see reduce)
+// Split-K (grid.z > 1) spreads the k-slices of one tile over several CTAs so
+// that a small token count still pulls weights through every SM; the partial
+// sums are added in a fixed order by alofa_splitk_reduce.
+//
+// Every wait on an mbarrier is bounded: after the limit the CTA raises the
+// status word, skips its remaining work, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED = 2 };
+
+constexpr int BM = 128;        // features per CTA (UMMA M)
+constexpr int BK = 64;         // k-slice: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;  // warp 0 producer, warp 1 MMA, warps 2-5 epilogue
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle:
+// rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+struct GemmArgs {
+  void* out;          // EPI_STORE/GATED: [T, N] bf16 or fp32; EPI_RESIDUAL: [T, N] fp32
+  float* partial;     // split-K: [splits, n_acc, T, N] fp32
+  const float* bias;  // [N] (GATED: [2N]) or null
+  int T, N, K;        // tokens, output features (GATED: per half), depth
+  int k_slices_per_split;
+  int out_bf16;
+  int* status;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args, const int stages) {
+  constexpr int N_ACC = (EPI == EPI_GATED) ? 2 : 1;
+  constexpr uint32_t A_BYTES = BM * BK * 2;
+  constexpr uint32_t B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = (N_ACC * BN <= 32) ? 32 : (N_ACC * BN <= 64) ? 64 : (N_ACC * BN <= 128) ? 128 : (N_ACC * BN <= 256) ? 256 : 512;
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[12], empty_bar[12], acc_bar;
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
+  const int total_slices = (args.K + BK - 1) / BK;
+  const int slice_begin = blockIdx.z * args.k_slices_per_split;
+  const int slice_end = min(total_slices, slice_begin + args.k_slices_per_split);
+  const int n_slices = slice_end - slice_begin;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) tmem_alloc(&tmem_base_smem, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- producer: TMA loads into the ring --------------------------------
+      for (int i = 0; i < n_slices; ++i) {
+        const int s = i % stages;
+        if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1, &abort_flag)) break;
+        uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        const int k = (slice_begin + i) * BK;
+        tma_load_2d(stage, &map_w, &full_bar[s], k, f0);
+        if (N_ACC == 2) tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, args.N + f0);
+        tma_load_2d(stage + N_ACC * A_BYTES, &map_x, &full_bar[s], k, t0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer --------------------------------------------------------
+      bool ok = true;
+      for (int i = 0; i < n_slices && ok; ++i) {
+        const int s = i % stages;
+        ok = mbar_wait(&full_bar[s], (i / stages) & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+        const uint64_t desc_b = smem_desc_sw128(stage + N_ACC * A_BYTES);
+#pragma unroll
+        for (int a = 0; a < N_ACC; ++a) {
+          const uint64_t desc_a = smem_desc_sw128(stage + a * A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_base + a * BN, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
+      }
+      umma_commit(&acc_bar);  // the accumulator is complete once all MMAs are done
+    }
+  } else {
+    // ---- epilogue: 4 warps, warp q reads lanes [32q, 32q + 32) ------------------
+    const int q = warp & 3;
+    const int f = f0 + q * 32 + lane;
+    const bool f_ok = f < args.N;
+    bool ok = n_slices > 0 ? mbar_wait(&acc_bar, 0, &abort_flag) : true;
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (ok) {
+      const bool split = gridDim.z > 1;
+      float bias0 = 0.f, bias1 = 0.f;
+      if (!split && args.bias && f_ok) {
+        bias0 = args.bias[f];
+        if (N_ACC == 2) bias1 = args.bias[args.N + f];
+      }
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= args.T) break;
+        uint32_t r0[16], r1[16];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        if (n_slices > 0) {
+          tmem_ld16(taddr, r0);
+          if (N_ACC == 2) tmem_ld16(taddr + BN, r1);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r0[j] = r1[j] = 0u;
+        }
+        if (!f_ok) continue;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + c0 + j;
+          if (t >= args.T) break;
+          const float a0 = __uint_as_float(r0[j]);
+          if (split) {
+            const size_t plane = (size_t)args.T * args.N;
+            float* p = args.partial + (size_t)blockIdx.z * N_ACC * plane + (size_t)t * args.N + f;
+            p[0] = a0;
+            if (N_ACC == 2) p[plane] = __uint_as_float(r1[j]);
+          } else if (EPI == EPI_GATED) {
+            const float g = a0 + bias0, u = __uint_as_float(r1[j]) + bias1;
+            const float y = g / (1.0f + __expf(-g)) * u;
+            if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
+            else ((float*)args.out)[(size_t)t * args.N + f] = y;
+          } else if (EPI == EPI_RESIDUAL) {
+            float* o = (float*)args.out + (size_t)t * args.N + f;
+            *o = *o + (a0 + bias0);
+          } else {
+            const float y = a0 + bias0;
+            if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
+            else ((float*)args.out)[(size_t)t * args.N + f] = y;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
+}
+
+// ---------------------------------------------------------------------------
+// Second stage of split-K: add the partial sums in split order, then the
+// epilogue.  partial [splits, n_acc, T, N].
+// ---------------------------------------------------------------------------
+template <int EPI>
+__global__ void splitk_reduce_kernel(void* __restrict__ out, const float* __restrict__ partial, const float* __restrict__ bias, int T, int N,
+                                     int splits, int out_bf16) {
+  constexpr int N_ACC = (EPI == EPI_GATED) ? 2 : 1;
+  const size_t plane = (size_t)T * N;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= plane) return;
+  const int f = (int)(idx % N);
+  float a0 = 0.f, a1 = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    a0 += partial[(size_t)z * N_ACC * plane + idx];
+    if (N_ACC == 2) a1 += partial[(size_t)z * N_ACC * plane + plane + idx];
+  }
+  if (bias) {
+    a0 += bias[f];
+    if (N_ACC == 2) a1 += bias[N + f];
+  }
+  float y = a0;
+  if (EPI == EPI_GATED) y = a0 / (1.0f + __expf(-a0)) * a1;
+  if (EPI == EPI_RESIDUAL) {
+    ((float*)out)[idx] += y;
+  } else if (out_bf16) {
+    ((bf16*)out)[idx] = __float2bfloat16_rn(y);
+  } else {
+    ((float*)out)[idx] = y;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, K] bf16 row-major matrix seen as boxes of [box_rows, 64] with 128-byte swizzle.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int EPI>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& args, int splits, cudaStream_t stream) {
+  constexpr int N_ACC = (EPI == EPI_GATED) ? 2 : 1;
+  constexpr size_t STAGE = (size_t)N_ACC * BM * BK * 2 + (size_t)BN * BK * 2;
+  int stages = (int)((200 * 1024) / STAGE);
+  if (stages > 12) stages = 12;
+  if (stages < 2) return ALOFA_ERR_ARGUMENT;
+  const size_t smem = STAGE * stages + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
+      return ALOFA_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid((args.N + BM - 1) / BM, (args.T + BN - 1) / BN, splits);
+  gemm_tc_kernel<BN, EPI><<<grid, NUM_THREADS, smem, stream>>>(mw, mx, args, stages);
+  return launch_status();
+}
+
+template <int EPI>
+static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& args, int splits, cudaStream_t stream) {
+  switch (bn) {
+    case 16: return launch_tc<16, EPI>(mw, mx, args, splits, stream);
+    case 32: return launch_tc<32, EPI>(mw, mx, args, splits, stream);
+    case 64: return launch_tc<64, EPI>(mw, mx, args, splits, stream);
+    case 128: return launch_tc<128, EPI>(mw, mx, args, splits, stream);
+    case 256: return launch_tc<256, EPI>(mw, mx, args, splits, stream);
+    default: return ALOFA_ERR_ARGUMENT;
+  }
+}
+
+// out = x W^T with the epilogue `epi`.  x [T, K] bf16, w [N (GATED: 2N), K] bf16.
+// bn: tokens per CTA (16..256).  splits > 1 needs `partial` of
+// splits * (GATED ? 2 : 1) * T * N floats and runs the reduce kernel after.
+// Returns ALOFA_ERR_ARGUMENT for sizes this kernel does not take (K % 8 != 0,
+// pointers not 16-byte aligned).
+ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float* bias, float* partial, int T, int N, int K, int epi, int out_bf16,
+                            int bn, int splits, int* status, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return ALOFA_OK;
+  if (K <= 0 || (K % 8) != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ALOFA_ERR_ARGUMENT;
+  if (epi == EPI_RESIDUAL && out_bf16) return ALOFA_ERR_ARGUMENT;
+  const int total_slices = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > total_slices) splits = total_slices;
+  if (splits > 1 && !partial) return ALOFA_ERR_ARGUMENT;
+  const int w_rows = (epi == EPI_GATED) ? 2 * N : N;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, w, w_rows, K, BM) || !make_map(&mx, x, T, K, bn)) return ALOFA_ERR_ARGUMENT;
+  GemmArgs args;
+  args.out = out;
+  args.partial = partial;
+  args.bias = bias;
+  args.T = T;
+  args.N = N;
+  args.K = K;
+  args.k_slices_per_split = (total_slices + splits - 1) / splits;
+  splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;  // no empty split
+  args.out_bf16 = out_bf16;
+  args.status = status;
+  int rc;
+  if (epi == EPI_STORE) rc = dispatch_bn<EPI_STORE>(bn, mw, mx, args, splits, stream);
+  else if (epi == EPI_RESIDUAL) rc = dispatch_bn<EPI_RESIDUAL>(bn, mw, mx, args, splits, stream);
+  else if (epi == EPI_GATED) rc = dispatch_bn<EPI_GATED>(bn, mw, mx, args, splits, stream);
+  else return ALOFA_ERR_ARGUMENT;
+  if (rc != ALOFA_OK || splits == 1) return rc;
+  const size_t plane = (size_t)T * N;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((plane + threads - 1) / threads);
+  if (epi == EPI_STORE) splitk_reduce_kernel<EPI_STORE><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  else if (epi == EPI_RESIDUAL) splitk_reduce_kernel<EPI_RESIDUAL><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  else splitk_reduce_kernel<EPI_GATED><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  return launch_status();
+}
+
+// How many splits alofa_gemm_tc will really use (it never leaves one empty).
+ALOFA_API int alofa_gemm_tc_splits(int K, int splits) {
+  const int total = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > total) splits = total;
+  const int per = (total + splits - 1) / splits;
+  return (total + per - 1) / per;
+}

@@ -9,4 +9,5 @@ def all_libraries() -> list:
         {"name": "alofa_scheduler", "sources": ["host/scheduler.cpp"], "cuda": False},
         {"name": "alofa_generic", "sources": ["kernels/generic.cu"]},
         {"name": "alofa_sampling", "sources": ["kernels/sampling.cu"]},
+        {"name": "alofa_gemm_tc", "sources": ["kernels/gemm_tc.cu"]},
     ]

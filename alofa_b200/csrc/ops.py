@@ -66,6 +66,18 @@ def _sampling():
     return lib
 
 
+def _gemm_tc():
+    lib = _libs.get("gemm_tc")
+    if lib is None:
+        lib = load_library("alofa_gemm_tc", ["kernels/gemm_tc.cu"])
+        lib.alofa_gemm_tc.restype = _I
+        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]
+        lib.alofa_gemm_tc_splits.restype = _I
+        lib.alofa_gemm_tc_splits.argtypes = [_I, _I]
+        _libs["gemm_tc"] = lib
+    return lib
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -204,3 +216,31 @@ def sample_chain(tokens, logits, work, fparams, iparams, bias_start, bias_index,
         ),
         "sample_chain", f"vocab={vocab}",
     )
+
+
+def gemm_tc_splits(k: int, splits: int) -> int:
+    """The number of k-splits gemm_tc really uses for depth ``k``."""
+    return _gemm_tc().alofa_gemm_tc_splits(k, splits)
+
+
+def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None) -> bool:
+    """Tensor-core product ``out = x @ w.T`` (bf16 operands, fp32 sums) with
+    the epilogue fused.  Returns False, having launched nothing, when the
+    kernel does not take these sizes (depth not a multiple of 8, unaligned)."""
+    m, k = x.shape
+    n = out.shape[1]
+    rows_w = 2 * n if epi == EPI_GATED else n
+    if w.shape != (rows_w, k) or out.shape[0] != m or (bias is not None and bias.shape[0] != rows_w):
+        raise AlofaError("invalid_argument", "gemm sizes disagree", f"out={tuple(out.shape)} x={tuple(x.shape)} w={tuple(w.shape)} epi={epi}")
+    rc = _gemm_tc().alofa_gemm_tc(
+        _dev(out, "out"), _dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
+        _dev(bias, "bias", torch.float32) if bias is not None else None,
+        _dev(partial, "partial", torch.float32) if partial is not None else None,
+        m, n, k, epi, _is_bf16(out, "out"), bn, splits, _dev(status, "status", torch.int32) if status is not None else None, _stream(),
+    )
+    if rc == 1:
+        return False
+    _done(rc, "gemm_tc", f"M={m} N={n} K={k} epi={epi} bn={bn} splits={splits}")
+    if splits > 1:
+        count_launches(1)
+    return True

@@ -42,11 +42,14 @@ class Model:
         return {i: self.layers[layer].cache_spec() for i, (layer, cache) in enumerate(self.run) if cache == i}
 
     def forward(self, ctx, caches: dict) -> torch.Tensor:
-        """Logits (fp32) at ``ctx.logit_rows`` for the step's tokens."""
+        """Logits (fp32) at ``ctx.logit_rows`` for the step's tokens (None when
+        no row is wanted; the final norm and the head run on wanted rows only)."""
         h = ctx.buf((ctx.n_tokens, self.spec.hidden_size), torch.float32)
         self.embedding.forward(ctx, h)
         for i, (layer, cache) in enumerate(self.run):
             self.layers[layer].forward(ctx, h, caches.get(cache), writes=(cache == i))
+        if ctx.n_out == 0:  # a prompt portion whose logits nobody wants
+            return None
         x = self.final_norm.forward(ctx, h, ctx.logit_rows)
         return self.head.forward(ctx, x)
 
