@@ -1,0 +1,361 @@
+// Causal grouped-query attention over the paged bfloat16 cache, for prefill
+// portions and decode tokens in one launch.
+//
+// One CTA owns one (request, KV head, tile of 64 query rows).  A query row is a
+// (token, head-of-the-group) pair: the g = heads / kv_heads query heads that
+// share a KV head are packed along the row axis, so the K/V pages of that head
+// are read once for all of them (for one decode token the tile holds its g
+// heads).  Keys are streamed in blocks of 64 through shared memory with
+// cp.async (double buffered), found through the request's block table row by
+// row, so any page size works.  Scores and the output accumulate in fp32 with
+// mma.sync m16n8k16 (bf16 operands); softmax is the streaming form in fp32:
+// running maximum, exp2 with the scale folded in, rescaled sums.
+// Visibility: key j is seen by the row at position P when j <= P and, with a
+// window, j > P - window.
+//
+// Decode-only launches may split the keys of a request over several CTAs
+// (split s owns keys [s * split_keys, (s + 1) * split_keys), a function of the
+// key index alone); the partial (output, maximum, sum) triples are merged by
+// attention_combine_kernel in split order.
+//
+// HEAD_DIM is a compile-time constant (a multiple of 16 up to 128): the
+// library is built per head size.  Formulas: src/alofa/kernels/cpu/scalar.mojo:392-470,
+// paged addressing src/alofa/kernels/cpu/paged.mojo:249-336.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 64
+#endif
+
+constexpr int HD = HEAD_DIM;
+constexpr int BLOCK_M = 64;   // query rows per CTA (4 warps x 16)
+constexpr int BLOCK_N = 64;   // keys per block
+constexpr int ROW = HD + 8;   // shared-memory row in elements: 16 bytes of padding keep ldmatrix conflict-free
+constexpr int KSTEPS = HD / 16;
+constexpr int DTILES = HD / 8;
+constexpr int CHUNKS = HD / 8;  // 16-byte chunks per row
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head_dim must be a multiple of 16 between 16 and 128");
+
+struct AttnParams {
+  bf16* out;             // [T, nh, HD]
+  const bf16* q;         // [T, nh, HD]
+  const bf16* k_cache;   // [slots, nkv, HD]
+  const bf16* v_cache;
+  const int* q_start;    // [R + 1] first row of each request in this step
+  const int* kv_len;     // [R] keys of each request after this step
+  const int* block_table;  // [R, max_blocks]
+  float* partial_o;      // split mode: [splits, T * nh, HD]
+  float* partial_ml;     // split mode: [splits, T * nh, 2]
+  int max_blocks, page_size, nh, nkv, window, split_keys, n_rows_total;
+  float scale_log2;      // scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t smem, const void* gptr, bool pred) {
+  const int bytes = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem), "l"(gptr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copy keys [j0, j0 + 64) of one KV head into a shared tile [64][ROW]; rows past
+// j_end (exclusive) or before j_begin are zero-filled.
+__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* cache, const int* table, int page_size, int nkv, int kvh, int j0,
+                                             int j_begin, int j_end) {
+  for (int idx = threadIdx.x; idx < BLOCK_N * CHUNKS; idx += 128) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const int j = j0 + r;
+    const bool ok = j >= j_begin && j < j_end;
+    const bf16* src = cache;
+    if (ok) {
+      const int page = table[j / page_size];
+      const size_t slot = (size_t)page * page_size + (j % page_size);
+      src = cache + (slot * nkv + kvh) * HD + c * 8;
+    }
+    cp_async16((uint32_t)__cvta_generic_to_shared(tile + r * ROW + c * 8), src, ok);
+  }
+}
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);          // [64][ROW]
+  bf16* k_tiles = q_tile + BLOCK_M * ROW;                    // [2][64][ROW]
+  bf16* v_tiles = k_tiles + 2 * BLOCK_N * ROW;               // [2][64][ROW]
+
+  const int seq = blockIdx.z, kvh = blockIdx.y;
+  const int g = p.nh / p.nkv;
+  const int row_begin = p.q_start[seq];
+  const int q_len = p.q_start[seq + 1] - row_begin;
+  const int kv_len = p.kv_len[seq];
+  const int pos0 = kv_len - q_len;
+  const int n_rows = q_len * g;
+  const int tile = SPLIT ? 0 : blockIdx.x;
+  const int row0 = tile * BLOCK_M;
+  if (row0 >= n_rows) return;
+  const int last_row = min(n_rows, row0 + BLOCK_M) - 1;
+  const int t_first = row0 / g, t_last = last_row / g;
+  int k_hi = pos0 + t_last;  // last visible key of the tile (inclusive)
+  int k_lo = 0;
+  if (p.window > 0) k_lo = max(0, pos0 + t_first - p.window + 1);
+  if (SPLIT) {
+    k_lo = max(k_lo, (int)blockIdx.x * p.split_keys);
+    k_hi = min(k_hi, ((int)blockIdx.x + 1) * p.split_keys - 1);
+    if (k_lo > k_hi) return;
+  }
+  const int* table = p.block_table + (size_t)seq * p.max_blocks;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- stage the query tile: row r = (token r / g, head kvh * g + r % g) ----
+  for (int idx = threadIdx.x; idx < BLOCK_M * CHUNKS; idx += 128) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const int row = row0 + r;
+    const bool ok = row < n_rows;
+    const bf16* src = p.q;
+    if (ok) src = p.q + ((size_t)(row_begin + row / g) * p.nh + kvh * g + row % g) * HD + c * 8;
+    cp_async16((uint32_t)__cvta_generic_to_shared(q_tile + r * ROW + c * 8), src, ok);
+  }
+  const int nb_lo = k_lo / BLOCK_N, nb_hi = k_hi / BLOCK_N;
+  load_kv_tile(k_tiles, p.k_cache, table, p.page_size, p.nkv, kvh, nb_lo * BLOCK_N, k_lo, k_hi + 1);
+  load_kv_tile(v_tiles, p.v_cache, table, p.page_size, p.nkv, kvh, nb_lo * BLOCK_N, k_lo, k_hi + 1);
+  cp_async_commit();
+
+  // this thread's two rows of the warp's 16-row slab
+  const int r_lo = row0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const int pos_lo = pos0 + min(r_lo, n_rows - 1) / g, pos_hi = pos0 + min(r_hi, n_rows - 1) / g;
+  const int warp_pos_min = pos0 + min(row0 + warp * 16, n_rows - 1) / g;
+  const int warp_pos_max = pos0 + min(row0 + warp * 16 + 15, n_rows - 1) / g;
+
+  uint32_t qf[KSTEPS][4];
+  float o[DTILES][4];
+#pragma unroll
+  for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+  for (int nb = nb_lo; nb <= nb_hi; ++nb) {
+    const int buf = (nb - nb_lo) & 1;
+    if (nb < nb_hi) {  // prefetch the next block into the other buffer
+      load_kv_tile(k_tiles + (buf ^ 1) * BLOCK_N * ROW, p.k_cache, table, p.page_size, p.nkv, kvh, (nb + 1) * BLOCK_N, k_lo, k_hi + 1);
+      load_kv_tile(v_tiles + (buf ^ 1) * BLOCK_N * ROW, p.v_cache, table, p.page_size, p.nkv, kvh, (nb + 1) * BLOCK_N, k_lo, k_hi + 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (nb == nb_lo) {
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const bf16* src = q_tile + (warp * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8;
+        ldmatrix_x4(qf[ks], (uint32_t)__cvta_generic_to_shared(src));
+      }
+    }
+    const bf16* kt = k_tiles + buf * BLOCK_N * ROW;
+    const bf16* vt = v_tiles + buf * BLOCK_N * ROW;
+
+    // ---- S = Q K^T : 16 rows x 64 keys per warp ---------------------------------
+    float s[BLOCK_N / 8][4];
+#pragma unroll
+    for (int n = 0; n < BLOCK_N / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+      for (int n2 = 0; n2 < BLOCK_N / 16; ++n2) {
+        // keys n2*16 .. +15, dims ks*16 .. +15: four 8x8 matrices
+        uint32_t kf[4];
+        const bf16* src = kt + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * ROW + ks * 16 + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(kf, (uint32_t)__cvta_generic_to_shared(src));
+        mma_16816(s[2 * n2], qf[ks], kf[0], kf[1]);
+        mma_16816(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
+      }
+    }
+    // ---- visibility -------------------------------------------------------------
+    const int j0 = nb * BLOCK_N;
+    const bool all_visible = (j0 + BLOCK_N - 1 <= min(warp_pos_min, k_hi)) && (j0 >= k_lo) &&
+                             (p.window <= 0 || j0 > warp_pos_max - p.window);
+    if (!all_visible) {
+#pragma unroll
+      for (int n = 0; n < BLOCK_N / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + n * 8 + (lane & 3) * 2 + (e & 1);
+          const int pos = (e < 2) ? pos_lo : pos_hi;
+          bool vis = j <= pos && j >= k_lo && j <= k_hi;
+          if (p.window > 0) vis = vis && j > pos - p.window;
+          if (!vis) s[n][e] = -INFINITY;
+        }
+      }
+    }
+    // ---- streaming softmax ----------------------------------------------------------
+    float bm_lo = -INFINITY, bm_hi = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < BLOCK_N / 8; ++n) {
+      bm_lo = fmaxf(bm_lo, fmaxf(s[n][0], s[n][1]));
+      bm_hi = fmaxf(bm_hi, fmaxf(s[n][2], s[n][3]));
+    }
+    bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 1));
+    bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 2));
+    bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 1));
+    bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 2));
+    const float mn_lo = fmaxf(m_lo, bm_lo), mn_hi = fmaxf(m_hi, bm_hi);
+    const float base_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo * p.scale_log2;
+    const float base_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi * p.scale_log2;
+    const float corr_lo = (m_lo == -INFINITY) ? 0.f : exp2f(m_lo * p.scale_log2 - base_lo);
+    const float corr_hi = (m_hi == -INFINITY) ? 0.f : exp2f(m_hi * p.scale_log2 - base_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    float sum_lo = 0.f, sum_hi = 0.f;
+    uint32_t pf[BLOCK_N / 16][4];
+#pragma unroll
+    for (int n = 0; n < BLOCK_N / 8; ++n) {
+      const float p0 = exp2f(s[n][0] * p.scale_log2 - base_lo), p1 = exp2f(s[n][1] * p.scale_log2 - base_lo);
+      const float p2 = exp2f(s[n][2] * p.scale_log2 - base_hi), p3 = exp2f(s[n][3] * p.scale_log2 - base_hi);
+      sum_lo += p0 + p1;
+      sum_hi += p2 + p3;
+      // the accumulator layout of two adjacent 8-key tiles is the A layout of one 16-key step
+      pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+      pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+    l_lo = l_lo * corr_lo + sum_lo;
+    l_hi = l_hi * corr_hi + sum_hi;
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+      o[d][0] *= corr_lo;
+      o[d][1] *= corr_lo;
+      o[d][2] *= corr_hi;
+      o[d][3] *= corr_hi;
+    }
+    // ---- O += P V ---------------------------------------------------------------------
+#pragma unroll
+    for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+#pragma unroll
+      for (int d2 = 0; d2 < HD / 16; ++d2) {
+        // keys kk*16 .. +15 (k), dims d2*16 .. +15 (n): transposed 8x8 loads
+        uint32_t vf[4];
+        const bf16* src = vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROW + d2 * 16 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(vf, (uint32_t)__cvta_generic_to_shared(src));
+        mma_16816(o[2 * d2], pf[kk], vf[0], vf[1]);
+        mma_16816(o[2 * d2 + 1], pf[kk], vf[2], vf[3]);
+      }
+    }
+    __syncthreads();  // everyone is done with this buffer before it is refilled
+  }
+  // ---- finish ---------------------------------------------------------------------------
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = half ? r_hi : r_lo;
+    if (row >= n_rows) continue;
+    const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
+    const size_t out_row = (size_t)(row_begin + row / g) * p.nh + kvh * g + row % g;
+    if (SPLIT) {
+      float* po = p.partial_o + ((size_t)blockIdx.x * p.n_rows_total + out_row) * HD;
+#pragma unroll
+      for (int d = 0; d < DTILES; ++d)
+        *reinterpret_cast<float2*>(po + d * 8 + (lane & 3) * 2) = make_float2(o[d][half * 2], o[d][half * 2 + 1]);
+      if ((lane & 3) == 0) {
+        float* ml = p.partial_ml + ((size_t)blockIdx.x * p.n_rows_total + out_row) * 2;
+        ml[0] = (m == -INFINITY) ? -INFINITY : m * p.scale_log2;
+        ml[1] = l;
+      }
+    } else {
+      const float inv = 1.0f / l;
+      bf16* po = p.out + out_row * HD;
+#pragma unroll
+      for (int d = 0; d < DTILES; ++d)
+        *reinterpret_cast<uint32_t*>(po + d * 8 + (lane & 3) * 2) = pack_bf16(o[d][half * 2] * inv, o[d][half * 2 + 1] * inv);
+    }
+  }
+}
+
+// Merge the splits of every (token, head) row in split order.  One block of HD
+// threads per row; rows are decode tokens (one query position per request).
+__global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                                         const int* __restrict__ kv_len, int nh, int window, int split_keys, int n_rows_total) {
+  const int row = blockIdx.x;       // token * nh + head; one token per request
+  const int seq = row / nh;
+  const int P = kv_len[seq] - 1;
+  int k_lo = 0;
+  if (window > 0) k_lo = max(0, P - window + 1);
+  const int s_lo = k_lo / split_keys, s_hi = P / split_keys;
+  float m = -INFINITY;
+  for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, partial_ml[((size_t)s * n_rows_total + row) * 2]);
+  float l = 0.f, acc = 0.f;
+  const int d = threadIdx.x;
+  for (int s = s_lo; s <= s_hi; ++s) {
+    const float* ml = partial_ml + ((size_t)s * n_rows_total + row) * 2;
+    const float w = (ml[0] == -INFINITY) ? 0.f : exp2f(ml[0] - m);
+    l += ml[1] * w;
+    acc += partial_o[((size_t)s * n_rows_total + row) * HD + d] * w;
+  }
+  out[(size_t)row * HD + d] = __float2bfloat16_rn(acc / l);
+}
+
+static size_t attention_smem_bytes() { return (size_t)(BLOCK_M + 4 * BLOCK_N) * ROW * sizeof(bf16); }
+
+ALOFA_API int alofa_attention_head_dim() { return HD; }
+
+// tiles: query tiles of the longest request = ceil(max_q_len * g / 64).  n_splits > 0
+// selects split mode (every request has exactly one token in this step and
+// g <= 64); partial_o / partial_ml must then hold n_splits planes.
+ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len,
+                                   const int* block_table, int max_blocks, int page_size, int n_seqs, int n_tokens, int tiles, int nh, int nkv,
+                                   int window, float scale, int n_splits, int split_keys, float* partial_o, float* partial_ml,
+                                   cudaStream_t stream) {
+  if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
+  if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || tiles <= 0) return ALOFA_ERR_ARGUMENT;
+  if (n_splits > 0 && (nh / nkv > BLOCK_M || split_keys <= 0 || split_keys % BLOCK_N != 0 || !partial_o || !partial_ml || n_seqs != n_tokens))
+    return ALOFA_ERR_ARGUMENT;
+  AttnParams p;
+  p.out = (bf16*)out;
+  p.q = (const bf16*)q;
+  p.k_cache = (const bf16*)k_cache;
+  p.v_cache = (const bf16*)v_cache;
+  p.q_start = q_start;
+  p.kv_len = kv_len;
+  p.block_table = block_table;
+  p.partial_o = partial_o;
+  p.partial_ml = partial_ml;
+  p.max_blocks = max_blocks;
+  p.page_size = page_size;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.window = window;
+  p.split_keys = split_keys;
+  p.n_rows_total = n_tokens * nh;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const size_t smem = attention_smem_bytes();
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return ALOFA_ERR_LAUNCH;
+    configured = true;
+  }
+  if (n_splits > 0) {
+    attention_bf16_kernel<true><<<dim3(n_splits, nkv, n_seqs), 128, smem, stream>>>(p);
+    if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    attention_combine_kernel<<<n_tokens * nh, HD, 0, stream>>>((bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
+  } else {
+    attention_bf16_kernel<false><<<dim3(tiles, nkv, n_seqs), 128, smem, stream>>>(p);
+  }
+  return launch_status();
+}

@@ -10,4 +10,5 @@ def all_libraries() -> list:
         {"name": "alofa_generic", "sources": ["kernels/generic.cu"]},
         {"name": "alofa_sampling", "sources": ["kernels/sampling.cu"]},
         {"name": "alofa_gemm_tc", "sources": ["kernels/gemm_tc.cu"]},
+        *[{"name": f"alofa_attention_hd{hd}", "sources": ["kernels/attention_bf16.cu"], "defines": {"HEAD_DIM": hd}} for hd in (16, 32, 48, 64, 128)],
     ]

@@ -97,7 +97,22 @@ class GQAttention(Part):
         self.attend(ctx, attn, q, cache, group)
         self.out(h, attn)
 
+    SPLIT_KEYS = 256  # keys per CTA when a decode-only step splits each request's keys
+
     def attend(self, ctx, out, q, cache, group):
+        """Attention of the step's rows over the cache: the tensor-core kernel
+        for bfloat16 and head sizes it is built for, else the generic one."""
+        if q.dtype == torch.bfloat16 and ops.attention_bf16_supported(self.hd):
+            splits, po, pml = 0, None, None
+            if ctx.decode_only and self.nh // self.nkv <= 64 and ctx.max_kv_len > self.SPLIT_KEYS:
+                splits = -(-ctx.max_kv_len // self.SPLIT_KEYS)
+                po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
+                pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
+            ops.attention_bf16(
+                out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
+                self.nh, self.nkv, self.hd, self.window, self.scale, splits, self.SPLIT_KEYS, po, pml,
+            )
+            return
         ops.paged_attention_generic(
             out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
             self.nh, self.nkv, self.hd, self.window, self.scale,

@@ -108,7 +108,7 @@ def test_rope_store(ops, dtype, hd, rot):
     assert_close(v_cache.float().cpu().reshape(32, -1), want_v, 0.0, "v cache")
 
 
-def attention_case(ops, dtype, hd, nh, nkv, lens, q_lens, page, window, rng, craft=None, given=None):
+def attention_case(ops, dtype, hd, nh, nkv, lens, q_lens, page, window, rng, craft=None, given=None, fast=False, split_keys=0):
     """Sequences of ``lens`` keys; the last ``q_lens[i]`` positions of each are
     queries in this launch.  Returns (got, want) as float64 arrays."""
     if given is not None:
@@ -133,6 +133,16 @@ def attention_case(ops, dtype, hd, nh, nkv, lens, q_lens, page, window, rng, cra
             want.append(full[p])
     q = dev(np.stack(q_rows), dtype)
     out = torch.empty_like(q)
+    if fast:
+        q_start = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+        n_splits, po, pml = 0, None, None
+        if split_keys:
+            n_splits = -(-max(lens) // split_keys)
+            po = torch.empty(n_splits, len(q_rows) * nh, hd, device="cuda")
+            pml = torch.empty(n_splits, len(q_rows) * nh, 2, device="cuda")
+        ops.attention_bf16(out, q, k_cache, v_cache, dev(q_start), dev(np.array(lens, dtype=np.int32)), table, page, len(lens), max(q_lens),
+                           nh, nkv, hd, window, 1.0 / np.sqrt(hd), n_splits, split_keys, po, pml)
+        return out.float().cpu().numpy().astype(np.float64), np.stack(want)
     ops.paged_attention_generic(out, q, k_cache, v_cache, dev(np.array(positions, dtype=np.int32)), dev(np.array(seq_of, dtype=np.int32)),
                                 table, page, nh, nkv, hd, window, 1.0 / np.sqrt(hd))
     return out.float().cpu().numpy().astype(np.float64), np.stack(want)
@@ -186,6 +196,60 @@ def test_attention_window_edge(ops, dtype, window):
         got, want = attention_case(ops, dtype, hd, nh, nkv, lens=[n], q_lens=[1], page=16, window=window, rng=rng, craft=craft)
         assert (np.abs(want[0]).min() > 45.0) == seen
         assert_close(got, want, TOL[dtype], f"window {window} offset {offset}")
+
+
+@pytest.mark.parametrize("hd, nh, nkv", [(16, 4, 2), (32, 3, 1), (48, 5, 5), (64, 14, 2), (80, 6, 3), (128, 8, 1)])
+@pytest.mark.parametrize("page", [16, 48, 64])
+def test_attention_bf16_sizes_portions_and_windows(ops, hd, nh, nkv, page):
+    """The tensor-core kernel: whole prompts, portions that start mid-sequence,
+    single tokens, in one launch; with and without a window."""
+    for window in (None, 40):
+        rng = np.random.default_rng(hd + page)
+        got, want = attention_case(ops, BF16, hd, nh, nkv, lens=[1, 37, 300, 129, 200, 64], q_lens=[1, 37, 2, 1, 131, 64], page=page, window=window, rng=rng, fast=True)
+        assert_close(got, want, TOL[BF16], f"hd={hd} page={page} window={window}")
+
+
+@pytest.mark.parametrize("hd, nh, nkv", [(64, 14, 2), (32, 3, 1), (128, 8, 8)])
+def test_attention_bf16_split_keys(ops, hd, nh, nkv):
+    """Decode tokens with each request's keys split over several CTAs."""
+    for window in (None, 300):
+        rng = np.random.default_rng(hd)
+        lens = [1, 63, 64, 65, 300, 1000, 129]
+        got, want = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=[1] * len(lens), page=16, window=window, rng=rng, fast=True, split_keys=128)
+        assert_close(got, want, TOL[BF16], f"split hd={hd} window={window}")
+        whole, _ = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=[1] * len(lens), page=16, window=window, rng=np.random.default_rng(hd), fast=True)
+        assert_close(got, whole, TOL[BF16], "split vs unsplit")
+
+
+def test_attention_bf16_far_key_and_window_edge(ops):
+    hd, nh, nkv = 64, 4, 2
+    for split in (0, 64):
+        for far in (0, 63, 64, 127, 128, 500, 699):
+            rng = np.random.default_rng(far)
+
+            def craft(qs, ks, vs, far=far):
+                direction = rng.normal(size=hd)
+                direction /= np.linalg.norm(direction)
+                qs[0][-1, :] = np.tile(12.0 * direction, nh)
+                ks[0][far, :] = np.tile(12.0 * direction, nkv)
+                vs[0][far, :] = 100.0
+
+            got, want = attention_case(ops, BF16, hd, nh, nkv, lens=[700], q_lens=[1], page=16, window=None, rng=rng, craft=craft, fast=True, split_keys=split)
+            assert np.abs(want[0]).min() > 90.0
+            assert_close(got, want, TOL[BF16], f"far key at {far} split {split}")
+        for window in (1, 64, 65, 129):
+            for offset, seen in ((window - 1, True), (window, False)):
+                rng = np.random.default_rng(window)
+
+                def craft(qs, ks, vs, offset=offset):
+                    direction = np.ones(hd) / np.sqrt(hd)
+                    qs[0][-1, :] = np.tile(14.0 * direction, nh)
+                    ks[0][299 - offset, :] = np.tile(14.0 * direction, nkv)
+                    vs[0][299 - offset, :] = 50.0
+
+                got, want = attention_case(ops, BF16, hd, nh, nkv, lens=[300], q_lens=[1], page=16, window=window, rng=rng, craft=craft, fast=True, split_keys=split)
+                assert (np.abs(want[0]).min() > 45.0) == seen
+                assert_close(got, want, TOL[BF16], f"window {window} offset {offset} split {split}")
 
 
 def test_attention_rows_do_not_depend_on_the_batch(ops):
