@@ -48,6 +48,8 @@ def _native():
             "cm_release": (I, [P, I]),
             "cm_share_prefix": (I, [P, I, I, I]),
             "cm_block_table": (I, [P, I, I, ctypes.c_void_p, I]),
+            "cm_plan_step": (I, [P, I, P, P, P, P, P, P, I, P]),
+            "cm_commit_step": (I, [P, I, P, P]),
             "cm_free_pages": (I, [P, I]),
             "cm_num_pages": (I, [P, I]),
             "cm_reserved_len": (I, [P, I]),
@@ -161,6 +163,21 @@ class CacheManager:
         out = np.empty(self.max_blocks, dtype=np.int32)
         n = self.block_table_into(slot, group, out)
         return out[:n].copy()
+
+    def plan_step(self, slots, counts, want_counts, wants, meta_ptr: int, offsets, max_blocks: int):
+        """Reserve pages for every entry and fill the step's metadata in one
+        native call; returns (longest entry, most keys, total tokens).  The
+        arrays are int32 numpy arrays; ``meta_ptr`` addresses the int32 buffer."""
+        info = (ctypes.c_int * 3)()
+        rc = _lib.cm_plan_step(self._h, len(slots), slots.ctypes.data, counts.ctypes.data, want_counts.ctypes.data, wants.ctypes.data,
+                               meta_ptr, offsets.ctypes.data, max_blocks, info)
+        if rc == -1:
+            raise AlofaError("capacity", "the cache has too few free pages for this step", f"free={self.free_pages()}")
+        _check(rc, "plan_step")
+        return info[0], info[1], info[2]
+
+    def commit_step(self, slots, counts) -> None:
+        _check(_lib.cm_commit_step(self._h, len(slots), slots.ctypes.data, counts.ctypes.data), "commit_step")
 
     # -- books ------------------------------------------------------------
     def free_pages(self, group: Optional[int] = None):

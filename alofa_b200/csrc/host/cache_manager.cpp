@@ -263,6 +263,87 @@ int cm_block_table(void* h, int s, int g, int32_t* out, int max) {
   return n;
 }
 
+// Plan one step in a single call: for every entry (state slot, token count)
+// reserve pages for its new tokens and fill the step's metadata arrays.
+//   slots[n], counts[n]   the entries, in batch order
+//   want_counts[n], wants the wanted places of each entry (relative to its tokens)
+//   meta                  the int32 metadata buffer; off[] gives the word offset of
+//                         token-independent fields in this order: positions,
+//                         seq_of_token, q_start, kv_len, state_slots, logit_rows,
+//                         then per group slot_map, block_table
+//   max_blocks            row length of the block tables in meta
+//   info out              max tokens of an entry, max keys of an entry, total tokens
+// Token ids are copied by the caller.  Returns 0, or ERR_CAPACITY when a
+// reservation does not fit (earlier entries keep their reservation), or
+// ERR_ARGUMENT for a bad slot or place.
+int cm_plan_step(void* h, int n, const int* slots, const int* counts, const int* want_counts, const int* wants, int32_t* meta,
+                 const int* off, int max_blocks, int* info) {
+  auto* m = static_cast<Manager*>(h);
+  if (!m || n <= 0) return ERR_ARGUMENT;
+  const int G = (int)m->groups.size();
+  int32_t* positions = meta + off[0];
+  int32_t* seq_of = meta + off[1];
+  int32_t* q_start = meta + off[2];
+  int32_t* kv_len = meta + off[3];
+  int32_t* state_slots = meta + off[4];
+  int32_t* logit_rows = meta + off[5];
+  int row = 0, out = 0, want_at = 0, max_q = 0, max_kv = 0;
+  for (int i = 0; i < n; ++i) {
+    const int s = slots[i], cnt = counts[i];
+    if (s < 0 || s >= (int)m->requests.size() || !m->requests[s].live || cnt <= 0) return ERR_ARGUMENT;
+    Request& r = m->requests[s];
+    const int start = r.computed_len;
+    int rc = cm_reserve(h, s, start + cnt);
+    if (rc != 0) return rc;
+    q_start[i] = row;
+    kv_len[i] = start + cnt;
+    state_slots[i] = s;
+    for (int t = 0; t < cnt; ++t) {
+      positions[row + t] = start + t;
+      seq_of[row + t] = i;
+    }
+    for (int w = 0; w < want_counts[i]; ++w) {
+      const int place = wants[want_at++];
+      if (place < 0 || place >= cnt) return ERR_ARGUMENT;
+      logit_rows[out++] = row + place;
+    }
+    for (int g = 0; g < G; ++g) {
+      const Group& grp = m->groups[g];
+      int32_t* slot_map = meta + off[6 + 2 * g];
+      int32_t* table = meta + off[7 + 2 * g] + (size_t)i * max_blocks;
+      const int nb = (int)r.table[g].size();
+      if (nb > max_blocks) return ERR_CAPACITY;
+      for (int b = 0; b < nb; ++b) table[b] = r.table[g][b];
+      for (int b = nb; b < max_blocks; ++b) table[b] = -1;
+      for (int t = 0; t < cnt; ++t) {
+        const int p = start + t;
+        slot_map[row + t] = r.table[g][p / grp.page_size] * grp.page_size + p % grp.page_size;
+      }
+    }
+    row += cnt;
+    if (cnt > max_q) max_q = cnt;
+    if (start + cnt > max_kv) max_kv = start + cnt;
+  }
+  q_start[n] = row;
+  info[0] = max_q;
+  info[1] = max_kv;
+  info[2] = row;
+  return 0;
+}
+
+// Advance every entry of a planned step by its token count.
+int cm_commit_step(void* h, int n, const int* slots, const int* counts) {
+  auto* m = static_cast<Manager*>(h);
+  if (!m) return ERR_ARGUMENT;
+  for (int i = 0; i < n; ++i) {
+    const int s = slots[i];
+    if (s < 0 || s >= (int)m->requests.size() || !m->requests[s].live) return ERR_ARGUMENT;
+    int rc = cm_advance(h, s, m->requests[s].computed_len + counts[i]);
+    if (rc < 0) return rc;
+  }
+  return 0;
+}
+
 int cm_free_pages(void* h, int g) {
   auto* m = static_cast<Manager*>(h);
   if (!m || g < 0 || g >= (int)m->groups.size()) return ERR_ARGUMENT;

@@ -96,6 +96,8 @@ class StepContext:
         self.max_q_len = 0
         self.max_kv_len = 0
         self.decode_only = False
+        self.max_context = 0  # the longest a request may ever get
+        self.capturing = False  # the step is being recorded as a CUDA graph: launch shapes must not depend on this step's lengths
 
     def host_field(self, name: str) -> np.ndarray:
         at, count = self.layout.fields[name]

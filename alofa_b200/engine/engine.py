@@ -66,7 +66,7 @@ class Engine:
         blocks_per_request = -(-self.max_tokens // cfg.block_size)
         capacity = cfg.capacity_blocks or cfg.max_batch * blocks_per_request
         step_tokens = max(cfg.token_budget, cfg.max_batch, 1)
-        self.runner = StepRunner(self.model, cfg.block_size, capacity, cfg.max_batch, self.max_tokens, step_tokens)
+        self.runner = StepRunner(self.model, cfg.block_size, capacity, cfg.max_batch, self.max_tokens, step_tokens, cfg.cuda_graphs)
         groups = [(g.block_size, g.window or 0, g.num_pages) for g in self.runner.group_specs]
         self.sched_config = SchedConfig(
             token_budget=cfg.token_budget, max_chunk=min(cfg.max_chunk, step_tokens), max_batch=cfg.max_batch, max_tokens=self.max_tokens,
@@ -202,10 +202,12 @@ class Engine:
     def _sample_step(self, entries, owners):
         from ..sampling.sampler import sample_rows
 
-        ctx, logits = self.runner.forward_logits(entries)
+        ctx, logits, tokens = self.runner.forward_sampled(entries)
         if logits is None:
             return None
-        return sample_rows(ctx, logits, owners).cpu()
+        if not all(req.params.plain() for req in owners):
+            tokens = sample_rows(ctx, logits, owners)
+        return tokens.cpu()
 
     def _finish(self, rid: int) -> None:
         req = self._live.pop(rid, None)

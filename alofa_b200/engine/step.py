@@ -3,12 +3,17 @@ wanted places out.
 
 A step runs only the tokens it is given, as one batch, from the cache that
 earlier steps left: portions of prompts beside single decoded tokens, cut
-anywhere.  It reserves pages for the new tokens, fills the step's metadata,
-copies it to the device once, runs the model, and then tells the cache manager
-that the entries are written (which gives back pages behind windows).  Which
-requests run, and with how many tokens, is decided above it (scheduler, trace
-replay).  The reference's counterpart is ``BatchExecutor.plan`` + ``forward``
-(src/alofa/engine/executor.mojo:555-859)."""
+anywhere.  It reserves pages for the new tokens and fills the step's metadata
+(one native call into the cache manager), copies the metadata to the device
+once, runs the model, and then tells the cache manager that the entries are
+written (which gives back pages behind windows).  Which requests run, and with
+how many tokens, is decided above it (scheduler, trace replay).  The
+reference's counterpart is ``BatchExecutor.plan`` + ``forward``
+(src/alofa/engine/executor.mojo:555-859).
+
+Steps that hold one token per request and want every row (plain decoding) are
+replayed as CUDA graphs, one graph per batch size: the metadata buffer has the
+same layout and address every time, so a replay only needs the new metadata."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -19,6 +24,7 @@ import torch
 
 from ..cache.manager import CacheManager, GroupSpec
 from ..cache.storage import CacheStorage, group_windows
+from ..csrc import ops
 from ..errors import AlofaError
 from ..parts.base import PagedKV
 from ..parts.model import Model
@@ -37,10 +43,18 @@ class StepEntry:
     uniform: float = 0.0
 
 
+@dataclass
+class DecodeGraph:
+    graph: "torch.cuda.CUDAGraph"
+    logits: torch.Tensor
+    tokens: torch.Tensor
+    kernels: int
+
+
 class StepRunner:
     """Owns the caches of one model and runs steps over them."""
 
-    def __init__(self, model: Model, block_size: int, num_pages, max_requests: int, max_tokens: int, max_step_tokens: int):
+    def __init__(self, model: Model, block_size: int, num_pages, max_requests: int, max_tokens: int, max_step_tokens: int, cuda_graphs: bool = True):
         self.model = model
         self.rt = model.rt
         self.block_size = block_size
@@ -58,12 +72,15 @@ class StepRunner:
         mb = self.manager.max_blocks
         self._group_shapes = [GroupView(block_size, g.window or 0, mb) for g in self.group_specs]
         words = Layout.make(max_step_tokens, max_requests, max_step_tokens, self._group_shapes).total
+        on_gpu = self.rt.device.type == "cuda"
         self._dev_meta = torch.zeros(words, dtype=torch.int32, device=self.rt.device)
-        self._host_meta = [torch.zeros(words, dtype=torch.int32).pin_memory() if self.rt.device.type == "cuda" else torch.zeros(words, dtype=torch.int32) for _ in range(2)]
+        self._host_meta = [torch.zeros(words, dtype=torch.int32).pin_memory() if on_gpu else torch.zeros(words, dtype=torch.int32) for _ in range(2)]
         self._host_event = [None, None]
         self._flip = 0
         self._status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
-        self._table_row = np.zeros(mb, dtype=np.int32)
+        self._layouts = {}
+        self.cuda_graphs = cuda_graphs and on_gpu and model.graph_safe()
+        self._graphs = {}
 
     # -- requests -----------------------------------------------------------
     def admit(self, request_id: int) -> int:
@@ -78,78 +95,68 @@ class StepRunner:
         return self.manager.computed_len(slot)
 
     # -- the step -----------------------------------------------------------
+    def _layout(self, n_tokens: int, n_seqs: int, n_out: int):
+        key = (n_tokens, n_seqs, n_out)
+        hit = self._layouts.get(key)
+        if hit is None:
+            lay = Layout.make(n_tokens, n_seqs, n_out, self._group_shapes)
+            names = ["positions", "seq_of_token", "q_start", "kv_len", "state_slots", "logit_rows"]
+            for gi in range(len(self._group_shapes)):
+                names += [f"slot_map{gi}", f"block_table{gi}"]
+            offsets = np.array([lay.fields[n][0] for n in names], dtype=np.int32)
+            hit = (lay, offsets)
+            if len(self._layouts) < 4096:
+                self._layouts[key] = hit
+        return hit
+
     def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
         """Reserve pages and fill the step's metadata (host and device)."""
         n_seqs = len(entries)
-        n_tokens = sum(len(e.tokens) for e in entries)
-        n_out = sum(len(e.want) for e in entries)
-        if n_seqs == 0 or n_tokens == 0:
+        if n_seqs == 0:
             raise AlofaError("invalid_argument", "nothing was planned for this step")
+        slots = np.fromiter((e.slot for e in entries), dtype=np.int32, count=n_seqs)
+        counts = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=n_seqs)
+        want_counts = np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=n_seqs)
+        n_tokens, n_out = int(counts.sum()), int(want_counts.sum())
+        if counts.min() <= 0:
+            raise AlofaError("invalid_argument", "a step entry has no tokens")
         if n_tokens > self.max_step_tokens or n_seqs > self.max_requests:
             raise AlofaError("capacity", "the step is larger than the engine was built for", f"tokens={n_tokens} max={self.max_step_tokens} requests={n_seqs} max={self.max_requests}")
-        if len({e.slot for e in entries}) != n_seqs:
+        if len(set(slots.tolist())) != n_seqs:
             raise AlofaError("invalid_argument", "a request appears twice in one step")
-        vocab = self.model.spec.vocab_size
-        starts = []
-        for e in entries:
-            if len(e.tokens) == 0:
-                raise AlofaError("invalid_argument", "a step entry has no tokens", f"slot={e.slot}")
-            start = self.manager.computed_len(e.slot)
-            if start + len(e.tokens) > self.max_tokens:
-                raise AlofaError("out_of_range", "history would outgrow the context window", f"slot={e.slot} have={start} add={len(e.tokens)} max_tokens={self.max_tokens}")
-            starts.append(start)
-        reserved = []
-        try:
-            for e, start in zip(entries, starts):
-                self.manager.reserve(e.slot, start + len(e.tokens))
-                reserved.append(e)
-        except AlofaError:
-            raise
+        if n_tokens == n_seqs:
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=n_seqs)
+        else:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if tokens.min() < 0 or tokens.max() >= self.model.spec.vocab_size:
+            raise AlofaError("out_of_range", "token id outside the vocabulary", f"vocab={self.model.spec.vocab_size}")
+        for e, n in zip(entries, counts):
+            have = self.manager.computed_len(e.slot)
+            if have + n > self.max_tokens:
+                raise AlofaError("out_of_range", "history would outgrow the context window", f"slot={e.slot} have={have} add={n} max_tokens={self.max_tokens}")
+        if n_out == n_seqs and n_tokens == n_seqs:
+            wants = np.zeros(n_seqs, dtype=np.int32)
+        elif n_out:
+            wants = np.concatenate([np.asarray(e.want, dtype=np.int32) for e in entries if len(e.want)])
+        else:
+            wants = np.zeros(1, dtype=np.int32)
 
-        layout = Layout.make(n_tokens, n_seqs, n_out, self._group_shapes)
+        layout, offsets = self._layout(n_tokens, n_seqs, n_out)
         flip = self._flip
         self._flip ^= 1
         if self._host_event[flip] is not None:
             self._host_event[flip].synchronize()
         host_t = self._host_meta[flip]
         host = host_t.numpy()
-        f = {k: host[at : at + n] for k, (at, n) in layout.fields.items()}
-        row = out = 0
-        max_q = max_kv = 0
-        temp = f["temperature"].view(np.float32)
-        unif = f["uniform"].view(np.float32)
-        bs = self.block_size
-        for si, (e, start) in enumerate(zip(entries, starts)):
-            n = len(e.tokens)
-            toks = np.asarray(e.tokens, dtype=np.int64)
-            if toks.min() < 0 or toks.max() >= vocab:
-                raise AlofaError("out_of_range", "token id outside the vocabulary", f"slot={e.slot} vocab={vocab}")
-            f["token_ids"][row : row + n] = toks
-            pos = np.arange(start, start + n, dtype=np.int32)
-            f["positions"][row : row + n] = pos
-            f["seq_of_token"][row : row + n] = si
-            f["q_start"][si] = row
-            f["kv_len"][si] = start + n
-            f["state_slots"][si] = e.slot
-            for w in e.want:
-                if not 0 <= w < n:
-                    raise AlofaError("out_of_range", "wanted place is outside the entry's tokens", f"slot={e.slot} want={w} tokens={n}")
-                f["logit_rows"][out] = row + w
-                temp[out] = e.temperature
-                unif[out] = e.uniform
-                out += 1
-            for gi, g in enumerate(self._group_shapes):
-                table = f[f"block_table{gi}"].reshape(n_seqs, g.max_blocks)[si]
-                nb = self.manager.block_table_into(e.slot, gi, self._table_row)
-                table[:nb] = self._table_row[:nb]
-                table[nb:] = -1
-                f[f"slot_map{gi}"][row : row + n] = table[pos // bs] * bs + pos % bs
-            row += n
-            max_q = max(max_q, n)
-            max_kv = max(max_kv, start + n)
-        f["q_start"][n_seqs] = row
-        dev = self._dev_meta[: layout.total]
-        dev.copy_(host_t[: layout.total], non_blocking=True)
+        at, n = layout.fields["token_ids"]
+        host[at : at + n] = tokens
+        if n_out:
+            at, n = layout.fields["temperature"]
+            host[at : at + n].view(np.float32)[:] = np.repeat(np.fromiter((e.temperature for e in entries), dtype=np.float32, count=n_seqs), want_counts)
+            at, n = layout.fields["uniform"]
+            host[at : at + n].view(np.float32)[:] = np.repeat(np.fromiter((e.uniform for e in entries), dtype=np.float32, count=n_seqs), want_counts)
+        max_q, max_kv, _ = self.manager.plan_step(slots, counts, want_counts, wants, host_t.data_ptr(), offsets, self.manager.max_blocks)
+        self._dev_meta[: layout.total].copy_(host_t[: layout.total], non_blocking=True)
         if self.rt.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
@@ -157,33 +164,79 @@ class StepRunner:
         ctx = StepContext(self.rt, layout, self._dev_meta, host, self._group_shapes, self._status)
         ctx.max_q_len, ctx.max_kv_len = max_q, max_kv
         ctx.decode_only = max_q == 1
-        ctx.entries = entries
-        ctx.starts = starts
+        ctx.max_context = self.max_tokens
+        ctx.slots, ctx.counts = slots, counts
         return ctx
 
     def commit(self, ctx: StepContext) -> None:
         """The step's entries are written: advance the cache manager."""
-        for e, start in zip(ctx.entries, ctx.starts):
-            self.manager.advance(e.slot, start + len(e.tokens))
+        self.manager.commit_step(ctx.slots, ctx.counts)
+
+    def _run(self, ctx: StepContext, sample: bool):
+        """(logits or None, tokens or None) for a prepared step."""
+        graphable = self.cuda_graphs and ctx.decode_only and ctx.n_out == ctx.n_seqs
+        if graphable:
+            g = self._graphs.get(ctx.n_seqs)
+            if g is None:
+                g = self._capture(ctx)
+            if g is not None:
+                g.graph.replay()
+                ops.count_launches(g.kernels)
+                return g.logits, g.tokens
+        logits = self.model.forward(ctx, self.storage.caches)
+        tokens = None
+        if sample and logits is not None:
+            tokens = torch.empty(ctx.n_out, dtype=torch.int32, device=self.rt.device)
+            ops.sample(tokens, logits, ctx.temperature, ctx.uniform)
+        return logits, tokens
+
+    def _capture(self, ctx: StepContext) -> Optional[DecodeGraph]:
+        """Record the decode step of this batch size as a CUDA graph.  The step
+        is first run once outright (its cache writes are the same ones the
+        replay repeats), which also loads every kernel before recording."""
+        ctx.capturing = True
+        self.model.forward(ctx, self.storage.caches)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.storage.caches)
+            tokens = torch.empty(ctx.n_out, dtype=torch.int32, device=self.rt.device)
+            ops.sample(tokens, logits, ctx.temperature, ctx.uniform)
+        entry = DecodeGraph(graph, logits, tokens, ops.launch_count() - before)
+        self._graphs[ctx.n_seqs] = entry
+        return entry
 
     def forward(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; logits (fp32, on the device) at the wanted places in
-        the order of the entries and of their ``want``, or None if none."""
+        the order of the entries and of their ``want``, or None if none.  The
+        tensor is valid until the next step."""
         ctx = self.prepare(entries)
-        logits = self.model.forward(ctx, self.storage.caches)
+        logits, _ = self._run(ctx, sample=False)
         self.commit(ctx)
         return logits if ctx.n_out else None
 
     def forward_logits(self, entries: Sequence[StepEntry]):
         """Run one step; (context, logits or None) for a sampler to use."""
         ctx = self.prepare(entries)
-        logits = self.model.forward(ctx, self.storage.caches)
+        logits, _ = self._run(ctx, sample=False)
         self.commit(ctx)
         return ctx, (logits if ctx.n_out else None)
+
+    def forward_sampled(self, entries: Sequence[StepEntry]):
+        """Run one step and pick a token at every wanted place by temperature
+        alone: (context, logits, tokens int32 on the device)."""
+        ctx = self.prepare(entries)
+        logits, tokens = self._run(ctx, sample=True)
+        self.commit(ctx)
+        return ctx, logits, tokens
 
     def check_status(self) -> None:
         """Raise if a kernel flagged bad input since the last check (reads the
         device, so it waits for the stream)."""
-        if int(self._status.item()) != 0:
+        code = int(self._status.item())
+        if code != 0:
             self._status.zero_()
+            if code == 2:
+                raise AlofaError("state", "a kernel gave up waiting on its own pipeline")
             raise AlofaError("out_of_range", "a kernel met a token id outside the vocabulary")

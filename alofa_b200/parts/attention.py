@@ -26,6 +26,10 @@ from .linear import RESIDUAL, STORE, Linear
 class GQAttention(Part):
     family = "mixer"
 
+    @property
+    def graph_safe(self):
+        return self.position.graph_safe
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         p = self.param
@@ -104,8 +108,9 @@ class GQAttention(Part):
         for bfloat16 and head sizes it is built for, else the generic one."""
         if q.dtype == torch.bfloat16 and ops.attention_bf16_supported(self.hd):
             splits, po, pml = 0, None, None
-            if ctx.decode_only and self.nh // self.nkv <= 64 and ctx.max_kv_len > self.SPLIT_KEYS:
-                splits = -(-ctx.max_kv_len // self.SPLIT_KEYS)
+            longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
+            if ctx.decode_only and self.nh // self.nkv <= 64 and longest > self.SPLIT_KEYS:
+                splits = -(-longest // self.SPLIT_KEYS)
                 po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
                 pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
             ops.attention_bf16(

@@ -76,6 +76,10 @@ class Part:
     touched in :meth:`load`."""
 
     family = ""
+    # True when forward only launches kernels on the current stream with no
+    # host-side dependence on device data: such a part can be recorded in a
+    # CUDA graph.  Parts must opt in.
+    graph_safe = False
 
     def __init__(self, spec: PartSpec, rt: Runtime):
         self.spec = spec

@@ -31,6 +31,10 @@ class PrenormResidual(Part):
         for part in self.parts():
             part.load(state)
 
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part in self.parts())
+
     def cache_spec(self):
         return self.mixer.cache_spec()
 

@@ -17,6 +17,7 @@ from .linear import STORE, Linear
 
 class TokenEmbedding(Part):
     family = "embedding"
+    graph_safe = True
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -36,6 +37,7 @@ class TokenEmbedding(Part):
 
 class LinearHead(Part):
     family = "head"
+    graph_safe = True
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)

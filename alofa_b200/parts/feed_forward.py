@@ -14,6 +14,7 @@ from .linear import GATED, RESIDUAL, Linear
 
 class GatedMLP(Part):
     family = "feed_forward"
+    graph_safe = True
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)

@@ -37,6 +37,10 @@ class Model:
         for part in self.parts():
             part.load(state)
 
+    def graph_safe(self) -> bool:
+        """True when every part may be recorded in a CUDA graph."""
+        return all(part.graph_safe for part in self.parts())
+
     def cache_plan(self) -> dict:
         """run index -> cache spec, for the entries that own a cache."""
         return {i: self.layers[layer].cache_spec() for i, (layer, cache) in enumerate(self.run) if cache == i}

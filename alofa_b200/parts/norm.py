@@ -9,6 +9,7 @@ from .base import Part, TensorSpec, as_float32_vector, register_part
 
 class RMSNorm(Part):
     family = "norm"
+    graph_safe = True
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)

@@ -18,6 +18,7 @@ from .base import Part, register_part
 
 class RotaryNeox(Part):
     family = "position"
+    graph_safe = True
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -58,6 +59,7 @@ class NoPosition(Part):
     """No position encoding: queries and keys are used as projected."""
 
     family = "position"
+    graph_safe = True
 
     def rotary_table(self):
         return None, 0

@@ -56,12 +56,10 @@ def sample_chain_rows(logits: torch.Tensor, rows: list) -> torch.Tensor:
 
 
 def sample_rows(ctx, logits: torch.Tensor, owners: list) -> torch.Tensor:
-    """One token per wanted row of a step; ``owners`` are the engine's
-    requests in row order (``params``, ``prompt``, ``output``)."""
-    if all(req.params.plain() for req in owners):
-        tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        ops.sample(tokens, logits, ctx.temperature, ctx.uniform)
-        return tokens
+    """One token per wanted row of a step through the whole chain;
+    ``owners`` are the engine's requests in row order (``params``, ``prompt``,
+    ``output``).  Rows shaped by temperature alone are served by the step
+    itself (StepRunner.forward_sampled)."""
     uniform = ctx.host_field("uniform").view(np.float32)
     # history for the penalties = prompt + generated so far (src/alofa/cli.mojo:475-492)
     rows = [(req.params, float(uniform[i]), req.prompt + req.output) for i, req in enumerate(owners)]
