@@ -348,6 +348,9 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
     if (cudaFuncSetAttribute(attention_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
         cudaFuncSetAttribute(attention_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return ALOFA_ERR_LAUNCH;
+    prefer_max_shared(attention_bf16_kernel<false>);
+    prefer_max_shared(attention_bf16_kernel<true>);
+    prefer_max_shared(attention_combine_kernel);
     configured = true;
   }
   if (n_splits > 0) {

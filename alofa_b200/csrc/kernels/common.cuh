@@ -55,4 +55,20 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return m;
 }
 
+// Ask for the largest shared-memory carve-out for a kernel, once.  Kernels that
+// follow one another in a step then all run under the same L1/shared split;
+// a change of the split between two launches costs a drain of the SMs.
+template <typename K>
+static inline void prefer_max_shared(K kernel) {
+  cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+#define ALOFA_PREFER_MAX_SHARED(kernel)  \
+  do {                                   \
+    static bool done_ = false;           \
+    if (!done_) {                        \
+      prefer_max_shared(kernel);         \
+      done_ = true;                      \
+    }                                    \
+  } while (0)
+
 static inline int launch_status() { return cudaGetLastError() == cudaSuccess ? ALOFA_OK : ALOFA_ERR_LAUNCH; }

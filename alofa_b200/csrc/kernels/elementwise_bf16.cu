@@ -1,0 +1,193 @@
+// Memory-bound kernels of the bfloat16 path, vectorised, with the second stage
+// of split-K folded in: where a matrix product left partial sums
+// [splits, T, N] (fp32), the consumer adds them up in split order while it
+// reads, so the sum never makes a round trip through memory of its own.
+//
+//   alofa_norm_fused        h += bias + sum_z partial[z]  (optional), then
+//                           x = h / sqrt(mean(h^2) + eps) * w      (RMSNorm,
+//                           src/alofa/kernels/cpu/scalar.mojo:93-129)
+//   alofa_rope_store_fused  qkv = bias + sum_z partial[z] (or a bf16 tensor),
+//                           NeoX rotation of q and k, k and v written to
+//                           their cache slots (scalar.mojo:283-344,
+//                           paged.mojo:208-246)
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// RMSNorm with optional split-K reduction into the residual stream.
+// One block per output row; hidden % 4 == 0.
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, float* __restrict__ h, const float* __restrict__ w,
+                                                         const float* __restrict__ partial, const float* __restrict__ bias,
+                                                         const int* __restrict__ rows, int n_tokens, int hidden, int splits, float eps) {
+  extern __shared__ float row_buf[];  // hidden floats
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float4* hr = reinterpret_cast<float4*>(h + (size_t)src * hidden);
+  const int n4 = hidden >> 2;
+  const size_t plane4 = ((size_t)n_tokens * hidden) >> 2;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < n4; c += blockDim.x) {
+    float4 v = hr[c];
+    if (partial) {
+      const float4* p = reinterpret_cast<const float4*>(partial) + (size_t)src * n4 + c;
+      for (int z = 0; z < splits; ++z) {
+        const float4 a = p[(size_t)z * plane4];
+        v.x += a.x;
+        v.y += a.y;
+        v.z += a.z;
+        v.w += a.w;
+      }
+      if (bias) {
+        const float4 b = reinterpret_cast<const float4*>(bias)[c];
+        v.x += b.x;
+        v.y += b.y;
+        v.z += b.z;
+        v.w += b.w;
+      }
+      hr[c] = v;
+    }
+    reinterpret_cast<float4*>(row_buf)[c] = v;
+    ss = fmaf(v.x, v.x, ss);
+    ss = fmaf(v.y, v.y, ss);
+    ss = fmaf(v.z, v.z, ss);
+    ss = fmaf(v.w, v.w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  for (int c = threadIdx.x; c < n4; c += blockDim.x) {
+    const float4 v = reinterpret_cast<float4*>(row_buf)[c];
+    const float4 g = reinterpret_cast<const float4*>(w)[c];
+    const float y0 = v.x * scale * g.x, y1 = v.y * scale * g.y, y2 = v.z * scale * g.z, y3 = v.w * scale * g.w;
+    if (sizeof(TO) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+      uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      reinterpret_cast<uint2*>(out + (size_t)r * hidden)[c] = packed;
+    } else {
+      reinterpret_cast<float4*>(out + (size_t)r * hidden)[c] = make_float4(y0, y1, y2, y3);
+    }
+  }
+}
+
+ALOFA_API int alofa_norm_fused(void* out, void* h, const float* w, const float* partial, const float* bias, const int* rows, int n_rows,
+                               int n_tokens, int hidden, int splits, float eps, int out_bf16, cudaStream_t stream) {
+  if (n_rows <= 0) return ALOFA_OK;
+  if (hidden % 4 != 0 || hidden > 12288) return ALOFA_ERR_ARGUMENT;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  ALOFA_PREFER_MAX_SHARED(norm_fused_kernel<bf16>);
+  ALOFA_PREFER_MAX_SHARED(norm_fused_kernel<float>);
+  if (out_bf16)
+    norm_fused_kernel<bf16><<<n_rows, 256, smem, stream>>>((bf16*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps);
+  else
+    norm_fused_kernel<float><<<n_rows, 256, smem, stream>>>((float*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Rotation of q and k and the cache write, 8 + 8 elements per thread.
+// Source: bf16 qkv [T, C] or fp32 partials [splits, T, C] (+ bias [C]),
+// C = (nh + 2 nkv) * hd.  Requires rot == hd and hd % 16 == 0.
+// ---------------------------------------------------------------------------
+struct Vec8 {
+  float v[8];
+};
+
+__device__ __forceinline__ Vec8 load8(const bf16* src) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(src);
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  Vec8 o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(p[i]);
+    o.v[2 * i] = f.x;
+    o.v[2 * i + 1] = f.y;
+  }
+  return o;
+}
+__device__ __forceinline__ Vec8 load8_partial(const float* partial, const float* bias, size_t offset, int col, size_t plane, int splits) {
+  Vec8 o;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o.v[i] = bias ? bias[col + i] : 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float4 a = *reinterpret_cast<const float4*>(partial + (size_t)z * plane + offset);
+    const float4 b = *reinterpret_cast<const float4*>(partial + (size_t)z * plane + offset + 4);
+    o.v[0] += a.x; o.v[1] += a.y; o.v[2] += a.z; o.v[3] += a.w;
+    o.v[4] += b.x; o.v[5] += b.y; o.v[6] += b.z; o.v[7] += b.w;
+  }
+  return o;
+}
+__device__ __forceinline__ void store8(bf16* dst, const Vec8& x) {
+  __nv_bfloat162 p[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(x.v[2 * i], x.v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(p);
+}
+
+__global__ void rope_store_fused_kernel(bf16* __restrict__ q_out, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                                        const bf16* __restrict__ qkv, const float* __restrict__ partial, const float* __restrict__ bias,
+                                        const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                                        const int* __restrict__ slot_map, int n_tokens, int nh, int nkv, int hd, int splits, int write_cache) {
+  const int chunks = hd >> 4;  // pairs of 8-element chunks per head
+  const int heads = nh + 2 * nkv;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)n_tokens * heads * chunks) return;
+  const int c = (int)(idx % chunks);
+  const int head = (int)((idx / chunks) % heads);
+  const int t = (int)(idx / ((size_t)chunks * heads));
+  const int half = hd >> 1;
+  const int C = heads * hd;
+  const int col = head * hd + c * 8;
+  Vec8 a, b;
+  if (partial) {
+    const size_t plane = (size_t)n_tokens * C;
+    a = load8_partial(partial, bias, (size_t)t * C + col, col, plane, splits);
+    b = load8_partial(partial, bias, (size_t)t * C + col + half, col + half, plane, splits);
+  } else {
+    a = load8(qkv + (size_t)t * C + col);
+    b = load8(qkv + (size_t)t * C + col + half);
+  }
+  bf16* dst;
+  bool rotate = true;
+  if (head < nh) {
+    dst = q_out + ((size_t)t * nh + head) * hd;
+  } else {
+    if (!write_cache) return;
+    const int slot = slot_map[t];
+    if (slot < 0) return;
+    if (head < nh + nkv) {
+      dst = k_cache + ((size_t)slot * nkv + (head - nh)) * hd;
+    } else {
+      dst = v_cache + ((size_t)slot * nkv + (head - nh - nkv)) * hd;
+      rotate = false;
+    }
+  }
+  if (rotate) {
+    const float* cs = cos_sin + ((size_t)positions[t] * half + c * 8) * 2;
+    Vec8 ya, yb;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float co = cs[2 * i], si = cs[2 * i + 1];
+      ya.v[i] = a.v[i] * co - b.v[i] * si;
+      yb.v[i] = b.v[i] * co + a.v[i] * si;
+    }
+    a = ya;
+    b = yb;
+  }
+  store8(dst + c * 8, a);
+  store8(dst + c * 8 + half, b);
+}
+
+ALOFA_API int alofa_rope_store_fused(void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* partial, const float* bias,
+                                     const float* cos_sin, const int* positions, const int* slot_map, int n_tokens, int nh, int nkv, int hd,
+                                     int splits, int write_cache, cudaStream_t stream) {
+  if (n_tokens <= 0) return ALOFA_OK;
+  if (hd % 16 != 0 || (!qkv && !partial)) return ALOFA_ERR_ARGUMENT;
+  const size_t total = (size_t)n_tokens * (nh + 2 * nkv) * (hd >> 4);
+  const int threads = 128;
+  ALOFA_PREFER_MAX_SHARED(rope_store_fused_kernel);
+  rope_store_fused_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
+      (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const bf16*)qkv, partial, bias, cos_sin, positions, slot_map, n_tokens, nh, nkv, hd, splits,
+      write_cache);
+  return launch_status();
+}

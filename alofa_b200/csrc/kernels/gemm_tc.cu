@@ -115,6 +115,9 @@ struct GemmArgs {
   int k_slices_per_split;
   int out_bf16;
   int* status;
+#ifdef ALOFA_GEMM_TIMING
+  long long* stamps;  // [8] clock64 of CTA (0,0,0): start, after setup, first data, accumulator done, epilogue done, end
+#endif
 };
 
 template <int BN, int EPI>
@@ -124,7 +127,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   constexpr uint32_t A_BYTES = BM * BK * 2;
   constexpr uint32_t B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = N_ACC * A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = (N_ACC * BN <= 32) ? 32 : (N_ACC * BN <= 64) ? 64 : (N_ACC * BN <= 128) ? 128 : (N_ACC * BN <= 256) ? 256 : 512;
+  constexpr int CHAINS = 1;
+  constexpr int ACC_COLS = N_ACC * CHAINS * BN;
+  constexpr uint32_t TMEM_COLS = (ACC_COLS <= 32) ? 32 : (ACC_COLS <= 64) ? 64 : (ACC_COLS <= 128) ? 128 : (ACC_COLS <= 256) ? 256 : 512;
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -135,6 +140,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
+#ifdef ALOFA_GEMM_TIMING
+  const bool probe = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && args.stamps;
+  if (probe && threadIdx.x == 0) args.stamps[0] = clock64();
+#endif
   const int total_slices = (args.K + BK - 1) / BK;
   const int slice_begin = blockIdx.z * args.k_slices_per_split;
   const int slice_end = min(total_slices, slice_begin + args.k_slices_per_split);
@@ -154,6 +163,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
+#ifdef ALOFA_GEMM_TIMING
+  if (probe && threadIdx.x == 0) args.stamps[1] = clock64();
+#endif
 
   if (warp == 0) {
     if (lane == 0) {
@@ -177,6 +189,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int s = i % stages;
         ok = mbar_wait(&full_bar[s], (i / stages) & 1, &abort_flag);
         if (!ok) break;
+#ifdef ALOFA_GEMM_TIMING
+        if (probe && i == 0) args.stamps[2] = clock64();
+#endif
         tc_fence_after();
         const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
         const uint64_t desc_b = smem_desc_sw128(stage + N_ACC * A_BYTES);
@@ -185,7 +200,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           const uint64_t desc_a = smem_desc_sw128(stage + a * A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(tmem_base + a * BN, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_base + (a * CHAINS + k % CHAINS) * BN, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), IDESC,
+                      (i > 0 || k >= CHAINS) ? 1u : 0u);
         }
         umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
       }
@@ -199,6 +215,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     bool ok = n_slices > 0 ? mbar_wait(&acc_bar, 0, &abort_flag) : true;
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
+#ifdef ALOFA_GEMM_TIMING
+    if (probe && warp == 2 && lane == 0) args.stamps[3] = clock64();
+#endif
     if (ok) {
       const bool split = gridDim.z > 1;
       float bias0 = 0.f, bias1 = 0.f;
@@ -213,16 +232,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
         if (n_slices > 0) {
           tmem_ld16(taddr, r0);
-          if (N_ACC == 2) tmem_ld16(taddr + BN, r1);
+          if (N_ACC == 2) tmem_ld16(taddr + CHAINS * BN, r1);
           tmem_ld_wait();
+#pragma unroll
+          for (int c = 1; c < CHAINS; ++c) {
+            uint32_t x0[16], x1[16];
+            tmem_ld16(taddr + c * BN, x0);
+            if (N_ACC == 2) tmem_ld16(taddr + (CHAINS + c) * BN, x1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __uint_as_float(x0[j]));
+              if (N_ACC == 2) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __uint_as_float(x1[j]));
+            }
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) r0[j] = r1[j] = 0u;
         }
         if (!f_ok) continue;
+        const int t_base = t0 + c0;
+        if (!split && EPI == EPI_RESIDUAL) {
+          // read the 16 residual values first, then write: the loads overlap
+          float* o = (float*)args.out + (size_t)t_base * args.N + f;
+          float prev[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) prev[j] = (t_base + j < args.T) ? o[(size_t)j * args.N] : 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (t_base + j < args.T) o[(size_t)j * args.N] = prev[j] + (__uint_as_float(r0[j]) + bias0);
+          continue;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int t = t0 + c0 + j;
+          const int t = t_base + j;
           if (t >= args.T) break;
           const float a0 = __uint_as_float(r0[j]);
           if (split) {
@@ -235,13 +278,207 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const float y = g / (1.0f + __expf(-g)) * u;
             if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
             else ((float*)args.out)[(size_t)t * args.N + f] = y;
-          } else if (EPI == EPI_RESIDUAL) {
-            float* o = (float*)args.out + (size_t)t * args.N + f;
-            *o = *o + (a0 + bias0);
           } else {
             const float y = a0 + bias0;
             if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
             else ((float*)args.out)[(size_t)t * args.N + f] = y;
+          }
+        }
+      }
+    }
+  }
+#ifdef ALOFA_GEMM_TIMING
+  if (probe && warp == 2 && lane == 0) args.stamps[4] = clock64();
+#endif
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+#ifdef ALOFA_GEMM_TIMING
+  if (probe && warp == 2 && lane == 0) args.stamps[5] = clock64();
+#endif
+  if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
+}
+
+// ---------------------------------------------------------------------------
+// The same product with the tokens as the M operand, for prompt portions:
+// one CTA owns 128 tokens and BNF weight rows (features; for EPI_GATED the
+// first half of the tile's rows are gate rows, the second half the matching up
+// rows, loaded by two TMA boxes into one shared-memory tile).  A tcgen05.mma of
+// M = 128 takes the same time for any N up to 256, so wide feature tiles are
+// what brings the tensor cores near their rate.  The accumulator has one lane
+// per token and one column per feature: each epilogue thread owns a token row
+// and writes runs of 16 consecutive features with 16-byte stores.
+// ---------------------------------------------------------------------------
+template <int BNF, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args, const int stages) {
+  constexpr bool GATED = EPI == EPI_GATED;
+  constexpr int FEATS = GATED ? BNF / 2 : BNF;  // output features per CTA
+  constexpr uint32_t A_BYTES = 128 * BK * 2;    // token tile
+  constexpr uint32_t B_BYTES = BNF * BK * 2;    // weight tile
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = BNF <= 32 ? 32 : BNF <= 64 ? 64 : BNF <= 128 ? 128 : 256;
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BNF >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[12], empty_bar[12], acc_bar;
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f0 = blockIdx.x * FEATS, t0 = blockIdx.y * 128;
+  const int total_slices = (args.K + BK - 1) / BK;
+  const int slice_begin = blockIdx.z * args.k_slices_per_split;
+  const int n_slices = min(total_slices, slice_begin + args.k_slices_per_split) - slice_begin;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) tmem_alloc(&tmem_base_smem, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < n_slices; ++i) {
+        const int s = i % stages;
+        if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1, &abort_flag)) break;
+        uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        const int k = (slice_begin + i) * BK;
+        tma_load_2d(stage, &map_x, &full_bar[s], k, t0);
+        if (GATED) {
+          tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
+          tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], k, args.N + f0);
+        } else {
+          tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int i = 0; i < n_slices; ++i) {
+        const int s = i % stages;
+        if (!mbar_wait(&full_bar[s], (i / stages) & 1, &abort_flag)) break;
+        tc_fence_after();
+        const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+        const uint64_t desc_a = smem_desc_sw128(stage), desc_b = smem_desc_sw128(stage + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)
+          umma_bf16(tmem_base, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(&acc_bar);
+    }
+  } else {
+    const int q = warp & 3;
+    const int t = t0 + q * 32 + lane;
+    bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (ok && t0 + q * 32 < args.T) {
+      const bool split = gridDim.z > 1;
+      const bool t_ok = t < args.T;
+      const int N = args.N;
+      const size_t plane = (size_t)args.T * N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < FEATS; c0 += 16) {
+        const int f = f0 + c0;
+        if (f >= N) break;
+        uint32_t r0[16], r1[16];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        tmem_ld16(taddr, r0);
+        if (GATED) tmem_ld16(taddr + FEATS, r1);
+        tmem_ld_wait();
+        if (!t_ok) continue;
+        float v[16], u[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          v[j] = __uint_as_float(r0[j]);
+          u[j] = GATED ? __uint_as_float(r1[j]) : 0.f;
+        }
+        const bool whole = f + 16 <= N;
+        if (split) {
+          float* p = args.partial + (size_t)blockIdx.z * (GATED ? 2 : 1) * plane + (size_t)t * N + f;
+          if (whole && (N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              *reinterpret_cast<float4*>(p + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (GATED) *reinterpret_cast<float4*>(p + plane + j) = make_float4(u[j], u[j + 1], u[j + 2], u[j + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f + j < N) {
+                p[j] = v[j];
+                if (GATED) p[plane + j] = u[j];
+              }
+          }
+          continue;
+        }
+        if (args.bias) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (f + j < N) {
+              v[j] += args.bias[f + j];
+              if (GATED) u[j] += args.bias[N + f + j];
+            }
+        }
+        if (GATED) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + __expf(-v[j])) * u[j];
+        }
+        if (EPI == EPI_RESIDUAL) {
+          float* o = (float*)args.out + (size_t)t * N + f;
+          if (whole && (N & 3) == 0) {
+            float4 prev[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) prev[j] = reinterpret_cast<float4*>(o)[j];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              reinterpret_cast<float4*>(o)[j] = make_float4(prev[j].x + v[4 * j], prev[j].y + v[4 * j + 1], prev[j].z + v[4 * j + 2], prev[j].w + v[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f + j < N) o[j] += v[j];
+          }
+        } else if (args.out_bf16) {
+          bf16* o = (bf16*)args.out + (size_t)t * N + f;
+          if (whole && (N & 7) == 0) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              packed[j] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            reinterpret_cast<uint4*>(o)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            reinterpret_cast<uint4*>(o)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f + j < N) o[j] = __float2bfloat16_rn(v[j]);
+          }
+        } else {
+          float* o = (float*)args.out + (size_t)t * N + f;
+          if (whole && (N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (f + j < N) o[j] = v[j];
           }
         }
       }
@@ -329,11 +566,45 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
       return ALOFA_ERR_LAUNCH;
+    prefer_max_shared(gemm_tc_kernel<BN, EPI>);
+    prefer_max_shared(splitk_reduce_kernel<EPI>);
     configured = true;
   }
   dim3 grid((args.N + BM - 1) / BM, (args.T + BN - 1) / BN, splits);
   gemm_tc_kernel<BN, EPI><<<grid, NUM_THREADS, smem, stream>>>(mw, mx, args, stages);
   return launch_status();
+}
+
+template <int BNF, int EPI>
+static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& args, int splits, cudaStream_t stream) {
+  constexpr size_t STAGE = (size_t)128 * BK * 2 + (size_t)BNF * BK * 2;
+  constexpr int FEATS = (EPI == EPI_GATED) ? BNF / 2 : BNF;
+  // two CTAs share an SM (shared memory and the 512 tensor-memory columns allow
+  // it): while one runs its epilogue the other keeps the tensor cores busy
+  int stages = (int)((108 * 1024) / STAGE);
+  if (stages > 12) stages = 12;
+  if (stages < 2) stages = 2;
+  const size_t smem = STAGE * stages + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_tokens_kernel<BNF, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
+      return ALOFA_ERR_LAUNCH;
+    prefer_max_shared(gemm_tc_tokens_kernel<BNF, EPI>);
+    configured = true;
+  }
+  dim3 grid((args.N + FEATS - 1) / FEATS, (args.T + 127) / 128, splits);
+  gemm_tc_tokens_kernel<BNF, EPI><<<grid, NUM_THREADS, smem, stream>>>(mw, mx, args, stages);
+  return launch_status();
+}
+
+template <int EPI>
+static int dispatch_tokens(int bnf, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& args, int splits, cudaStream_t stream) {
+  switch (bnf) {
+    case 64: return launch_tokens<64, EPI>(mw, mx, args, splits, stream);
+    case 128: return launch_tokens<128, EPI>(mw, mx, args, splits, stream);
+    case 256: return launch_tokens<256, EPI>(mw, mx, args, splits, stream);
+    default: return ALOFA_ERR_ARGUMENT;
+  }
 }
 
 template <int EPI>
@@ -350,11 +621,12 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 
 // out = x W^T with the epilogue `epi`.  x [T, K] bf16, w [N (GATED: 2N), K] bf16.
 // bn: tokens per CTA (16..256).  splits > 1 needs `partial` of
-// splits * (GATED ? 2 : 1) * T * N floats and runs the reduce kernel after.
+// splits * (GATED ? 2 : 1) * T * N floats and, when do_reduce is set, runs the
+// reduce kernel after (else the caller's next kernel adds the partials up).
 // Returns ALOFA_ERR_ARGUMENT for sizes this kernel does not take (K % 8 != 0,
 // pointers not 16-byte aligned).
 ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float* bias, float* partial, int T, int N, int K, int epi, int out_bf16,
-                            int bn, int splits, int* status, cudaStream_t stream) {
+                            int bn, int splits, int do_reduce, int* status, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return ALOFA_OK;
   if (K <= 0 || (K % 8) != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ALOFA_ERR_ARGUMENT;
   if (epi == EPI_RESIDUAL && out_bf16) return ALOFA_ERR_ARGUMENT;
@@ -363,8 +635,17 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   if (splits > total_slices) splits = total_slices;
   if (splits > 1 && !partial) return ALOFA_ERR_ARGUMENT;
   const int w_rows = (epi == EPI_GATED) ? 2 * N : N;
+  // bn > 0: weights on the M side, bn tokens per CTA.  bn < 0: tokens on the M
+  // side (128 per CTA), -bn weight rows per MMA (for GATED half gate, half up).
+  const bool tokens_on_m = bn < 0;
+  const int bnf = -bn;
   CUtensorMap mw, mx;
-  if (!make_map(&mw, w, w_rows, K, BM) || !make_map(&mx, x, T, K, bn)) return ALOFA_ERR_ARGUMENT;
+  if (tokens_on_m) {
+    const int w_box = (epi == EPI_GATED) ? bnf / 2 : bnf;
+    if (!make_map(&mw, w, w_rows, K, w_box) || !make_map(&mx, x, T, K, 128)) return ALOFA_ERR_ARGUMENT;
+  } else if (!make_map(&mw, w, w_rows, K, BM) || !make_map(&mx, x, T, K, bn)) {
+    return ALOFA_ERR_ARGUMENT;
+  }
   GemmArgs args;
   args.out = out;
   args.partial = partial;
@@ -376,18 +657,43 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;  // no empty split
   args.out_bf16 = out_bf16;
   args.status = status;
+#ifdef ALOFA_GEMM_TIMING
+  args.stamps = (long long*)status;  // the timing build reuses the status pointer for its stamps
+  args.status = nullptr;
+#endif
   int rc;
-  if (epi == EPI_STORE) rc = dispatch_bn<EPI_STORE>(bn, mw, mx, args, splits, stream);
+  if (tokens_on_m) {
+    if (epi == EPI_STORE) rc = dispatch_tokens<EPI_STORE>(bnf, mw, mx, args, splits, stream);
+    else if (epi == EPI_RESIDUAL) rc = dispatch_tokens<EPI_RESIDUAL>(bnf, mw, mx, args, splits, stream);
+    else if (epi == EPI_GATED) rc = dispatch_tokens<EPI_GATED>(bnf, mw, mx, args, splits, stream);
+    else return ALOFA_ERR_ARGUMENT;
+  } else if (epi == EPI_STORE) rc = dispatch_bn<EPI_STORE>(bn, mw, mx, args, splits, stream);
   else if (epi == EPI_RESIDUAL) rc = dispatch_bn<EPI_RESIDUAL>(bn, mw, mx, args, splits, stream);
   else if (epi == EPI_GATED) rc = dispatch_bn<EPI_GATED>(bn, mw, mx, args, splits, stream);
   else return ALOFA_ERR_ARGUMENT;
-  if (rc != ALOFA_OK || splits == 1) return rc;
+  if (rc != ALOFA_OK || splits == 1 || !do_reduce) return rc;
   const size_t plane = (size_t)T * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)((plane + threads - 1) / threads);
   if (epi == EPI_STORE) splitk_reduce_kernel<EPI_STORE><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
   else if (epi == EPI_RESIDUAL) splitk_reduce_kernel<EPI_RESIDUAL><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
   else splitk_reduce_kernel<EPI_GATED><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  return launch_status();
+}
+
+// The second stage alone: out (op)= bias + sum_z partial[z], for partial sums a
+// deferred product left behind.
+ALOFA_API int alofa_splitk_reduce(void* out, const float* partial, const float* bias, int T, int N, int splits, int epi, int out_bf16,
+                                  cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return ALOFA_OK;
+  if (epi == EPI_RESIDUAL && out_bf16) return ALOFA_ERR_ARGUMENT;
+  const size_t plane = (size_t)T * N;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((plane + threads - 1) / threads);
+  if (epi == EPI_STORE) splitk_reduce_kernel<EPI_STORE><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  else if (epi == EPI_RESIDUAL) splitk_reduce_kernel<EPI_RESIDUAL><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  else if (epi == EPI_GATED) splitk_reduce_kernel<EPI_GATED><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  else return ALOFA_ERR_ARGUMENT;
   return launch_status();
 }
 

@@ -30,6 +30,8 @@ __global__ void embed_gather_kernel(float* __restrict__ out, const TW* __restric
 ALOFA_API int alofa_embed_gather(void* out, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
                                  int table_bf16, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
+  ALOFA_PREFER_MAX_SHARED(embed_gather_kernel<bf16>);
+  ALOFA_PREFER_MAX_SHARED(embed_gather_kernel<float>);
   if (table_bf16)
     embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>((float*)out, (const bf16*)table, ids, hidden, vocab, status);
   else

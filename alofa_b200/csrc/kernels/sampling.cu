@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
 ALOFA_API int alofa_sample(int* tokens, const float* logits, const float* temperature, const float* uniform, int n_rows,
                            int vocab, cudaStream_t stream) {
   if (n_rows <= 0) return ALOFA_OK;
+  ALOFA_PREFER_MAX_SHARED(sample_kernel);
   sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
   return launch_status();
 }

@@ -71,7 +71,9 @@ def _gemm_tc():
     if lib is None:
         lib = load_library("alofa_gemm_tc", ["kernels/gemm_tc.cu"])
         lib.alofa_gemm_tc.restype = _I
-        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P]
+        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]
+        lib.alofa_splitk_reduce.restype = _I
+        lib.alofa_splitk_reduce.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _P]
         lib.alofa_gemm_tc_splits.restype = _I
         lib.alofa_gemm_tc_splits.argtypes = [_I, _I]
         _libs["gemm_tc"] = lib
@@ -92,6 +94,18 @@ def _attention(head_dim: int):
 def attention_bf16_supported(head_dim: int) -> bool:
     """Head sizes the bfloat16 attention kernel is built for."""
     return head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+def _elementwise():
+    lib = _libs.get("elementwise")
+    if lib is None:
+        lib = load_library("alofa_elementwise_bf16", ["kernels/elementwise_bf16.cu"])
+        lib.alofa_norm_fused.restype = _I
+        lib.alofa_norm_fused.argtypes = [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P]
+        lib.alofa_rope_store_fused.restype = _I
+        lib.alofa_rope_store_fused.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]
+        _libs["elementwise"] = lib
+    return lib
 
 
 def _stream() -> int:
@@ -239,7 +253,7 @@ def gemm_tc_splits(k: int, splits: int) -> int:
     return _gemm_tc().alofa_gemm_tc_splits(k, splits)
 
 
-def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None) -> bool:
+def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True) -> bool:
     """Tensor-core product ``out = x @ w.T`` (bf16 operands, fp32 sums) with
     the epilogue fused.  Returns False, having launched nothing, when the
     kernel does not take these sizes (depth not a multiple of 8, unaligned)."""
@@ -252,12 +266,13 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
         _dev(out, "out"), _dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
         _dev(bias, "bias", torch.float32) if bias is not None else None,
         _dev(partial, "partial", torch.float32) if partial is not None else None,
-        m, n, k, epi, _is_bf16(out, "out"), bn, splits, _dev(status, "status", torch.int32) if status is not None else None, _stream(),
+        m, n, k, epi, _is_bf16(out, "out"), bn, splits, 1 if reduce else 0,
+        _dev(status, "status", torch.int32) if status is not None else None, _stream(),
     )
     if rc == 1:
         return False
     _done(rc, "gemm_tc", f"M={m} N={n} K={k} epi={epi} bn={bn} splits={splits}")
-    if splits > 1:
+    if splits > 1 and reduce:
         count_launches(1)
     return True
 
@@ -281,3 +296,50 @@ def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, block_table, page_
     _done(rc, "attention_bf16", f"hd={hd} nh={nh} nkv={nkv} splits={n_splits}")
     if n_splits > 0:
         count_launches(1)
+
+
+def norm_fused(out, h, weight, eps: float, rows=None, partial=None, splits: int = 0, bias=None) -> bool:
+    """RMSNorm of rows of the fp32 stream ``h`` (vectorised; hidden % 4 == 0).
+    With ``partial`` [splits, T, hidden] the pending partial sums (and bias)
+    are first added into ``h``.  Returns False when the size is not taken."""
+    n, hidden = out.shape
+    if hidden % 4:
+        return False
+    f32 = torch.float32
+    rc = _elementwise().alofa_norm_fused(
+        _dev(out, "out"), _dev(h, "h", f32), _dev(weight, "weight", f32), _dev(partial, "partial", f32) if partial is not None else None,
+        _dev(bias, "bias", f32) if bias is not None else None, _dev(rows, "rows", torch.int32) if rows is not None else None,
+        n, h.shape[0], hidden, splits, float(eps), _is_bf16(out, "out"), _stream(),
+    )
+    if rc == 1:
+        return False
+    _done(rc, "norm_fused")
+    return True
+
+
+def rope_store_fused(q_out, k_cache, v_cache, qkv, partial, splits, bias, cos_sin, positions, slot_map, nh, nkv, hd, write_cache=True) -> None:
+    """bf16 rotate-and-store with full rotary (rot == hd, hd % 16 == 0); the
+    source is ``qkv`` (bf16) or split-K ``partial`` sums [splits, T, C] + bias."""
+    n = q_out.shape[0]
+    bf, f32 = torch.bfloat16, torch.float32
+    _done(
+        _elementwise().alofa_rope_store_fused(
+            _dev(q_out, "q_out", bf), _dev(k_cache, "k_cache", bf) if write_cache else None, _dev(v_cache, "v_cache", bf) if write_cache else None,
+            _dev(qkv, "qkv", bf) if qkv is not None else None, _dev(partial, "partial", f32) if partial is not None else None,
+            _dev(bias, "bias", f32) if bias is not None else None, _dev(cos_sin, "cos_sin", f32), _dev(positions, "positions", torch.int32),
+            _dev(slot_map, "slot_map", torch.int32) if write_cache else None, n, nh, nkv, hd, splits, 1 if write_cache else 0, _stream(),
+        ),
+        "rope_store_fused", f"hd={hd}",
+    )
+
+
+def splitk_reduce(out, partial, bias, splits: int, epi: int) -> None:
+    """out (op)= bias + sum of ``partial`` [splits, T, N] in split order."""
+    t, n = out.shape
+    _done(
+        _gemm_tc().alofa_splitk_reduce(
+            _dev(out, "out"), _dev(partial, "partial", torch.float32), _dev(bias, "bias", torch.float32) if bias is not None else None,
+            t, n, splits, epi, _is_bf16(out, "out"), _stream(),
+        ),
+        "splitk_reduce",
+    )

@@ -99,6 +99,31 @@ class StepContext:
         self.max_context = 0  # the longest a request may ever get
         self.capturing = False  # the step is being recorded as a CUDA graph: launch shapes must not depend on this step's lengths
 
+        self.pending = None  # (residual stream, Partial): sums a deferred product still owes it
+
+    def set_pending(self, h, partial) -> None:
+        """A product into the residual stream ``h`` left partial sums behind;
+        the next reader of ``h`` adds them (norms do it while they read)."""
+        self.flush_pending()
+        self.pending = (h, partial)
+
+    def take_pending(self, h):
+        """The partial sums owed to ``h``, handing over the duty to add them."""
+        if self.pending is not None and self.pending[0] is h:
+            partial = self.pending[1]
+            self.pending = None
+            return partial
+        return None
+
+    def flush_pending(self) -> None:
+        """Add any owed partial sums into their residual stream now."""
+        if self.pending is not None:
+            from ..csrc import ops
+
+            h, partial = self.pending
+            self.pending = None
+            ops.splitk_reduce(h, partial.sums, partial.bias, partial.splits, ops.EPI_RESIDUAL)
+
     def host_field(self, name: str) -> np.ndarray:
         at, count = self.layout.fields[name]
         return self.host[at : at + count]

@@ -89,17 +89,29 @@ class GQAttention(Part):
         group = ctx.groups[cache.group]
         nkv_in = self.nkv if writes else 0
         qkv = ctx.buf((n, (self.nh + 2 * nkv_in) * self.hd), dt)
-        (self.qkv if writes else self.q_only)(qkv, x)
         table, rot = self.position.rotary_table()
-        if getattr(self.position, "apply", None) is not None:
-            q_view = qkv[:, : self.q_dim].view(n, self.nh, self.hd)
-            k_view = qkv[:, self.q_dim : self.q_dim + nkv_in * self.hd].view(n, nkv_in, self.hd)
-            self.position.apply(ctx, q_view, k_view)
+        custom = getattr(self.position, "apply", None)
+        # the vectorised rotate-and-store: bf16, the whole head rotated, head size a multiple of 16
+        vectorised = dt == torch.bfloat16 and custom is None and rot == self.hd and self.hd % 16 == 0
+        owed = (self.qkv if writes else self.q_only)(qkv, x, defer=vectorised)
         q = ctx.buf((n, self.q_dim), dt)
-        ops.rope_store(q, cache.k, cache.v, qkv, table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, rot, writes)
+        if vectorised:
+            ops.rope_store_fused(
+                q, cache.k, cache.v, None if owed is not None else qkv, owed.sums if owed is not None else None,
+                owed.splits if owed is not None else 0, owed.bias if owed is not None else None,
+                table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, writes,
+            )
+        else:
+            if custom is not None:
+                q_view = qkv[:, : self.q_dim].view(n, self.nh, self.hd)
+                k_view = qkv[:, self.q_dim : self.q_dim + nkv_in * self.hd].view(n, nkv_in, self.hd)
+                custom(ctx, q_view, k_view)
+            ops.rope_store(q, cache.k, cache.v, qkv, table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, rot, writes)
         attn = ctx.buf((n, self.q_dim), dt)
         self.attend(ctx, attn, q, cache, group)
-        self.out(h, attn)
+        owed = self.out(h, attn, defer=True)
+        if owed is not None:
+            ctx.set_pending(h, owed)
 
     SPLIT_KEYS = 256  # keys per CTA when a decode-only step splits each request's keys
 

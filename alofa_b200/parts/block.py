@@ -38,10 +38,17 @@ class PrenormResidual(Part):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
+    absorbs_pending = True  # its norms add partial sums owed to h; other readers get them flushed first
+
+    def _norm(self, norm, ctx, h):
+        if not getattr(norm, "absorbs_pending", False):
+            ctx.flush_pending()
+        return norm.forward(ctx, h)
+
     def forward(self, ctx, h, cache, writes=True):
-        x = self.mixer_norm.forward(ctx, h)
+        x = self._norm(self.mixer_norm, ctx, h)
         self.mixer.forward(ctx, x, h, cache, writes)
-        x = self.feed_forward_norm.forward(ctx, h)
+        x = self._norm(self.feed_forward_norm, ctx, h)
         self.feed_forward.forward(ctx, x, h)
 
 

@@ -1,10 +1,10 @@
 """Choice of the tensor-core matrix product for bfloat16 operands.
 
-``plan(linear)`` returns a callable ``(out, x) -> bool`` that runs the
-tcgen05 kernel and returns True, or returns False, having launched nothing,
-when the call's sizes are ones that kernel refuses (the caller then uses the
-generic kernel), or None when the weight can never go that way (depth not a
-multiple of 8: a TMA row must start on a 16-byte boundary).
+``plan(linear)`` returns a callable ``(out, x, defer) -> True | Partial | False``
+that runs the tcgen05 kernel, or returns False, having launched nothing, when
+the call's sizes are ones that kernel refuses (the caller then uses the generic
+kernel), or None when the weight can never go that way (depth not a multiple
+of 8: a TMA row must start on a 16-byte boundary).
 
 Tokens per CTA and the number of k-splits are chosen from the token count and
 the weight's shape so that even a handful of decode tokens pulls the weight
@@ -20,16 +20,29 @@ SMS = 148
 K_SLICE = 64
 
 
-def _tokens_per_cta(tokens: int, feature_tiles: int) -> int:
-    for bn in (16, 32, 64, 128):
+def _tile(tokens: int, features: int, gated: bool) -> int:
+    """The kernel's tile argument.  Positive: weights on the M side of the MMA
+    with that many tokens per CTA (decode: few tokens, weights streamed).
+    Negative: tokens on the M side (128 per CTA) with that many weight rows
+    per MMA (prompt portions: an MMA of M = 128 costs the same for any N up to
+    256, so wide feature tiles are what pays)."""
+    for bn in (16, 32, 64):
         if tokens <= bn:
             return bn
-    # prompts: smaller token tiles while the grid would not fill the GPU twice over
-    return 128 if feature_tiles * -(-tokens // 256) < 2 * SMS else 256
+    if gated:
+        return -256  # 128 gate rows and their 128 up rows
+    # narrow outputs: 128-wide tiles keep more SMs busy
+    return -128 if -(-features // 256) * -(-tokens // 128) < SMS else -256
 
 
-def _splits(tokens: int, feature_tiles: int, bn: int, depth: int) -> int:
-    ctas = feature_tiles * -(-tokens // bn)
+def _ctas(tokens: int, features: int, tile: int, gated: bool) -> int:
+    if tile > 0:
+        return -(-features // 128) * -(-tokens // tile)
+    per_cta = -tile // 2 if gated else -tile
+    return -(-features // per_cta) * -(-tokens // 128)
+
+
+def _splits(ctas: int, depth: int) -> int:
     slices = -(-depth // K_SLICE)
     if ctas >= SMS // 2 or slices < 2:
         return 1
@@ -37,24 +50,30 @@ def _splits(tokens: int, feature_tiles: int, bn: int, depth: int) -> int:
 
 
 def plan(linear):
+    from .linear import Partial
+
     w = linear.weight
     depth = linear.in_features
     if depth % 8 or w.data_ptr() % 16:
         return None
-    feature_tiles = -(-linear.out_features // 128)
-    n_acc = 2 if linear.epi == ops.EPI_GATED else 1
+    gated = linear.epi == ops.EPI_GATED
+    n_acc = 2 if gated else 1
 
-    def run(out: torch.Tensor, x: torch.Tensor) -> bool:
+    def run(out, x: torch.Tensor, defer: bool = False):
         tokens = x.shape[0]
         if tokens == 0:
             return True
         if x.data_ptr() % 16 or not x.is_contiguous():
             return False
-        bn = _tokens_per_cta(tokens, feature_tiles)
-        splits = ops.gemm_tc_splits(depth, _splits(tokens, feature_tiles, bn, depth))
+        bn = _tile(tokens, linear.out_features, gated)
+        splits = ops.gemm_tc_splits(depth, _splits(_ctas(tokens, linear.out_features, bn, gated), depth))
         partial = None
         if splits > 1:
-            partial = torch.empty(splits * n_acc * tokens * linear.out_features, dtype=torch.float32, device=x.device)
-        return ops.gemm_tc(out, x, w, linear.bias, linear.epi, bn, splits, partial)
+            partial = torch.empty((splits * n_acc, tokens, linear.out_features), dtype=torch.float32, device=x.device)
+        deferred = defer and splits > 1 and n_acc == 1
+        dst = partial[0] if deferred else out  # a deferred product writes partial sums only
+        if not ops.gemm_tc(dst, x, w, linear.bias, linear.epi, bn, splits, partial, reduce=not deferred):
+            return False
+        return Partial(partial, splits, linear.bias) if deferred else True
 
     return run

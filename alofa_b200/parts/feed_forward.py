@@ -41,7 +41,9 @@ class GatedMLP(Part):
     def forward(self, ctx, x, h):
         act = ctx.buf((x.shape[0], self.inter), self.rt.dtype)
         self.gate_up(act, x)
-        self.down(h, act)
+        owed = self.down(h, act, defer=True)
+        if owed is not None:
+            ctx.set_pending(h, owed)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -4,8 +4,17 @@ One :class:`Linear` holds a weight ``[out, in]`` (row-major, as stored in the
 checkpoint; src/alofa/kernels/cpu/scalar.mojo:10-18) and picks the kernel per
 call: the tensor-core kernel when the operands are bfloat16 and the sizes are
 ones it takes, else the generic FMA kernel, which takes every size and is the
-only one the 32-bit path uses."""
+only one the 32-bit path uses.
+
+When the tensor-core kernel splits the depth over several CTAs it leaves
+partial sums; a caller whose next kernel can add them up while reading (the
+norm that follows a residual product, the rotate-and-store that follows q/k/v)
+asks for them with ``defer=True`` and gets a :class:`Partial` back instead of a
+finished output."""
 from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -13,6 +22,16 @@ from ..csrc import ops
 from ..errors import AlofaError
 
 STORE, RESIDUAL, GATED = ops.EPI_STORE, ops.EPI_RESIDUAL, ops.EPI_GATED
+
+
+@dataclass
+class Partial:
+    """Split-K partial sums ``[splits, tokens, features]`` (fp32) that still
+    have to be added up, with the bias that goes on top."""
+
+    sums: torch.Tensor
+    splits: int
+    bias: Optional[torch.Tensor]
 
 
 class Linear:
@@ -33,7 +52,12 @@ class Linear:
 
             self._fast = fast_linear.plan(self)
 
-    def __call__(self, out: torch.Tensor, x: torch.Tensor) -> None:
-        if self._fast is not None and x.dtype == torch.bfloat16 and self._fast(out, x):
-            return
+    def __call__(self, out: Optional[torch.Tensor], x: torch.Tensor, defer: bool = False) -> Optional[Partial]:
+        """Run the product.  With ``defer`` the result may come back as a
+        :class:`Partial` (``out`` is then untouched); else None."""
+        if self._fast is not None and x.dtype == torch.bfloat16:
+            done = self._fast(out, x, defer)
+            if done is not False:
+                return done if isinstance(done, Partial) else None
         ops.gemm_generic(out, x, self.weight, self.bias, self.epi)
+        return None

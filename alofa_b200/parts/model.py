@@ -51,10 +51,17 @@ class Model:
         h = ctx.buf((ctx.n_tokens, self.spec.hidden_size), torch.float32)
         self.embedding.forward(ctx, h)
         for i, (layer, cache) in enumerate(self.run):
-            self.layers[layer].forward(ctx, h, caches.get(cache), writes=(cache == i))
+            block = self.layers[layer]
+            if not getattr(block, "absorbs_pending", False):
+                ctx.flush_pending()
+            block.forward(ctx, h, caches.get(cache), writes=(cache == i))
         if ctx.n_out == 0:  # a prompt portion whose logits nobody wants
+            ctx.pending = None
             return None
+        if not getattr(self.final_norm, "absorbs_pending", False):
+            ctx.flush_pending()
         x = self.final_norm.forward(ctx, h, ctx.logit_rows)
+        ctx.pending = None
         return self.head.forward(ctx, x)
 
 

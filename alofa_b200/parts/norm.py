@@ -3,6 +3,8 @@ no mean subtraction, the weight is used as stored
 (src/alofa/kernels/cpu/scalar.mojo:93-129)."""
 from __future__ import annotations
 
+import torch
+
 from ..csrc import ops
 from .base import Part, TensorSpec, as_float32_vector, register_part
 
@@ -23,11 +25,20 @@ class RMSNorm(Part):
     def load(self, state):
         self.weight = as_float32_vector(state[self.prefix + "weight"])
 
+    absorbs_pending = True  # adds split-K partial sums owed to h while reading it
+
     def forward(self, ctx, h, rows=None):
         """Normalised rows of the fp32 stream ``h`` in the compute dtype;
         ``rows`` (int32 on the device) picks rows of ``h``."""
         n = h.shape[0] if rows is None else rows.shape[0]
         out = ctx.buf((n, self.size), self.rt.dtype)
+        owed = ctx.take_pending(h)
+        if owed is not None:
+            if ops.norm_fused(out, h, self.weight, self.eps, rows, owed.sums, owed.splits, owed.bias):
+                return out
+            ops.splitk_reduce(h, owed.sums, owed.bias, owed.splits, ops.EPI_RESIDUAL)
+        if self.rt.dtype == torch.bfloat16 and ops.norm_fused(out, h, self.weight, self.eps, rows):
+            return out
         ops.rmsnorm(out, h, self.weight, self.eps, rows)
         return out
 

@@ -164,9 +164,15 @@ def run(args) -> dict:
         runner.release(slot)
 
     prefill_tokens = prompt(PROMPT_LEN)
-    for _ in range(max(1, min(args.warmup, 3))):
-        one_prefill()
-    prefill_ms = timed(one_prefill, 5)
+    if args.phase == "decode":
+        prefill_ms = float("nan")
+    else:
+        for _ in range(max(1, min(args.warmup, 3))):
+            one_prefill()
+        prefill_ms = timed(one_prefill, 5)
+    if args.phase == "prefill":
+        print(json.dumps({"phase": "prefill", "ms": prefill_ms, "tok_s": PROMPT_LEN / prefill_ms * 1e3}))
+        raise SystemExit(0)
     pf = prefill_flops(cfg, layers, PROMPT_LEN, numbers)
     prefill = {"value": round(PROMPT_LEN / prefill_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 4),
                "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
@@ -199,6 +205,9 @@ def run(args) -> dict:
         return {"ms": ms, "tok_s": batch / ms * 1e3, "bytes": step_bytes, "launches": launches, "clocks": clock_report}
 
     main = decode_point(args.batch, args.steps, args.warmup, ClockSampler())
+    if args.phase == "decode":
+        print(json.dumps({"phase": "decode", "batch": args.batch, "ms_per_step": main["ms"], "tok_s": main["tok_s"], "launches": main["launches"]}))
+        raise SystemExit(0)
     b1 = decode_point(1, max(8, args.steps // 2), args.warmup)
     b64 = decode_point(64, max(8, args.steps // 2), args.warmup)
     achieved = main["bytes"] / (main["ms"] * 1e-3) / 1e9
@@ -253,6 +262,7 @@ def main() -> int:
     ap.add_argument("--impl", default="alofa_b200")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the full shape (named in config)")
+    ap.add_argument("--phase", choices=["all", "decode", "prefill"], default="all", help="profiling aid: run only one part; the JSON line then lacks the others")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps(reference_arm()))

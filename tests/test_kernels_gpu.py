@@ -108,6 +108,96 @@ def test_rope_store(ops, dtype, hd, rot):
     assert_close(v_cache.float().cpu().reshape(32, -1), want_v, 0.0, "v cache")
 
 
+@pytest.mark.parametrize("out_dtype", [F32, BF16])
+def test_norm_fused_adds_owed_partial_sums(ops, out_dtype):
+    rng = np.random.default_rng(11)
+    hidden, tokens, splits = 896, 9, 5
+    h = rng.normal(size=(tokens, hidden)).astype(np.float32)
+    partial = rng.normal(size=(splits, tokens, hidden)).astype(np.float32)
+    bias = rng.normal(size=hidden).astype(np.float32)
+    w = (1 + 0.1 * rng.normal(size=hidden)).astype(np.float32)
+    hd = dev(h)
+    out = torch.empty(tokens, hidden, dtype=out_dtype, device="cuda")
+    assert ops.norm_fused(out, hd, dev(w), 1e-6, None, dev(partial), splits, dev(bias))
+    total = h.astype(np.float64) + partial.astype(np.float64).sum(axis=0) + bias
+    assert_close(hd.cpu(), total, 1e-6, "stream after the sums")
+    assert_close(out.float().cpu(), plain.rmsnorm(total, w, 1e-6), TOL[out_dtype], "norm of the summed stream")
+    rows = np.array([7, 2], dtype=np.int32)
+    out = torch.empty(2, hidden, dtype=out_dtype, device="cuda")
+    assert ops.norm_fused(out, dev(h), dev(w), 1e-6, dev(rows), dev(partial), splits, None)
+    assert_close(out.float().cpu(), plain.rmsnorm((h.astype(np.float64) + partial.astype(np.float64).sum(axis=0))[rows], w, 1e-6), TOL[out_dtype], "gathered rows")
+    assert not ops.norm_fused(torch.empty(2, 6, dtype=out_dtype, device="cuda"), dev(h[:, :6].copy()), dev(w[:6].copy()), 1e-6)  # width not a multiple of 4
+
+
+@pytest.mark.parametrize("hd", [16, 48, 64, 128])
+def test_rope_store_fused_from_tensor_and_from_partial_sums(ops, hd):
+    from alofa_b200.config.spec import PartSpec
+    from alofa_b200.parts.base import Runtime
+    from alofa_b200.parts.position import RotaryNeox
+
+    rng = np.random.default_rng(hd)
+    n, nh, nkv, splits = 13, 3, 2, 4
+    C = (nh + 2 * nkv) * hd
+    table = RotaryNeox(PartSpec("rotary_neox", {"head_dim": hd, "theta": 1e6, "max_position": 700}), Runtime(torch.device("cuda"), BF16)).build_table(700)
+    positions = rng.integers(0, 700, n).astype(np.int32)
+    slots = rng.permutation(40)[:n].astype(np.int32)
+    slots[3] = -1
+    partial = rng.normal(size=(splits, n, C)).astype(np.float32)
+    bias = rng.normal(size=C).astype(np.float32)
+    summed = partial.astype(np.float64).sum(axis=0) + bias
+    for source in ("partial", "tensor"):
+        k_cache = torch.full((40, nkv, hd), 3.0, dtype=BF16, device="cuda")
+        v_cache = torch.full((40, nkv, hd), 3.0, dtype=BF16, device="cuda")
+        q_out = torch.empty(n, nh * hd, dtype=BF16, device="cuda")
+        if source == "partial":
+            qkv = summed
+            ops.rope_store_fused(q_out, k_cache, v_cache, None, dev(partial), splits, dev(bias), table, dev(positions), dev(slots), nh, nkv, hd)
+        else:
+            qkv = rounded(summed, BF16)
+            ops.rope_store_fused(q_out, k_cache, v_cache, dev(qkv, BF16), None, 0, None, table, dev(positions), dev(slots), nh, nkv, hd)
+        q, k, v = qkv[:, : nh * hd], qkv[:, nh * hd : (nh + nkv) * hd], qkv[:, (nh + nkv) * hd :]
+        assert_close(q_out.float().cpu(), plain.rope(q, positions, nh, hd, 1e6), TOL[BF16], f"q {source}")
+        want_k, want_v = np.full((40, nkv * hd), 3.0), np.full((40, nkv * hd), 3.0)
+        rk = plain.rope(k, positions, nkv, hd, 1e6)
+        for t, s_ in enumerate(slots):
+            if s_ >= 0:
+                want_k[s_], want_v[s_] = rk[t], v[t]
+        assert_close(k_cache.float().cpu().reshape(40, -1), want_k, TOL[BF16], f"k {source}")
+        assert_close(v_cache.float().cpu().reshape(40, -1), want_v, TOL[BF16], f"v {source}")
+
+
+@pytest.mark.parametrize("shape", [(5, 128, 64, 16, 1), (33, 379, 96, 64, 1), (300, 1152, 896, 128, 3), (8, 896, 4864, 16, 19), (513, 640, 320, 256, 2),
+                                   (5, 128, 64, -64, 1), (130, 379, 96, -128, 1), (300, 1152, 896, -256, 3), (513, 650, 320, -256, 2), (257, 200, 240, -128, 1)])
+def test_gemm_tc_epilogues_and_split_depth(ops, shape):
+    """The tcgen05 product against fp64: every epilogue, ragged sizes, split
+    depth; weights on the M side (tile > 0) and tokens on the M side (tile < 0)."""
+    m, n, k, bn, splits = shape
+    rng = np.random.default_rng(m + n)
+    x = rounded(rng.normal(size=(m, k)), BF16)
+    w = rounded(rng.normal(size=(2 * n, k)) / np.sqrt(k), BF16)
+    bias = rng.normal(size=2 * n).astype(np.float32)
+    real = ops.gemm_tc_splits(k, splits)
+
+    def ws(n_acc):
+        return torch.empty(real * n_acc, m, n, device="cuda") if real > 1 else None
+
+    for od in (BF16, F32):
+        out = torch.empty(m, n, dtype=od, device="cuda")
+        assert ops.gemm_tc(out, dev(x, BF16), dev(w[:n], BF16), dev(bias[:n]), ops.EPI_STORE, bn, splits, ws(1))
+        assert_close(out.float().cpu(), plain.linear(x, w[:n], bias[:n]), TOL[od], "store")
+        assert ops.gemm_tc(out, dev(x, BF16), dev(w, BF16), None, ops.EPI_GATED, bn, splits, ws(2))
+        assert_close(out.float().cpu(), plain.silu(plain.linear(x, w[:n])) * plain.linear(x, w[n:]), TOL[od], "gated")
+    res = rng.normal(size=(m, n)).astype(np.float32)
+    acc = dev(res)
+    assert ops.gemm_tc(acc, dev(x, BF16), dev(w[:n], BF16), None, ops.EPI_RESIDUAL, bn, splits, ws(1))
+    assert_close(acc.cpu(), res + plain.linear(x, w[:n]), 2e-5, "residual")
+    if real > 1:  # deferred: the partial sums alone, added up by the caller
+        part = ws(1)
+        assert ops.gemm_tc(part[0], dev(x, BF16), dev(w[:n], BF16), None, ops.EPI_RESIDUAL, bn, splits, part, reduce=False)
+        assert_close(part.sum(dim=0).cpu(), plain.linear(x, w[:n]), 2e-5, "partial sums")
+    assert not ops.gemm_tc(torch.empty(4, 8, dtype=BF16, device="cuda"), torch.zeros(4, 12, dtype=BF16, device="cuda"), torch.zeros(8, 12, dtype=BF16, device="cuda"), None, ops.EPI_STORE, 16)
+
+
 def attention_case(ops, dtype, hd, nh, nkv, lens, q_lens, page, window, rng, craft=None, given=None, fast=False, split_keys=0):
     """Sequences of ``lens`` keys; the last ``q_lens[i]`` positions of each are
     queries in this launch.  Returns (got, want) as float64 arrays."""

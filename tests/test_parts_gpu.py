@@ -130,6 +130,7 @@ def test_each_part_alone(dtype):
     # mixer alone: h2 = h + attention(x)
     h2 = h.clone()
     block.mixer.forward(ctx, x, h2, runner.storage.caches[0], True)
+    ctx.flush_pending()  # a part may leave split-K partial sums owed to the stream
     xin = rounded(x.float().cpu().numpy(), dtype)
     a = "layers.0.attn."
     pos = np.arange(21)
@@ -141,6 +142,7 @@ def test_each_part_alone(dtype):
     # feed-forward alone
     h3 = torch.zeros_like(h)
     block.feed_forward.forward(ctx, x, h3)
+    ctx.flush_pending()
     f = "layers.0.ffn."
     assert_close(h3.cpu(), plain.swiglu_mlp(xin, w[f + "gate_proj.weight"], w[f + "up_proj.weight"], w[f + "down_proj.weight"]), TOL[dtype], "feed-forward")
     # head on the wanted row
