@@ -46,7 +46,7 @@ struct AttnParams {
   const int* block_table;  // [R, max_blocks]
   float* partial_o;      // split mode: [splits, T * nh, HD]
   float* partial_ml;     // split mode: [splits, T * nh, 2]
-  int max_blocks, page_size, nh, nkv, window, split_keys, n_rows_total;
+  int max_blocks, page_size, nh, nkv, window, split_keys, n_rows_total, table_entries;
   float scale_log2;      // scale * log2(e)
 };
 
@@ -73,30 +73,82 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copy keys [j0, j0 + 64) of one KV head into a shared tile [64][ROW]; rows past
-// j_end (exclusive) or before j_begin are zero-filled.
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* cache, const int* table, int page_size, int nkv, int kvh, int j0,
-                                             int j_begin, int j_end) {
-  for (int idx = threadIdx.x; idx < BLOCK_N * CHUNKS; idx += 128) {
-    const int r = idx / CHUNKS, c = idx % CHUNKS;
-    const int j = j0 + r;
-    const bool ok = j >= j_begin && j < j_end;
-    const bf16* src = cache;
-    if (ok) {
-      const int page = table[j / page_size];
-      const size_t slot = (size_t)page * page_size + (j % page_size);
-      src = cache + (slot * nkv + kvh) * HD + c * 8;
+// Copy keys [j0, j0 + 64) of one KV head, keys and values, into shared tiles
+// [64][ROW]; rows past j_end (exclusive) or before j_begin are zero-filled.
+// `table` is the shared copy of the request's block-table entries from entry
+// `first_entry` on (a lookup in global memory here would stall every copy
+// behind it).  When a page holds whole key blocks (page_size % 64 == 0) the
+// block lies in one page and a row's address is the block's base plus a fixed
+// stride; else every row looks its page up.
+__device__ __forceinline__ void load_kv_tiles(bf16* k_tile, bf16* v_tile, const bf16* k_cache, const bf16* v_cache, const int* table,
+                                              int first_entry, int page_size, bool block_in_page, int nkv, int kvh, int j0, int j_begin,
+                                              int j_end) {
+  if constexpr (128 % CHUNKS != 0) {
+    // head sizes whose rows do not divide a round of 128 threads: one chunk at a time
+    for (int idx = threadIdx.x; idx < BLOCK_N * CHUNKS; idx += 128) {
+      const int r = idx / CHUNKS, c = idx % CHUNKS;
+      const int j = j0 + r;
+      const bool ok = j >= j_begin && j < j_end;
+      size_t offset = 0;
+      if (ok) {
+        const int e = j / page_size;
+        const int slot = table[e - first_entry] * page_size + (j - e * page_size);
+        offset = ((size_t)slot * nkv + kvh) * HD + c * 8;
+      }
+      cp_async16((uint32_t)__cvta_generic_to_shared(k_tile + r * ROW + c * 8), k_cache + offset, ok);
+      cp_async16((uint32_t)__cvta_generic_to_shared(v_tile + r * ROW + c * 8), v_cache + offset, ok);
     }
-    cp_async16((uint32_t)__cvta_generic_to_shared(tile + r * ROW + c * 8), src, ok);
+    return;
+  }
+  const int r0 = threadIdx.x / CHUNKS, c = threadIdx.x % CHUNKS;
+  const uint32_t k_dst = (uint32_t)__cvta_generic_to_shared(k_tile + r0 * ROW + c * 8);
+  const uint32_t v_dst = (uint32_t)__cvta_generic_to_shared(v_tile + r0 * ROW + c * 8);
+  constexpr int ROWS_PER_ROUND = (128 % CHUNKS == 0) ? 128 / CHUNKS : 1;
+  if (block_in_page) {
+    const int e = j0 / page_size;
+    const size_t first_slot = (size_t)table[e - first_entry] * page_size + (j0 - e * page_size);
+    const size_t base = ((first_slot + r0) * nkv + kvh) * HD + c * 8;
+    const size_t step = (size_t)ROWS_PER_ROUND * nkv * HD;
+#pragma unroll
+    for (int it = 0; it < BLOCK_N / ROWS_PER_ROUND; ++it) {
+      const int j = j0 + r0 + it * ROWS_PER_ROUND;
+      const bool ok = j >= j_begin && j < j_end;
+      const size_t offset = ok ? base + it * step : 0;
+      cp_async16(k_dst + it * ROWS_PER_ROUND * ROW * 2, k_cache + offset, ok);
+      cp_async16(v_dst + it * ROWS_PER_ROUND * ROW * 2, v_cache + offset, ok);
+    }
+    return;
+  }
+#pragma unroll
+  for (int it = 0; it < BLOCK_N / ROWS_PER_ROUND; ++it) {
+    const int j = j0 + r0 + it * ROWS_PER_ROUND;
+    const bool ok = j >= j_begin && j < j_end;
+    size_t offset = 0;
+    if (ok) {
+      const int e = j / page_size;
+      const int slot = table[e - first_entry] * page_size + (j - e * page_size);
+      offset = ((size_t)slot * nkv + kvh) * HD + c * 8;
+    }
+    cp_async16(k_dst + it * ROWS_PER_ROUND * ROW * 2, k_cache + offset, ok);
+    cp_async16(v_dst + it * ROWS_PER_ROUND * ROW * 2, v_cache + offset, ok);
   }
 }
 
-template <bool SPLIT>
+// 2^x by the hardware approximation (2 ulp); 2^-inf = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// STAGES key blocks are in flight at a time; a decode split of up to
+// STAGES * 64 keys is fetched in one go, so its latency is paid once.
+template <bool SPLIT, int STAGES>
 __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);          // [64][ROW]
-  bf16* k_tiles = q_tile + BLOCK_M * ROW;                    // [2][64][ROW]
-  bf16* v_tiles = k_tiles + 2 * BLOCK_N * ROW;               // [2][64][ROW]
+  bf16* k_tiles = q_tile + BLOCK_M * ROW;                    // [STAGES][64][ROW]
+  bf16* v_tiles = k_tiles + STAGES * BLOCK_N * ROW;          // [STAGES][64][ROW]
 
   const int seq = blockIdx.z, kvh = blockIdx.y;
   const int g = p.nh / p.nkv;
@@ -118,8 +170,17 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
     k_hi = min(k_hi, ((int)blockIdx.x + 1) * p.split_keys - 1);
     if (k_lo > k_hi) return;
   }
-  const int* table = p.block_table + (size_t)seq * p.max_blocks;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the block-table entries this CTA will use, copied to shared memory once
+  int* table = reinterpret_cast<int*>(v_tiles + STAGES * BLOCK_N * ROW);
+  const int first_entry = k_lo / p.page_size;
+  const bool block_in_page = p.page_size % BLOCK_N == 0;
+  {
+    const int* src = p.block_table + (size_t)seq * p.max_blocks + first_entry;
+    const int n_entries = k_hi / p.page_size - first_entry + 1;
+    for (int e = threadIdx.x; e < n_entries; e += 128) table[e] = src[e];
+    __syncthreads();
+  }
 
   // ---- stage the query tile: row r = (token r / g, head kvh * g + r % g) ----
   for (int idx = threadIdx.x; idx < BLOCK_M * CHUNKS; idx += 128) {
@@ -131,9 +192,14 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
     cp_async16((uint32_t)__cvta_generic_to_shared(q_tile + r * ROW + c * 8), src, ok);
   }
   const int nb_lo = k_lo / BLOCK_N, nb_hi = k_hi / BLOCK_N;
-  load_kv_tile(k_tiles, p.k_cache, table, p.page_size, p.nkv, kvh, nb_lo * BLOCK_N, k_lo, k_hi + 1);
-  load_kv_tile(v_tiles, p.v_cache, table, p.page_size, p.nkv, kvh, nb_lo * BLOCK_N, k_lo, k_hi + 1);
-  cp_async_commit();
+#pragma unroll
+  for (int st = 0; st < STAGES; ++st) {  // one commit group per stage, empty past the last block
+    if (nb_lo + st <= nb_hi) {
+      load_kv_tiles(k_tiles + st * BLOCK_N * ROW, v_tiles + st * BLOCK_N * ROW, p.k_cache, p.v_cache, table, first_entry, p.page_size,
+                    block_in_page, p.nkv, kvh, (nb_lo + st) * BLOCK_N, k_lo, k_hi + 1);
+    }
+    cp_async_commit();
+  }
 
   // this thread's two rows of the warp's 16-row slab
   const int r_lo = row0 + warp * 16 + (lane >> 2), r_hi = r_lo + 8;
@@ -148,16 +214,17 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
   for (int nb = nb_lo; nb <= nb_hi; ++nb) {
-    const int buf = (nb - nb_lo) & 1;
-    if (nb < nb_hi) {  // prefetch the next block into the other buffer
-      load_kv_tile(k_tiles + (buf ^ 1) * BLOCK_N * ROW, p.k_cache, table, p.page_size, p.nkv, kvh, (nb + 1) * BLOCK_N, k_lo, k_hi + 1);
-      load_kv_tile(v_tiles + (buf ^ 1) * BLOCK_N * ROW, p.v_cache, table, p.page_size, p.nkv, kvh, (nb + 1) * BLOCK_N, k_lo, k_hi + 1);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    const int buf = (nb - nb_lo) % STAGES;
+#ifdef ALOFA_ATTN_TIMING
+    long long* stamps = reinterpret_cast<long long*>(p.partial_ml);
+    const bool probe = !SPLIT && stamps && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && nb - nb_lo < 8;
+    if (probe) stamps[(nb - nb_lo) * 8 + 0] = clock64();
+#endif
+    cp_async_wait<STAGES - 1>();  // the group of this block (and the query tile) has landed
     __syncthreads();
+#ifdef ALOFA_ATTN_TIMING
+    if (probe) stamps[(nb - nb_lo) * 8 + 1] = clock64();
+#endif
     if (nb == nb_lo) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -184,6 +251,9 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
         mma_16816(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
       }
     }
+#ifdef ALOFA_ATTN_TIMING
+    if (probe) stamps[(nb - nb_lo) * 8 + 2] = clock64();
+#endif
     // ---- visibility -------------------------------------------------------------
     const int j0 = nb * BLOCK_N;
     const bool all_visible = (j0 + BLOCK_N - 1 <= min(warp_pos_min, k_hi)) && (j0 >= k_lo) &&
@@ -215,16 +285,16 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
     const float mn_lo = fmaxf(m_lo, bm_lo), mn_hi = fmaxf(m_hi, bm_hi);
     const float base_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo * p.scale_log2;
     const float base_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi * p.scale_log2;
-    const float corr_lo = (m_lo == -INFINITY) ? 0.f : exp2f(m_lo * p.scale_log2 - base_lo);
-    const float corr_hi = (m_hi == -INFINITY) ? 0.f : exp2f(m_hi * p.scale_log2 - base_hi);
+    const float corr_lo = (m_lo == -INFINITY) ? 0.f : fast_exp2(m_lo * p.scale_log2 - base_lo);
+    const float corr_hi = (m_hi == -INFINITY) ? 0.f : fast_exp2(m_hi * p.scale_log2 - base_hi);
     m_lo = mn_lo;
     m_hi = mn_hi;
     float sum_lo = 0.f, sum_hi = 0.f;
     uint32_t pf[BLOCK_N / 16][4];
 #pragma unroll
     for (int n = 0; n < BLOCK_N / 8; ++n) {
-      const float p0 = exp2f(s[n][0] * p.scale_log2 - base_lo), p1 = exp2f(s[n][1] * p.scale_log2 - base_lo);
-      const float p2 = exp2f(s[n][2] * p.scale_log2 - base_hi), p3 = exp2f(s[n][3] * p.scale_log2 - base_hi);
+      const float p0 = fast_exp2(s[n][0] * p.scale_log2 - base_lo), p1 = fast_exp2(s[n][1] * p.scale_log2 - base_lo);
+      const float p2 = fast_exp2(s[n][2] * p.scale_log2 - base_hi), p3 = fast_exp2(s[n][3] * p.scale_log2 - base_hi);
       sum_lo += p0 + p1;
       sum_hi += p2 + p3;
       // the accumulator layout of two adjacent 8-key tiles is the A layout of one 16-key step
@@ -240,6 +310,9 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
       o[d][2] *= corr_hi;
       o[d][3] *= corr_hi;
     }
+#ifdef ALOFA_ATTN_TIMING
+    if (probe) stamps[(nb - nb_lo) * 8 + 3] = clock64();
+#endif
     // ---- O += P V ---------------------------------------------------------------------
 #pragma unroll
     for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
@@ -253,7 +326,21 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
         mma_16816(o[2 * d2 + 1], pf[kk], vf[2], vf[3]);
       }
     }
+#ifdef ALOFA_ATTN_TIMING
+    if (probe) stamps[(nb - nb_lo) * 8 + 4] = clock64();
+#endif
     __syncthreads();  // everyone is done with this buffer before it is refilled
+#ifdef ALOFA_ATTN_TIMING
+    if (probe) stamps[(nb - nb_lo) * 8 + 5] = clock64();
+#endif
+    if (nb + STAGES <= nb_hi) {
+      load_kv_tiles(k_tiles + buf * BLOCK_N * ROW, v_tiles + buf * BLOCK_N * ROW, p.k_cache, p.v_cache, table, first_entry, p.page_size,
+                    block_in_page, p.nkv, kvh, (nb + STAGES) * BLOCK_N, k_lo, k_hi + 1);
+    }
+    cp_async_commit();
+#ifdef ALOFA_ATTN_TIMING
+    if (probe) stamps[(nb - nb_lo) * 8 + 6] = clock64();
+#endif
   }
   // ---- finish ---------------------------------------------------------------------------
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -309,17 +396,21 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __
   out[(size_t)row * HD + d] = __float2bfloat16_rn(acc / l);
 }
 
-static size_t attention_smem_bytes() { return (size_t)(BLOCK_M + 4 * BLOCK_N) * ROW * sizeof(bf16); }
+constexpr int PREFILL_STAGES = 2, SPLIT_STAGES = 4;
+static size_t attention_smem_bytes(int stages, int table_entries) {
+  return (size_t)(BLOCK_M + 2 * stages * BLOCK_N) * ROW * sizeof(bf16) + (size_t)table_entries * sizeof(int);
+}
 
 ALOFA_API int alofa_attention_head_dim() { return HD; }
 
-// tiles: query tiles of the longest request = ceil(max_q_len * g / 64).  n_splits > 0
+// max_kv_len: the most keys any request of this step has (sizes the shared copy of
+// block-table entries).  tiles: query tiles of the longest request = ceil(max_q_len * g / 64).  n_splits > 0
 // selects split mode (every request has exactly one token in this step and
 // g <= 64); partial_o / partial_ml must then hold n_splits planes.
 ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len,
                                    const int* block_table, int max_blocks, int page_size, int n_seqs, int n_tokens, int tiles, int nh, int nkv,
                                    int window, float scale, int n_splits, int split_keys, float* partial_o, float* partial_ml,
-                                   cudaStream_t stream) {
+                                   int max_kv_len, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || tiles <= 0) return ALOFA_ERR_ARGUMENT;
   if (n_splits > 0 && (nh / nkv > BLOCK_M || split_keys <= 0 || split_keys % BLOCK_N != 0 || !partial_o || !partial_ml || n_seqs != n_tokens))
@@ -342,23 +433,29 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
   p.split_keys = split_keys;
   p.n_rows_total = n_tokens * nh;
   p.scale_log2 = scale * 1.4426950408889634f;
-  const size_t smem = attention_smem_bytes();
+  // entries of a block table one CTA may touch: a split's keys, or up to the longest request
+  const int reach = n_splits > 0 ? split_keys : max_kv_len;
+  p.table_entries = reach / page_size + 2;
+  const size_t smem = attention_smem_bytes(n_splits > 0 ? SPLIT_STAGES : PREFILL_STAGES, p.table_entries);
+  if (smem > 200 * 1024) return ALOFA_ERR_ARGUMENT;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-        cudaFuncSetAttribute(attention_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_bf16_kernel<false, PREFILL_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_bf16_kernel<true, SPLIT_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024) != cudaSuccess)
       return ALOFA_ERR_LAUNCH;
-    prefer_max_shared(attention_bf16_kernel<false>);
-    prefer_max_shared(attention_bf16_kernel<true>);
+    prefer_max_shared(attention_bf16_kernel<false, PREFILL_STAGES>);
+    prefer_max_shared(attention_bf16_kernel<true, SPLIT_STAGES>);
     prefer_max_shared(attention_combine_kernel);
     configured = true;
   }
   if (n_splits > 0) {
-    attention_bf16_kernel<true><<<dim3(n_splits, nkv, n_seqs), 128, smem, stream>>>(p);
+    attention_bf16_kernel<true, SPLIT_STAGES><<<dim3(n_splits, nkv, n_seqs), 128, smem, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
     attention_combine_kernel<<<n_tokens * nh, HD, 0, stream>>>((bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
   } else {
-    attention_bf16_kernel<false><<<dim3(tiles, nkv, n_seqs), 128, smem, stream>>>(p);
+    attention_bf16_kernel<false, PREFILL_STAGES><<<dim3(tiles, nkv, n_seqs), 128, smem, stream>>>(p);
   }
   return launch_status();
 }

@@ -31,13 +31,19 @@ __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, f
   for (int c = threadIdx.x; c < n4; c += blockDim.x) {
     float4 v = hr[c];
     if (partial) {
+      // the splits are read eight at a time (the loads overlap) and added in split order
       const float4* p = reinterpret_cast<const float4*>(partial) + (size_t)src * n4 + c;
-      for (int z = 0; z < splits; ++z) {
-        const float4 a = p[(size_t)z * plane4];
-        v.x += a.x;
-        v.y += a.y;
-        v.z += a.z;
-        v.w += a.w;
+      for (int z0 = 0; z0 < splits; z0 += 8) {
+        float4 a[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = (z0 + i < splits) ? p[(size_t)(z0 + i) * plane4] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v.x += a[i].x;
+          v.y += a[i].y;
+          v.z += a[i].z;
+          v.w += a[i].w;
+        }
       }
       if (bias) {
         const float4 b = reinterpret_cast<const float4*>(bias)[c];
@@ -109,11 +115,19 @@ __device__ __forceinline__ Vec8 load8_partial(const float* partial, const float*
   Vec8 o;
 #pragma unroll
   for (int i = 0; i < 8; ++i) o.v[i] = bias ? bias[col + i] : 0.f;
-  for (int z = 0; z < splits; ++z) {
-    const float4 a = *reinterpret_cast<const float4*>(partial + (size_t)z * plane + offset);
-    const float4 b = *reinterpret_cast<const float4*>(partial + (size_t)z * plane + offset + 4);
-    o.v[0] += a.x; o.v[1] += a.y; o.v[2] += a.z; o.v[3] += a.w;
-    o.v[4] += b.x; o.v[5] += b.y; o.v[6] += b.z; o.v[7] += b.w;
+  for (int z0 = 0; z0 < splits; z0 += 4) {  // four splits in flight, added in split order
+    float4 a[4], b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const bool ok = z0 + i < splits;
+      a[i] = ok ? *reinterpret_cast<const float4*>(partial + (size_t)(z0 + i) * plane + offset) : make_float4(0.f, 0.f, 0.f, 0.f);
+      b[i] = ok ? *reinterpret_cast<const float4*>(partial + (size_t)(z0 + i) * plane + offset + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o.v[0] += a[i].x; o.v[1] += a[i].y; o.v[2] += a[i].z; o.v[3] += a[i].w;
+      o.v[4] += b[i].x; o.v[5] += b[i].y; o.v[6] += b[i].z; o.v[7] += b[i].w;
+    }
   }
   return o;
 }
@@ -178,13 +192,86 @@ __global__ void rope_store_fused_kernel(bf16* __restrict__ q_out, bf16* __restri
   store8(dst + c * 8 + half, b);
 }
 
+// The same from split-K partial sums, 4 + 4 elements per thread so that even a
+// handful of tokens spreads over many threads, eight splits in flight.
+__global__ void rope_store_partial_kernel(bf16* __restrict__ q_out, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                                          const float* __restrict__ partial, const float* __restrict__ bias,
+                                          const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                                          const int* __restrict__ slot_map, int n_tokens, int nh, int nkv, int hd, int splits, int write_cache) {
+  const int chunks = hd >> 3;  // pairs of 4-element chunks per head
+  const int heads = nh + 2 * nkv;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)n_tokens * heads * chunks) return;
+  const int c = (int)(idx % chunks);
+  const int head = (int)((idx / chunks) % heads);
+  const int t = (int)(idx / ((size_t)chunks * heads));
+  const int half = hd >> 1;
+  const int C = heads * hd;
+  const int col = head * hd + c * 4;
+  bf16* dst;
+  bool rotate = true;
+  if (head < nh) {
+    dst = q_out + ((size_t)t * nh + head) * hd;
+  } else {
+    if (!write_cache) return;
+    const int slot = slot_map[t];
+    if (slot < 0) return;
+    if (head < nh + nkv) {
+      dst = k_cache + ((size_t)slot * nkv + (head - nh)) * hd;
+    } else {
+      dst = v_cache + ((size_t)slot * nkv + (head - nh - nkv)) * hd;
+      rotate = false;
+    }
+  }
+  const size_t plane = (size_t)n_tokens * C;
+  const float* pa = partial + (size_t)t * C + col;
+  float4 a = bias ? *reinterpret_cast<const float4*>(bias + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 b = bias ? *reinterpret_cast<const float4*>(bias + col + half) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z0 = 0; z0 < splits; z0 += 8) {
+    float4 xa[8], xb[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool ok = z0 + i < splits;
+      xa[i] = ok ? *reinterpret_cast<const float4*>(pa + (size_t)(z0 + i) * plane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      xb[i] = ok ? *reinterpret_cast<const float4*>(pa + (size_t)(z0 + i) * plane + half) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a.x += xa[i].x; a.y += xa[i].y; a.z += xa[i].z; a.w += xa[i].w;
+      b.x += xb[i].x; b.y += xb[i].y; b.z += xb[i].z; b.w += xb[i].w;
+    }
+  }
+  float va[4] = {a.x, a.y, a.z, a.w}, vb[4] = {b.x, b.y, b.z, b.w};
+  if (rotate) {
+    const float* cs = cos_sin + ((size_t)positions[t] * half + c * 4) * 2;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float co = cs[2 * i], si = cs[2 * i + 1];
+      const float ya = va[i] * co - vb[i] * si, yb = vb[i] * co + va[i] * si;
+      va[i] = ya;
+      vb[i] = yb;
+    }
+  }
+  __nv_bfloat162 lo0 = __floats2bfloat162_rn(va[0], va[1]), lo1 = __floats2bfloat162_rn(va[2], va[3]);
+  __nv_bfloat162 hi0 = __floats2bfloat162_rn(vb[0], vb[1]), hi1 = __floats2bfloat162_rn(vb[2], vb[3]);
+  *reinterpret_cast<uint2*>(dst + c * 4) = make_uint2(*reinterpret_cast<uint32_t*>(&lo0), *reinterpret_cast<uint32_t*>(&lo1));
+  *reinterpret_cast<uint2*>(dst + c * 4 + half) = make_uint2(*reinterpret_cast<uint32_t*>(&hi0), *reinterpret_cast<uint32_t*>(&hi1));
+}
+
 ALOFA_API int alofa_rope_store_fused(void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* partial, const float* bias,
                                      const float* cos_sin, const int* positions, const int* slot_map, int n_tokens, int nh, int nkv, int hd,
                                      int splits, int write_cache, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   if (hd % 16 != 0 || (!qkv && !partial)) return ALOFA_ERR_ARGUMENT;
-  const size_t total = (size_t)n_tokens * (nh + 2 * nkv) * (hd >> 4);
   const int threads = 128;
+  if (partial) {
+    const size_t n = (size_t)n_tokens * (nh + 2 * nkv) * (hd >> 3);
+    ALOFA_PREFER_MAX_SHARED(rope_store_partial_kernel);
+    rope_store_partial_kernel<<<(unsigned)((n + threads - 1) / threads), threads, 0, stream>>>(
+        (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, partial, bias, cos_sin, positions, slot_map, n_tokens, nh, nkv, hd, splits, write_cache);
+    return launch_status();
+  }
+  const size_t total = (size_t)n_tokens * (nh + 2 * nkv) * (hd >> 4);
   ALOFA_PREFER_MAX_SHARED(rope_store_fused_kernel);
   rope_store_fused_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
       (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const bf16*)qkv, partial, bias, cos_sin, positions, slot_map, n_tokens, nh, nkv, hd, splits,

@@ -506,9 +506,19 @@ __global__ void splitk_reduce_kernel(void* __restrict__ out, const float* __rest
   if (idx >= plane) return;
   const int f = (int)(idx % N);
   float a0 = 0.f, a1 = 0.f;
-  for (int z = 0; z < splits; ++z) {
-    a0 += partial[(size_t)z * N_ACC * plane + idx];
-    if (N_ACC == 2) a1 += partial[(size_t)z * N_ACC * plane + plane + idx];
+  for (int z0 = 0; z0 < splits; z0 += 8) {  // eight splits in flight, added in split order
+    float x0[8], x1[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const bool ok = z0 + i < splits;
+      x0[i] = ok ? partial[(size_t)(z0 + i) * N_ACC * plane + idx] : 0.f;
+      x1[i] = (ok && N_ACC == 2) ? partial[(size_t)(z0 + i) * N_ACC * plane + plane + idx] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a0 += x0[i];
+      a1 += x1[i];
+    }
   }
   if (bias) {
     a0 += bias[f];

@@ -120,11 +120,94 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
   if (tid == 0) tokens[r] = pick >= 0 ? pick : top.i;
 }
 
+// Greedy rows in two stages, so that a few rows still use many SMs: stage 1
+// finds the best entry of each of ARGMAX_PARTS slices of a row, stage 2 the
+// best of those (ties to the lowest index in both).  Rows whose temperature is
+// positive are left to sample_kernel.
+#define ARGMAX_PARTS 32
+
+__global__ void __launch_bounds__(256) argmax_parts_kernel(float* __restrict__ part_val, int* __restrict__ part_idx,
+                                                           const float* __restrict__ logits, int vocab) {
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const int r = blockIdx.y, part = blockIdx.x;
+  const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
+  const int lo = part * per, hi = min(vocab, lo + per);
+  const float* x = logits + (size_t)r * vocab;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  ArgMax best{-INFINITY, 0x7fffffff};
+  for (int i = lo + tid; i < hi; i += blockDim.x) best = better(best, ArgMax{x[i], i});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (lane == 0) {
+    sval[warp] = best.v;
+    sidx[warp] = best.i;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    ArgMax out{sval[0], sidx[0]};
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) out = better(out, ArgMax{sval[w], sidx[w]});
+    part_val[r * ARGMAX_PARTS + part] = out.v;
+    part_idx[r * ARGMAX_PARTS + part] = out.i;
+  }
+}
+
+__global__ void argmax_final_kernel(int* __restrict__ tokens, const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                    const float* __restrict__ temperature) {
+  const int r = blockIdx.x, lane = threadIdx.x;  // one warp per row
+  if (temperature && temperature[r] > 0.f) return;
+  ArgMax best{part_val[r * ARGMAX_PARTS + lane], part_idx[r * ARGMAX_PARTS + lane]};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (lane == 0) tokens[r] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+// Rows with a positive temperature only (greedy rows return at once).
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_hot_kernel(int* __restrict__ tokens, const float* __restrict__ logits,
+                                                                    const float* __restrict__ temperature,
+                                                                    const float* __restrict__ uniform, int vocab) {
+  __shared__ float scratch[32];
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  __shared__ int chosen;
+  const int r = blockIdx.x, tid = threadIdx.x;
+  const float temp = temperature[r];
+  if (!(temp > 0.f)) return;
+  const float* x = logits + (size_t)r * vocab;
+  const ArgMax top = block_argmax(x, vocab, sval, sidx);
+  const float xmax = top.v;
+  float part = 0.f;
+  for (int i = tid; i < vocab; i += blockDim.x) part += expf((x[i] - xmax) / temp);
+  const float total = block_sum(part, scratch);
+  auto p_of = [&](int i) { return expf((x[i] - xmax) / temp); };
+  const int pick = inverse_cdf(p_of, vocab, uniform[r] * total, scratch, &chosen);
+  if (tid == 0) tokens[r] = pick >= 0 ? pick : top.i;
+}
+
+// scratch: n_rows * ARGMAX_PARTS floats followed by as many ints, or null (then
+// one block per row does everything).  any_hot: some row has temperature > 0.
 ALOFA_API int alofa_sample(int* tokens, const float* logits, const float* temperature, const float* uniform, int n_rows,
-                           int vocab, cudaStream_t stream) {
+                           int vocab, void* scratch, int any_hot, cudaStream_t stream) {
   if (n_rows <= 0) return ALOFA_OK;
   ALOFA_PREFER_MAX_SHARED(sample_kernel);
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
+  if (!scratch) {
+    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
+    return launch_status();
+  }
+  float* part_val = (float*)scratch;
+  int* part_idx = (int*)(part_val + (size_t)n_rows * ARGMAX_PARTS);
+  ALOFA_PREFER_MAX_SHARED(argmax_parts_kernel);
+  ALOFA_PREFER_MAX_SHARED(argmax_final_kernel);
+  ALOFA_PREFER_MAX_SHARED(sample_hot_kernel);
+  argmax_parts_kernel<<<dim3(ARGMAX_PARTS, n_rows), 256, 0, stream>>>(part_val, part_idx, logits, vocab);
+  argmax_final_kernel<<<n_rows, 32, 0, stream>>>(tokens, part_val, part_idx, temperature);
+  if (any_hot && temperature && uniform) sample_hot_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
   return launch_status();
 }
 

@@ -55,7 +55,7 @@ def _sampling():
     if lib is None:
         lib = load_library("alofa_sampling", ["kernels/sampling.cu"])
         sigs = {
-            "alofa_sample": [_P, _P, _P, _P, _I, _I, _P],
+            "alofa_sample": [_P, _P, _P, _P, _I, _I, _P, _I, _P],
             "alofa_sample_chain": [_P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P],
         }
         for name, args in sigs.items():
@@ -86,7 +86,7 @@ def _attention(head_dim: int):
     if lib is None:
         lib = load_library(f"alofa_attention_hd{head_dim}", ["kernels/attention_bf16.cu"], defines={"HEAD_DIM": head_dim})
         lib.alofa_attention_bf16.restype = _I
-        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P]
+        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P]
         _libs[key] = lib
     return lib
 
@@ -217,17 +217,28 @@ def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, b
     )
 
 
-def sample(tokens, logits, temperature, uniform) -> None:
-    """tokens[r] = argmax (temperature 0) or inverse-CDF draw of softmax(x/T)."""
+ARGMAX_PARTS = 32
+
+
+def sample(tokens, logits, temperature, uniform, scratch=None, any_hot: bool = True) -> None:
+    """tokens[r] = argmax (temperature 0) or inverse-CDF draw of softmax(x/T).
+    With ``scratch`` (fp32, 2 * rows * ARGMAX_PARTS words) greedy rows are found
+    in two stages over many blocks; ``any_hot`` False promises that no row has a
+    positive temperature, so the draw kernel is not launched at all."""
     n, vocab = logits.shape
+    if scratch is not None and scratch.numel() < 2 * n * ARGMAX_PARTS:
+        raise AlofaError("invalid_argument", "sample scratch is too small", f"have={scratch.numel()} need={2 * n * ARGMAX_PARTS}")
     _done(
         _sampling().alofa_sample(
             _dev(tokens, "tokens", torch.int32), _dev(logits, "logits", torch.float32),
             _dev(temperature, "temperature", torch.float32) if temperature is not None else None,
-            _dev(uniform, "uniform", torch.float32) if uniform is not None else None, n, vocab, _stream(),
+            _dev(uniform, "uniform", torch.float32) if uniform is not None else None, n, vocab,
+            _dev(scratch, "scratch", torch.float32) if scratch is not None else None, 1 if any_hot else 0, _stream(),
         ),
         "sample",
     )
+    if scratch is not None:
+        count_launches(2 if any_hot else 1)
 
 
 def sample_chain(tokens, logits, work, fparams, iparams, bias_start, bias_index, bias_value, hist_start, hist_token, hist_count) -> None:
@@ -278,7 +289,7 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
 
 
 def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, block_table, page_size, n_seqs, max_q_len, nh, nkv, hd, window, scale,
-                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None) -> None:
+                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0) -> None:
     """Causal GQA over the paged bf16 cache for a step's requests; with
     ``n_splits`` > 0 (decode tokens only) the keys of each request are split
     over several CTAs and merged."""
@@ -291,7 +302,8 @@ def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, block_table, page_
         _dev(q_start, "q_start", torch.int32), _dev(kv_len, "kv_len", torch.int32), _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], page_size, n_seqs, n, tiles, nh, nkv, int(window or 0), float(scale), n_splits, split_keys,
         _dev(partial_o, "partial_o", torch.float32) if partial_o is not None else None,
-        _dev(partial_ml, "partial_ml", torch.float32) if partial_ml is not None else None, _stream(),
+        _dev(partial_ml, "partial_ml", torch.float32) if partial_ml is not None else None,
+        int(max_kv_len) if max_kv_len else block_table.shape[1] * page_size, _stream(),
     )
     _done(rc, "attention_bf16", f"hd={hd} nh={nh} nkv={nkv} splits={n_splits}")
     if n_splits > 0:

@@ -99,6 +99,7 @@ class StepContext:
         self.max_context = 0  # the longest a request may ever get
         self.capturing = False  # the step is being recorded as a CUDA graph: launch shapes must not depend on this step's lengths
 
+        self.any_hot = True  # some wanted row samples with a positive temperature
         self.pending = None  # (residual stream, Partial): sums a deferred product still owes it
 
     def set_pending(self, h, partial) -> None:

@@ -166,6 +166,7 @@ class StepRunner:
         ctx.decode_only = max_q == 1
         ctx.max_context = self.max_tokens
         ctx.slots, ctx.counts = slots, counts
+        ctx.any_hot = any(e.temperature > 0.0 for e in entries)
         return ctx
 
     def commit(self, ctx: StepContext) -> None:
@@ -186,9 +187,15 @@ class StepRunner:
         logits = self.model.forward(ctx, self.storage.caches)
         tokens = None
         if sample and logits is not None:
-            tokens = torch.empty(ctx.n_out, dtype=torch.int32, device=self.rt.device)
-            ops.sample(tokens, logits, ctx.temperature, ctx.uniform)
+            tokens = self._sample(ctx, logits, ctx.any_hot)
         return logits, tokens
+
+    def _sample(self, ctx: StepContext, logits: torch.Tensor, any_hot: bool) -> torch.Tensor:
+        """One token per wanted row by temperature alone (0 = the largest logit)."""
+        tokens = torch.empty(ctx.n_out, dtype=torch.int32, device=self.rt.device)
+        scratch = ctx.buf((2 * ctx.n_out * ops.ARGMAX_PARTS,), torch.float32)
+        ops.sample(tokens, logits, ctx.temperature, ctx.uniform, scratch, any_hot)
+        return tokens
 
     def _capture(self, ctx: StepContext) -> Optional[DecodeGraph]:
         """Record the decode step of this batch size as a CUDA graph.  The step
@@ -201,8 +208,7 @@ class StepRunner:
         before = ops.launch_count()
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx, self.storage.caches)
-            tokens = torch.empty(ctx.n_out, dtype=torch.int32, device=self.rt.device)
-            ops.sample(tokens, logits, ctx.temperature, ctx.uniform)
+            tokens = self._sample(ctx, logits, True)  # a replay may meet rows of any temperature
         entry = DecodeGraph(graph, logits, tokens, ops.launch_count() - before)
         self._graphs[ctx.n_seqs] = entry
         return entry

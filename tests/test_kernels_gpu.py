@@ -371,6 +371,11 @@ def test_sample_greedy_ties_and_temperature(ops):
     us = np.array([0.3, 0.3, 0.0, 0.999999, 0.5, 0.4], dtype=np.float32)  # row 0: two tied maxima, u below one half picks the first
     ops.sample(tokens, dev(logits), dev(temps), dev(us))
     got = tokens.cpu().tolist()
+    staged = torch.empty(6, dtype=torch.int32, device="cuda")  # the two-stage form gives the same tokens
+    ops.sample(staged, dev(logits), dev(temps), dev(us), torch.empty(2 * 6 * ops.ARGMAX_PARTS, device="cuda"), True)
+    assert staged.cpu().tolist() == got
+    ops.sample(staged, dev(logits), dev(np.zeros(6, dtype=np.float32)), dev(us), torch.empty(2 * 6 * ops.ARGMAX_PARTS, device="cuda"), False)
+    assert staged.cpu().tolist() == [int(np.argmax(r)) for r in logits]
     assert got[0] == 5 and got[5] == int(np.argmax(logits[5]))  # tiny temperature = greedy
     for r in range(1, 5):
         dist = plain.sample_distribution(logits[r], temperature=float(temps[r]))
