@@ -16,6 +16,7 @@
 // cumulative weight within fp32 rounding of a threshold may fall on the other
 // side of it.
 #include "common.cuh"
+#include "no_alloc.h"
 
 #define SAMPLE_THREADS 1024
 
@@ -205,6 +206,47 @@ ALOFA_API int alofa_sample(int* tokens, const float* logits, const float* temper
   ALOFA_PREFER_MAX_SHARED(argmax_parts_kernel);
   ALOFA_PREFER_MAX_SHARED(argmax_final_kernel);
   ALOFA_PREFER_MAX_SHARED(sample_hot_kernel);
+  argmax_parts_kernel<<<dim3(ARGMAX_PARTS, n_rows), 256, 0, stream>>>(part_val, part_idx, logits, vocab);
+  argmax_final_kernel<<<n_rows, 32, 0, stream>>>(tokens, part_val, part_idx, temperature);
+  if (any_hot && temperature && uniform) sample_hot_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// The same without a caller-provided scratch buffer (see no_alloc.h): the
+// stage-1 results live in an array that is part of the library image.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) float g_noalloc_scratch[2 * ALOFA_NOALLOC_MAX_ROWS * ARGMAX_PARTS];
+
+// Device address of g_noalloc_scratch on the current device, looked up once per
+// device.  In host code the array's name is only a handle for this lookup; it
+// is not an address a kernel could use.
+static float* noalloc_scratch_address() {
+  static float* address[64] = {nullptr};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+  if (!address[device]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) {
+      cudaGetLastError();  // leave no sticky error behind
+      return nullptr;
+    }
+    address[device] = static_cast<float*>(ptr);
+  }
+  return address[device];
+}
+
+ALOFA_API int alofa_sample_noalloc_max_rows(void) { return ALOFA_NOALLOC_MAX_ROWS; }
+
+ALOFA_API int alofa_sample_noalloc(int* tokens, const float* logits, const float* temperature, const float* uniform, int n_rows, int vocab,
+                                   int any_hot, cudaStream_t stream) {
+  if (n_rows <= 0) return ALOFA_OK;
+  if (n_rows > ALOFA_NOALLOC_MAX_ROWS) return ALOFA_NOALLOC_TOO_MANY_ROWS;
+  if (!tokens || !logits || vocab <= 0) return ALOFA_ERR_ARGUMENT;
+  float* scratch = noalloc_scratch_address();
+  if (!scratch) return ALOFA_ERR_LAUNCH;
+  float* part_val = scratch;
+  int* part_idx = reinterpret_cast<int*>(scratch + (size_t)n_rows * ARGMAX_PARTS);
   argmax_parts_kernel<<<dim3(ARGMAX_PARTS, n_rows), 256, 0, stream>>>(part_val, part_idx, logits, vocab);
   argmax_final_kernel<<<n_rows, 32, 0, stream>>>(tokens, part_val, part_idx, temperature);
   if (any_hot && temperature && uniform) sample_hot_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
