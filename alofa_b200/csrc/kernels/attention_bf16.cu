@@ -215,16 +215,8 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
 
   for (int nb = nb_lo; nb <= nb_hi; ++nb) {
     const int buf = (nb - nb_lo) % STAGES;
-#ifdef ALOFA_ATTN_TIMING
-    long long* stamps = reinterpret_cast<long long*>(p.partial_ml);
-    const bool probe = !SPLIT && stamps && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && nb - nb_lo < 8;
-    if (probe) stamps[(nb - nb_lo) * 8 + 0] = clock64();
-#endif
     cp_async_wait<STAGES - 1>();  // the group of this block (and the query tile) has landed
     __syncthreads();
-#ifdef ALOFA_ATTN_TIMING
-    if (probe) stamps[(nb - nb_lo) * 8 + 1] = clock64();
-#endif
     if (nb == nb_lo) {
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -251,9 +243,6 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
         mma_16816(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
       }
     }
-#ifdef ALOFA_ATTN_TIMING
-    if (probe) stamps[(nb - nb_lo) * 8 + 2] = clock64();
-#endif
     // ---- visibility -------------------------------------------------------------
     const int j0 = nb * BLOCK_N;
     const bool all_visible = (j0 + BLOCK_N - 1 <= min(warp_pos_min, k_hi)) && (j0 >= k_lo) &&
@@ -310,9 +299,6 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
       o[d][2] *= corr_hi;
       o[d][3] *= corr_hi;
     }
-#ifdef ALOFA_ATTN_TIMING
-    if (probe) stamps[(nb - nb_lo) * 8 + 3] = clock64();
-#endif
     // ---- O += P V ---------------------------------------------------------------------
 #pragma unroll
     for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
@@ -326,21 +312,12 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
         mma_16816(o[2 * d2 + 1], pf[kk], vf[2], vf[3]);
       }
     }
-#ifdef ALOFA_ATTN_TIMING
-    if (probe) stamps[(nb - nb_lo) * 8 + 4] = clock64();
-#endif
     __syncthreads();  // everyone is done with this buffer before it is refilled
-#ifdef ALOFA_ATTN_TIMING
-    if (probe) stamps[(nb - nb_lo) * 8 + 5] = clock64();
-#endif
     if (nb + STAGES <= nb_hi) {
       load_kv_tiles(k_tiles + buf * BLOCK_N * ROW, v_tiles + buf * BLOCK_N * ROW, p.k_cache, p.v_cache, table, first_entry, p.page_size,
                     block_in_page, p.nkv, kvh, (nb + STAGES) * BLOCK_N, k_lo, k_hi + 1);
     }
     cp_async_commit();
-#ifdef ALOFA_ATTN_TIMING
-    if (probe) stamps[(nb - nb_lo) * 8 + 6] = clock64();
-#endif
   }
   // ---- finish ---------------------------------------------------------------------------
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -371,6 +348,222 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
         *reinterpret_cast<uint32_t*>(po + d * 8 + (lane & 3) * 2) = pack_bf16(o[d][half * 2] * inv, o[d][half * 2 + 1] * inv);
     }
   }
+}
+
+// ---------------------------------------------------------------------------
+// Decode tokens, keys spread over the warps.  One CTA owns one (request, KV
+// head, split of 256 keys); its four warps each take one 64-key block of the
+// split, all against the same 16 query rows (the g <= 16 heads of the group,
+// padded), so the four blocks are fetched and processed side by side instead
+// of one after the other.  The warps' (output, maximum, sum) triples are merged
+// through shared memory in warp order, and the split's triple goes to the
+// partial buffers for attention_combine_kernel (or, with a single split,
+// straight to the output).
+// ---------------------------------------------------------------------------
+struct RowState {
+  float m_lo, m_hi, l_lo, l_hi;
+  float o[DTILES][4];
+};
+
+// One warp: 16 query rows against the 64 keys of one block held in shared tiles.
+__device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[KSTEPS][4], const bf16* kt, const bf16* vt, int j0, int lane,
+                                             int pos, int k_lo, int k_hi, int window, float scale_log2) {
+  float s[BLOCK_N / 8][4];
+#pragma unroll
+  for (int n = 0; n < BLOCK_N / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+    for (int n2 = 0; n2 < BLOCK_N / 16; ++n2) {
+      uint32_t kf[4];
+      const bf16* src = kt + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * ROW + ks * 16 + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4(kf, (uint32_t)__cvta_generic_to_shared(src));
+      mma_16816(s[2 * n2], qf[ks], kf[0], kf[1]);
+      mma_16816(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
+    }
+  }
+  const bool all_visible = j0 >= k_lo && j0 + BLOCK_N - 1 <= k_hi && (window <= 0 || j0 > pos - window);
+  if (!all_visible) {
+#pragma unroll
+    for (int n = 0; n < BLOCK_N / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + n * 8 + (lane & 3) * 2 + (e & 1);
+        bool vis = j <= pos && j >= k_lo && j <= k_hi;
+        if (window > 0) vis = vis && j > pos - window;
+        if (!vis) s[n][e] = -INFINITY;
+      }
+  }
+  float bm_lo = -INFINITY, bm_hi = -INFINITY;
+#pragma unroll
+  for (int n = 0; n < BLOCK_N / 8; ++n) {
+    bm_lo = fmaxf(bm_lo, fmaxf(s[n][0], s[n][1]));
+    bm_hi = fmaxf(bm_hi, fmaxf(s[n][2], s[n][3]));
+  }
+  bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 1));
+  bm_lo = fmaxf(bm_lo, __shfl_xor_sync(0xffffffffu, bm_lo, 2));
+  bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 1));
+  bm_hi = fmaxf(bm_hi, __shfl_xor_sync(0xffffffffu, bm_hi, 2));
+  const float mn_lo = fmaxf(st.m_lo, bm_lo), mn_hi = fmaxf(st.m_hi, bm_hi);
+  const float base_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo * scale_log2;
+  const float base_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi * scale_log2;
+  const float corr_lo = (st.m_lo == -INFINITY) ? 0.f : fast_exp2(st.m_lo * scale_log2 - base_lo);
+  const float corr_hi = (st.m_hi == -INFINITY) ? 0.f : fast_exp2(st.m_hi * scale_log2 - base_hi);
+  st.m_lo = mn_lo;
+  st.m_hi = mn_hi;
+  float sum_lo = 0.f, sum_hi = 0.f;
+  uint32_t pf[BLOCK_N / 16][4];
+#pragma unroll
+  for (int n = 0; n < BLOCK_N / 8; ++n) {
+    const float p0 = fast_exp2(s[n][0] * scale_log2 - base_lo), p1 = fast_exp2(s[n][1] * scale_log2 - base_lo);
+    const float p2 = fast_exp2(s[n][2] * scale_log2 - base_hi), p3 = fast_exp2(s[n][3] * scale_log2 - base_hi);
+    sum_lo += p0 + p1;
+    sum_hi += p2 + p3;
+    pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
+    pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+  }
+  st.l_lo = st.l_lo * corr_lo + sum_lo;
+  st.l_hi = st.l_hi * corr_hi + sum_hi;
+#pragma unroll
+  for (int d = 0; d < DTILES; ++d) {
+    st.o[d][0] *= corr_lo;
+    st.o[d][1] *= corr_lo;
+    st.o[d][2] *= corr_hi;
+    st.o[d][3] *= corr_hi;
+  }
+#pragma unroll
+  for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+#pragma unroll
+    for (int d2 = 0; d2 < HD / 16; ++d2) {
+      uint32_t vf[4];
+      const bf16* src = vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROW + d2 * 16 + (lane >> 4) * 8;
+      ldmatrix_x4_trans(vf, (uint32_t)__cvta_generic_to_shared(src));
+      mma_16816(st.o[2 * d2], pf[kk], vf[0], vf[1]);
+      mma_16816(st.o[2 * d2 + 1], pf[kk], vf[2], vf[3]);
+    }
+  }
+}
+
+constexpr int DECODE_SPLIT_KEYS = 4 * BLOCK_N;  // one block per warp
+constexpr int MERGE_ROW = HD + 4;               // floats per merged row in shared memory
+
+__global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);   // [16][ROW]
+  bf16* k_tiles = q_tile + 16 * ROW;                  // [4][64][ROW]
+  bf16* v_tiles = k_tiles + 4 * BLOCK_N * ROW;        // [4][64][ROW]
+  float* merge_o = reinterpret_cast<float*>(v_tiles + 4 * BLOCK_N * ROW);  // [4][16][MERGE_ROW]
+  float* merge_ml = merge_o + 4 * 16 * MERGE_ROW;                          // [4][16][2]
+
+  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int g = p.nh / p.nkv;
+  const int token = p.q_start[seq];
+  const int pos = p.kv_len[seq] - 1;  // the one query position of this request
+  int k_lo = 0;
+  if (p.window > 0) k_lo = max(0, pos - p.window + 1);
+  k_lo = max(k_lo, split * DECODE_SPLIT_KEYS);
+  const int k_hi = min(pos, (split + 1) * DECODE_SPLIT_KEYS - 1);
+  if (k_lo > k_hi) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // the query rows: head kvh * g + r for r < g, zero rows above
+  for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += 128) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool ok = r < g;
+    const bf16* src = ok ? p.q + ((size_t)token * p.nh + kvh * g + r) * HD + c * 8 : p.q;
+    cp_async16((uint32_t)__cvta_generic_to_shared(q_tile + r * ROW + c * 8), src, ok);
+  }
+  // this warp's block of keys
+  const int j0 = (split * 4 + warp) * BLOCK_N;
+  const bool has_keys = j0 <= k_hi && j0 + BLOCK_N - 1 >= k_lo;
+  bf16* kt = k_tiles + warp * BLOCK_N * ROW;
+  bf16* vt = v_tiles + warp * BLOCK_N * ROW;
+  if (has_keys) {
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+    for (int idx = lane; idx < BLOCK_N * CHUNKS; idx += 32) {
+      const int r = idx / CHUNKS, c = idx % CHUNKS;
+      const int j = j0 + r;
+      const bool ok = j >= k_lo && j <= k_hi;
+      size_t offset = 0;
+      if (ok) {
+        const int e = j / p.page_size;
+        const int slot = table[e] * p.page_size + (j - e * p.page_size);
+        offset = ((size_t)slot * p.nkv + kvh) * HD + c * 8;
+      }
+      cp_async16((uint32_t)__cvta_generic_to_shared(kt + r * ROW + c * 8), p.k_cache + offset, ok);
+      cp_async16((uint32_t)__cvta_generic_to_shared(vt + r * ROW + c * 8), p.v_cache + offset, ok);
+    }
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();  // the query tile was copied by all threads
+
+  RowState st;
+  st.m_lo = st.m_hi = -INFINITY;
+  st.l_lo = st.l_hi = 0.f;
+#pragma unroll
+  for (int d = 0; d < DTILES; ++d) st.o[d][0] = st.o[d][1] = st.o[d][2] = st.o[d][3] = 0.f;
+  if (has_keys) {
+    uint32_t qf[KSTEPS][4];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      const bf16* src = q_tile + (lane & 15) * ROW + ks * 16 + (lane >> 4) * 8;
+      ldmatrix_x4(qf[ks], (uint32_t)__cvta_generic_to_shared(src));
+    }
+    attend_block(st, qf, kt, vt, j0, lane, pos, k_lo, k_hi, p.window, p.scale_log2);
+  }
+  // ---- merge the four warps in warp order --------------------------------------------
+  st.l_lo += __shfl_xor_sync(0xffffffffu, st.l_lo, 1);
+  st.l_lo += __shfl_xor_sync(0xffffffffu, st.l_lo, 2);
+  st.l_hi += __shfl_xor_sync(0xffffffffu, st.l_hi, 1);
+  st.l_hi += __shfl_xor_sync(0xffffffffu, st.l_hi, 2);
+  {
+    const int r = lane >> 2;
+    float* mo = merge_o + (warp * 16) * MERGE_ROW;
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+      *reinterpret_cast<float2*>(mo + r * MERGE_ROW + d * 8 + (lane & 3) * 2) = make_float2(st.o[d][0], st.o[d][1]);
+      *reinterpret_cast<float2*>(mo + (r + 8) * MERGE_ROW + d * 8 + (lane & 3) * 2) = make_float2(st.o[d][2], st.o[d][3]);
+    }
+    if ((lane & 3) == 0) {
+      float* ml = merge_ml + warp * 32;
+      ml[r * 2] = (st.m_lo == -INFINITY) ? -INFINITY : st.m_lo * p.scale_log2;
+      ml[r * 2 + 1] = st.l_lo;
+      ml[(r + 8) * 2] = (st.m_hi == -INFINITY) ? -INFINITY : st.m_hi * p.scale_log2;
+      ml[(r + 8) * 2 + 1] = st.l_hi;
+    }
+  }
+  __syncthreads();
+  const bool single = gridDim.x == 1;
+  for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
+    const int r = idx / HD, d = idx % HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[w * 32 + r * 2]);
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = merge_ml[w * 32 + r * 2];
+      const float scale = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
+      l += merge_ml[w * 32 + r * 2 + 1] * scale;
+      acc += merge_o[(w * 16 + r) * MERGE_ROW + d] * scale;
+    }
+    const size_t out_row = (size_t)token * p.nh + kvh * g + r;
+    if (single) {
+      p.out[out_row * HD + d] = __float2bfloat16_rn(acc / l);
+    } else {
+      p.partial_o[((size_t)split * p.n_rows_total + out_row) * HD + d] = acc;
+      if (d == 0) {
+        float* ml = p.partial_ml + ((size_t)split * p.n_rows_total + out_row) * 2;
+        ml[0] = m;
+        ml[1] = l;
+      }
+    }
+  }
+}
+
+static size_t decode_smem_bytes() {
+  return (size_t)(16 + 8 * BLOCK_N) * ROW * sizeof(bf16) + (size_t)4 * 16 * MERGE_ROW * sizeof(float) + (size_t)4 * 32 * sizeof(float);
 }
 
 // Merge the splits of every (token, head) row in split order.  One block of HD
@@ -450,7 +643,20 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
     prefer_max_shared(attention_combine_kernel);
     configured = true;
   }
-  if (n_splits > 0) {
+  if (n_splits > 0 && nh / nkv <= 16 && split_keys == DECODE_SPLIT_KEYS) {
+    // decode tokens of small head groups: the key blocks of a split side by side on the warps
+    static bool decode_configured = false;
+    if (!decode_configured) {
+      if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes()) != cudaSuccess)
+        return ALOFA_ERR_LAUNCH;
+      prefer_max_shared(attention_decode_kernel);
+      decode_configured = true;
+    }
+    attention_decode_kernel<<<dim3(n_splits, nkv, n_seqs), 128, decode_smem_bytes(), stream>>>(p);
+    if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    if (n_splits > 1)
+      attention_combine_kernel<<<n_tokens * nh, HD, 0, stream>>>((bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
+  } else if (n_splits > 0) {
     attention_bf16_kernel<true, SPLIT_STAGES><<<dim3(n_splits, nkv, n_seqs), 128, smem, stream>>>(p);
     if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
     attention_combine_kernel<<<n_tokens * nh, HD, 0, stream>>>((bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);

@@ -589,9 +589,13 @@ template <int BNF, int EPI>
 static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& args, int splits, cudaStream_t stream) {
   constexpr size_t STAGE = (size_t)128 * BK * 2 + (size_t)BNF * BK * 2;
   constexpr int FEATS = (EPI == EPI_GATED) ? BNF / 2 : BNF;
-  // two CTAs share an SM (shared memory and the 512 tensor-memory columns allow
-  // it): while one runs its epilogue the other keeps the tensor cores busy
-  int stages = (int)((108 * 1024) / STAGE);
+  // Many token tiles: two CTAs share an SM (shared memory and the 512
+  // tensor-memory columns allow it), so that while one runs its epilogue the
+  // other keeps the tensor cores busy.  One token tile (decode): the CTAs are
+  // few and each streams its weights once, so the ring is made as deep as
+  // shared memory allows to keep many loads in flight.
+  const size_t budget = args.T > 128 ? 108 * 1024 : 200 * 1024;
+  int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
   const size_t smem = STAGE * stages + 1024;

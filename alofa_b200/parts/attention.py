@@ -113,11 +113,7 @@ class GQAttention(Part):
         if owed is not None:
             ctx.set_pending(h, owed)
 
-    @staticmethod
-    def split_keys(n_requests: int, n_kv_heads: int) -> int:
-        """Keys per CTA when a decode-only step splits each request's keys: a
-        function of the batch alone, so a batch always splits the same way."""
-        return 256 if n_requests * n_kv_heads <= 32 else 512
+    SPLIT_KEYS = 256  # keys per CTA when a decode-only step splits each request's keys (four 64-key blocks, one per warp)
 
     def attend(self, ctx, out, q, cache, group):
         """Attention of the step's rows over the cache: the tensor-core kernel
@@ -125,9 +121,9 @@ class GQAttention(Part):
         if q.dtype == torch.bfloat16 and ops.attention_bf16_supported(self.hd):
             splits, po, pml = 0, None, None
             longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
-            per_split = self.split_keys(ctx.n_seqs, self.nkv)
-            if ctx.decode_only and self.nh // self.nkv <= 64 and longest > per_split:
-                splits = -(-longest // per_split)
+            per_split = self.SPLIT_KEYS
+            if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):
+                splits = max(1, -(-longest // per_split))
                 po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
                 pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
             ops.attention_bf16(

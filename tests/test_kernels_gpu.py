@@ -301,19 +301,24 @@ def test_attention_bf16_sizes_portions_and_windows(ops, hd, nh, nkv, page):
 
 @pytest.mark.parametrize("hd, nh, nkv", [(64, 14, 2), (32, 3, 1), (128, 8, 8)])
 def test_attention_bf16_split_keys(ops, hd, nh, nkv):
-    """Decode tokens with each request's keys split over several CTAs."""
+    """Decode tokens with each request's keys split over several CTAs: splits of
+    128 keys (blocks one after the other) and of 256 (one block per warp)."""
     for window in (None, 300):
-        rng = np.random.default_rng(hd)
-        lens = [1, 63, 64, 65, 300, 1000, 129]
-        got, want = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=[1] * len(lens), page=16, window=window, rng=rng, fast=True, split_keys=128)
-        assert_close(got, want, TOL[BF16], f"split hd={hd} window={window}")
-        whole, _ = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=[1] * len(lens), page=16, window=window, rng=np.random.default_rng(hd), fast=True)
-        assert_close(got, whole, TOL[BF16], "split vs unsplit")
+        for split, page in ((128, 16), (256, 16), (256, 64), (256, 48)):
+            rng = np.random.default_rng(hd)
+            lens = [1, 63, 64, 65, 300, 1000, 129, 256, 257, 511]
+            got, want = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=[1] * len(lens), page=page, window=window, rng=rng, fast=True, split_keys=split)
+            assert_close(got, want, TOL[BF16], f"split {split} hd={hd} window={window} page={page}")
+            whole, _ = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=[1] * len(lens), page=page, window=window, rng=np.random.default_rng(hd), fast=True)
+            assert_close(got, whole, TOL[BF16], "split vs unsplit")
+    # a single split writes the output itself
+    got, want = attention_case(ops, BF16, hd, nh, nkv, lens=[200, 7], q_lens=[1, 1], page=16, window=None, rng=np.random.default_rng(1), fast=True, split_keys=256)
+    assert_close(got, want, TOL[BF16], "one split")
 
 
 def test_attention_bf16_far_key_and_window_edge(ops):
     hd, nh, nkv = 64, 4, 2
-    for split in (0, 64):
+    for split in (0, 64, 256):
         for far in (0, 63, 64, 127, 128, 500, 699):
             rng = np.random.default_rng(far)
 
