@@ -130,6 +130,12 @@ def compile_library(name: str, sources: list, defines: dict | None = None, cuda:
             tmp.unlink()
         raise AlofaError("build", f"compiling {name} failed", f"command={' '.join(cmd)}\n{output}")
     os.replace(tmp, out)
+    for stale in out.parent.glob(f"{name}-*.so"):  # older builds of the same library
+        if stale != out and ".tmp" not in stale.name:
+            try:
+                stale.unlink()
+            except OSError:
+                pass
     _say(f"compiled {name} in {time.time() - start:.1f} s")
     return out
 

@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
   bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);          // [64][ROW]
   bf16* k_tiles = q_tile + BLOCK_M * ROW;                    // [STAGES][64][ROW]
   bf16* v_tiles = k_tiles + STAGES * BLOCK_N * ROW;          // [STAGES][64][ROW]
+  pdl_begin();
 
   const int seq = blockIdx.z, kvh = blockIdx.y;
   const int g = p.nh / p.nkv;
@@ -454,6 +455,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
   bf16* v_tiles = k_tiles + 4 * BLOCK_N * ROW;        // [4][64][ROW]
   float* merge_o = reinterpret_cast<float*>(v_tiles + 4 * BLOCK_N * ROW);  // [4][16][MERGE_ROW]
   float* merge_ml = merge_o + 4 * 16 * MERGE_ROW;                          // [4][16][2]
+  pdl_begin();
 
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int g = p.nh / p.nkv;
@@ -571,6 +573,7 @@ static size_t decode_smem_bytes() {
 __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                          const int* __restrict__ kv_len, int nh, int window, int split_keys, int n_rows_total) {
   const int row = blockIdx.x;       // token * nh + head; one token per request
+  pdl_begin();
   const int seq = row / nh;
   const int P = kv_len[seq] - 1;
   int k_lo = 0;
@@ -652,16 +655,16 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
       prefer_max_shared(attention_decode_kernel);
       decode_configured = true;
     }
-    attention_decode_kernel<<<dim3(n_splits, nkv, n_seqs), 128, decode_smem_bytes(), stream>>>(p);
+    launch_dep(attention_decode_kernel, dim3(n_splits, nkv, n_seqs), 128, decode_smem_bytes(), stream, p);
     if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
     if (n_splits > 1)
-      attention_combine_kernel<<<n_tokens * nh, HD, 0, stream>>>((bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
+      launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
   } else if (n_splits > 0) {
-    attention_bf16_kernel<true, SPLIT_STAGES><<<dim3(n_splits, nkv, n_seqs), 128, smem, stream>>>(p);
+    launch_dep(attention_bf16_kernel<true, SPLIT_STAGES>, dim3(n_splits, nkv, n_seqs), 128, smem, stream, p);
     if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
-    attention_combine_kernel<<<n_tokens * nh, HD, 0, stream>>>((bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
+    launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
   } else {
-    attention_bf16_kernel<false, PREFILL_STAGES><<<dim3(tiles, nkv, n_seqs), 128, smem, stream>>>(p);
+    launch_dep(attention_bf16_kernel<false, PREFILL_STAGES>, dim3(tiles, nkv, n_seqs), 128, smem, stream, p);
   }
   return launch_status();
 }

@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define ALOFA_API extern "C" __attribute__((visibility("default")))
 
@@ -70,5 +71,42 @@ static inline void prefer_max_shared(K kernel) {
       done_ = true;                      \
     }                                    \
   } while (0)
+
+// Programmatic dependent launch.  A kernel launched with launch_dep may become
+// resident while the kernel before it in the stream is still running; it must
+// call pdl_begin() before it touches global memory: that lets the kernel after
+// it start launching in turn, then waits until everything the stream ran
+// before has completed and is visible.  Launch latency and per-CTA set-up
+// (barrier initialisation, tensor-memory allocation) thus overlap the tail of
+// the previous kernel.  Under an ordinary launch pdl_begin() does nothing.
+// ALOFA_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_begin() {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+static inline bool pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* env = getenv("ALOFA_PDL");
+    enabled = (env && env[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 static inline int launch_status() { return cudaGetLastError() == cudaSuccess ? ALOFA_OK : ALOFA_ERR_LAUNCH; }

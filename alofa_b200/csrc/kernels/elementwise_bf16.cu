@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, f
                                                          const int* __restrict__ rows, int n_tokens, int hidden, int splits, float eps) {
   extern __shared__ float row_buf[];  // hidden floats
   __shared__ float scratch[32];
+  pdl_begin();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float4* hr = reinterpret_cast<float4*>(h + (size_t)src * hidden);
@@ -84,9 +85,9 @@ ALOFA_API int alofa_norm_fused(void* out, void* h, const float* w, const float* 
   ALOFA_PREFER_MAX_SHARED(norm_fused_kernel<bf16>);
   ALOFA_PREFER_MAX_SHARED(norm_fused_kernel<float>);
   if (out_bf16)
-    norm_fused_kernel<bf16><<<n_rows, 256, smem, stream>>>((bf16*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps);
+    launch_dep(norm_fused_kernel<bf16>, n_rows, 256, smem, stream, (bf16*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps);
   else
-    norm_fused_kernel<float><<<n_rows, 256, smem, stream>>>((float*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps);
+    launch_dep(norm_fused_kernel<float>, n_rows, 256, smem, stream, (float*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps);
   return launch_status();
 }
 
@@ -143,6 +144,7 @@ __global__ void rope_store_fused_kernel(bf16* __restrict__ q_out, bf16* __restri
                                         const float* __restrict__ cos_sin, const int* __restrict__ positions,
                                         const int* __restrict__ slot_map, int n_tokens, int nh, int nkv, int hd, int splits, int write_cache) {
   const int chunks = hd >> 4;  // pairs of 8-element chunks per head
+  pdl_begin();
   const int heads = nh + 2 * nkv;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)n_tokens * heads * chunks) return;
@@ -199,6 +201,7 @@ __global__ void rope_store_partial_kernel(bf16* __restrict__ q_out, bf16* __rest
                                           const float* __restrict__ cos_sin, const int* __restrict__ positions,
                                           const int* __restrict__ slot_map, int n_tokens, int nh, int nkv, int hd, int splits, int write_cache) {
   const int chunks = hd >> 3;  // pairs of 4-element chunks per head
+  pdl_begin();
   const int heads = nh + 2 * nkv;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)n_tokens * heads * chunks) return;
@@ -267,13 +270,13 @@ ALOFA_API int alofa_rope_store_fused(void* q_out, void* k_cache, void* v_cache, 
   if (partial) {
     const size_t n = (size_t)n_tokens * (nh + 2 * nkv) * (hd >> 3);
     ALOFA_PREFER_MAX_SHARED(rope_store_partial_kernel);
-    rope_store_partial_kernel<<<(unsigned)((n + threads - 1) / threads), threads, 0, stream>>>(
+    launch_dep(rope_store_partial_kernel, (unsigned)((n + threads - 1) / threads), threads, 0, stream, 
         (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, partial, bias, cos_sin, positions, slot_map, n_tokens, nh, nkv, hd, splits, write_cache);
     return launch_status();
   }
   const size_t total = (size_t)n_tokens * (nh + 2 * nkv) * (hd >> 4);
   ALOFA_PREFER_MAX_SHARED(rope_store_fused_kernel);
-  rope_store_fused_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
+  launch_dep(rope_store_fused_kernel, (unsigned)((total + threads - 1) / threads), threads, 0, stream, 
       (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (const bf16*)qkv, partial, bias, cos_sin, positions, slot_map, n_tokens, nh, nkv, hd, splits,
       write_cache);
   return launch_status();

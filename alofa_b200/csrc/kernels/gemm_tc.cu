@@ -163,6 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
+  pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
 #ifdef ALOFA_GEMM_TIMING
   if (probe && threadIdx.x == 0) args.stamps[1] = clock64();
 #endif
@@ -349,6 +350,7 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
+  pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
 
   if (warp == 0) {
     if (lane == 0) {
@@ -502,6 +504,7 @@ __global__ void splitk_reduce_kernel(void* __restrict__ out, const float* __rest
                                      int splits, int out_bf16) {
   constexpr int N_ACC = (EPI == EPI_GATED) ? 2 : 1;
   const size_t plane = (size_t)T * N;
+  pdl_begin();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= plane) return;
   const int f = (int)(idx % N);
@@ -581,7 +584,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
     configured = true;
   }
   dim3 grid((args.N + BM - 1) / BM, (args.T + BN - 1) / BN, splits);
-  gemm_tc_kernel<BN, EPI><<<grid, NUM_THREADS, smem, stream>>>(mw, mx, args, stages);
+  launch_dep(gemm_tc_kernel<BN, EPI>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
   return launch_status();
 }
 
@@ -607,7 +610,7 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
     configured = true;
   }
   dim3 grid((args.N + FEATS - 1) / FEATS, (args.T + 127) / 128, splits);
-  gemm_tc_tokens_kernel<BNF, EPI><<<grid, NUM_THREADS, smem, stream>>>(mw, mx, args, stages);
+  launch_dep(gemm_tc_tokens_kernel<BNF, EPI>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
   return launch_status();
 }
 
@@ -689,9 +692,9 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   const size_t plane = (size_t)T * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)((plane + threads - 1) / threads);
-  if (epi == EPI_STORE) splitk_reduce_kernel<EPI_STORE><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
-  else if (epi == EPI_RESIDUAL) splitk_reduce_kernel<EPI_RESIDUAL><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
-  else splitk_reduce_kernel<EPI_GATED><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  if (epi == EPI_STORE) launch_dep(splitk_reduce_kernel<EPI_STORE>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
+  else if (epi == EPI_RESIDUAL) launch_dep(splitk_reduce_kernel<EPI_RESIDUAL>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
+  else launch_dep(splitk_reduce_kernel<EPI_GATED>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
   return launch_status();
 }
 
@@ -704,9 +707,9 @@ ALOFA_API int alofa_splitk_reduce(void* out, const float* partial, const float* 
   const size_t plane = (size_t)T * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)((plane + threads - 1) / threads);
-  if (epi == EPI_STORE) splitk_reduce_kernel<EPI_STORE><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
-  else if (epi == EPI_RESIDUAL) splitk_reduce_kernel<EPI_RESIDUAL><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
-  else if (epi == EPI_GATED) splitk_reduce_kernel<EPI_GATED><<<blocks, threads, 0, stream>>>(out, partial, bias, T, N, splits, out_bf16);
+  if (epi == EPI_STORE) launch_dep(splitk_reduce_kernel<EPI_STORE>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
+  else if (epi == EPI_RESIDUAL) launch_dep(splitk_reduce_kernel<EPI_RESIDUAL>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
+  else if (epi == EPI_GATED) launch_dep(splitk_reduce_kernel<EPI_GATED>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
   else return ALOFA_ERR_ARGUMENT;
   return launch_status();
 }

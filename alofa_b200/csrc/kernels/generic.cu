@@ -19,6 +19,7 @@
 template <typename TW>
 __global__ void embed_gather_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                     const int* __restrict__ ids, int hidden, int vocab, int* status) {
+  pdl_begin();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -33,9 +34,9 @@ ALOFA_API int alofa_embed_gather(void* out, const void* table, const int* ids, i
   ALOFA_PREFER_MAX_SHARED(embed_gather_kernel<bf16>);
   ALOFA_PREFER_MAX_SHARED(embed_gather_kernel<float>);
   if (table_bf16)
-    embed_gather_kernel<bf16><<<n_tokens, 256, 0, stream>>>((float*)out, (const bf16*)table, ids, hidden, vocab, status);
+    launch_dep(embed_gather_kernel<bf16>, n_tokens, 256, 0, stream, (float*)out, (const bf16*)table, ids, hidden, vocab, status);
   else
-    embed_gather_kernel<float><<<n_tokens, 256, 0, stream>>>((float*)out, (const float*)table, ids, hidden, vocab, status);
+    launch_dep(embed_gather_kernel<float>, n_tokens, 256, 0, stream, (float*)out, (const float*)table, ids, hidden, vocab, status);
   return launch_status();
 }
 

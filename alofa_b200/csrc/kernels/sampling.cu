@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(int* __restrict_
   __shared__ int sidx[32];
   __shared__ int chosen;
   const int r = blockIdx.x, tid = threadIdx.x;
+  pdl_begin();
   const float* x = logits + (size_t)r * vocab;
   const ArgMax top = block_argmax(x, vocab, sval, sidx);
   const float temp = temperature ? temperature[r] : 0.f;
@@ -132,6 +133,7 @@ __global__ void __launch_bounds__(256) argmax_parts_kernel(float* __restrict__ p
   __shared__ float sval[32];
   __shared__ int sidx[32];
   const int r = blockIdx.y, part = blockIdx.x;
+  pdl_begin();
   const int per = (vocab + ARGMAX_PARTS - 1) / ARGMAX_PARTS;
   const int lo = part * per, hi = min(vocab, lo + per);
   const float* x = logits + (size_t)r * vocab;
@@ -159,6 +161,7 @@ __global__ void __launch_bounds__(256) argmax_parts_kernel(float* __restrict__ p
 __global__ void argmax_final_kernel(int* __restrict__ tokens, const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                     const float* __restrict__ temperature) {
   const int r = blockIdx.x, lane = threadIdx.x;  // one warp per row
+  pdl_begin();
   if (temperature && temperature[r] > 0.f) return;
   ArgMax best{part_val[r * ARGMAX_PARTS + lane], part_idx[r * ARGMAX_PARTS + lane]};
 #pragma unroll
@@ -178,6 +181,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_hot_kernel(int* __restr
   __shared__ int sidx[32];
   __shared__ int chosen;
   const int r = blockIdx.x, tid = threadIdx.x;
+  pdl_begin();
   const float temp = temperature[r];
   if (!(temp > 0.f)) return;
   const float* x = logits + (size_t)r * vocab;
@@ -198,7 +202,7 @@ ALOFA_API int alofa_sample(int* tokens, const float* logits, const float* temper
   if (n_rows <= 0) return ALOFA_OK;
   ALOFA_PREFER_MAX_SHARED(sample_kernel);
   if (!scratch) {
-    sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
+    launch_dep(sample_kernel, n_rows, SAMPLE_THREADS, 0, stream, tokens, logits, temperature, uniform, vocab);
     return launch_status();
   }
   float* part_val = (float*)scratch;
@@ -206,9 +210,9 @@ ALOFA_API int alofa_sample(int* tokens, const float* logits, const float* temper
   ALOFA_PREFER_MAX_SHARED(argmax_parts_kernel);
   ALOFA_PREFER_MAX_SHARED(argmax_final_kernel);
   ALOFA_PREFER_MAX_SHARED(sample_hot_kernel);
-  argmax_parts_kernel<<<dim3(ARGMAX_PARTS, n_rows), 256, 0, stream>>>(part_val, part_idx, logits, vocab);
-  argmax_final_kernel<<<n_rows, 32, 0, stream>>>(tokens, part_val, part_idx, temperature);
-  if (any_hot && temperature && uniform) sample_hot_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, temperature, uniform, vocab);
+  launch_dep(argmax_parts_kernel, dim3(ARGMAX_PARTS, n_rows), 256, 0, stream, part_val, part_idx, logits, vocab);
+  launch_dep(argmax_final_kernel, n_rows, 32, 0, stream, tokens, part_val, part_idx, temperature);
+  if (any_hot && temperature && uniform) launch_dep(sample_hot_kernel, n_rows, SAMPLE_THREADS, 0, stream, tokens, logits, temperature, uniform, vocab);
   return launch_status();
 }
 
@@ -343,6 +347,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_chain_kernel(
     const int* __restrict__ bias_start, const int* __restrict__ bias_index, const float* __restrict__ bias_value,
     const int* __restrict__ hist_start, const int* __restrict__ hist_token, const int* __restrict__ hist_count) {
   __shared__ ChainShared sh;
+  pdl_begin();
   const int r = blockIdx.x, tid = threadIdx.x, V = vocab;
   const float* x = logits + (size_t)r * V;
   float* vals = work + (size_t)r * V;
@@ -470,7 +475,7 @@ ALOFA_API int alofa_sample_chain(int* tokens, const float* logits, float* work, 
                                  const int* hist_start, const int* hist_token, const int* hist_count, cudaStream_t stream) {
   if (n_rows <= 0) return ALOFA_OK;
   if (vocab >= (1 << 24)) return ALOFA_ERR_ARGUMENT;
-  sample_chain_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(tokens, logits, work, vocab, fparams, iparams, bias_start,
+  launch_dep(sample_chain_kernel, n_rows, SAMPLE_THREADS, 0, stream, tokens, logits, work, vocab, fparams, iparams, bias_start,
                                                              bias_index, bias_value, hist_start, hist_token, hist_count);
   return launch_status();
 }
