@@ -445,16 +445,20 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
   }
 }
 
-constexpr int DECODE_SPLIT_KEYS = 4 * BLOCK_N;  // one block per warp
-constexpr int MERGE_ROW = HD + 4;               // floats per merged row in shared memory
+constexpr int MERGE_ROW = HD + 4;  // floats per merged row in shared memory
 
-__global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams p) {
+// WARPS warps, one 64-key block each: a split is WARPS * 64 keys.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const AttnParams p) {
+  constexpr int DECODE_SPLIT_KEYS = WARPS * BLOCK_N;
+  constexpr int THREADS = WARPS * 32;
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);   // [16][ROW]
-  bf16* k_tiles = q_tile + 16 * ROW;                  // [4][64][ROW]
-  bf16* v_tiles = k_tiles + 4 * BLOCK_N * ROW;        // [4][64][ROW]
-  float* merge_o = reinterpret_cast<float*>(v_tiles + 4 * BLOCK_N * ROW);  // [4][16][MERGE_ROW]
-  float* merge_ml = merge_o + 4 * 16 * MERGE_ROW;                          // [4][16][2]
+  bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);       // [16][ROW]
+  bf16* k_tiles = q_tile + 16 * ROW;                      // [WARPS][64][ROW]
+  bf16* v_tiles = k_tiles + WARPS * BLOCK_N * ROW;        // [WARPS][64][ROW]
+  // the merge buffers reuse the key tiles once every warp is done with them
+  float* merge_o = reinterpret_cast<float*>(k_tiles);     // [WARPS][16][MERGE_ROW]
+  float* merge_ml = merge_o + WARPS * 16 * MERGE_ROW;     // [WARPS][16][2]
   pdl_begin();
 
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -469,14 +473,14 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // the query rows: head kvh * g + r for r < g, zero rows above
-  for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += 128) {
+  for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += THREADS) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;
     const bool ok = r < g;
     const bf16* src = ok ? p.q + ((size_t)token * p.nh + kvh * g + r) * HD + c * 8 : p.q;
     cp_async16((uint32_t)__cvta_generic_to_shared(q_tile + r * ROW + c * 8), src, ok);
   }
   // this warp's block of keys
-  const int j0 = (split * 4 + warp) * BLOCK_N;
+  const int j0 = (split * WARPS + warp) * BLOCK_N;
   const bool has_keys = j0 <= k_hi && j0 + BLOCK_N - 1 >= k_lo;
   bf16* kt = k_tiles + warp * BLOCK_N * ROW;
   bf16* vt = v_tiles + warp * BLOCK_N * ROW;
@@ -514,7 +518,8 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
     }
     attend_block(st, qf, kt, vt, j0, lane, pos, k_lo, k_hi, p.window, p.scale_log2);
   }
-  // ---- merge the four warps in warp order --------------------------------------------
+  // ---- merge the warps in warp order ---------------------------------------------------
+  __syncthreads();  // every warp is done with the key tiles the merge buffers overlay
   st.l_lo += __shfl_xor_sync(0xffffffffu, st.l_lo, 1);
   st.l_lo += __shfl_xor_sync(0xffffffffu, st.l_lo, 2);
   st.l_hi += __shfl_xor_sync(0xffffffffu, st.l_hi, 1);
@@ -537,14 +542,14 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
   }
   __syncthreads();
   const bool single = gridDim.x == 1;
-  for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
+  for (int idx = threadIdx.x; idx < g * HD; idx += THREADS) {
     const int r = idx / HD, d = idx % HD;
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[w * 32 + r * 2]);
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge_ml[w * 32 + r * 2]);
     float l = 0.f, acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       const float mw = merge_ml[w * 32 + r * 2];
       const float scale = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
       l += merge_ml[w * 32 + r * 2 + 1] * scale;
@@ -564,8 +569,23 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const AttnParams 
   }
 }
 
-static size_t decode_smem_bytes() {
-  return (size_t)(16 + 8 * BLOCK_N) * ROW * sizeof(bf16) + (size_t)4 * 16 * MERGE_ROW * sizeof(float) + (size_t)4 * 32 * sizeof(float);
+static size_t decode_smem_bytes(int warps) {
+  const size_t tiles = (size_t)(2 * warps * BLOCK_N) * ROW * sizeof(bf16);
+  const size_t merge = (size_t)warps * 16 * MERGE_ROW * sizeof(float) + (size_t)warps * 32 * sizeof(float);
+  return (size_t)16 * ROW * sizeof(bf16) + (tiles > merge ? tiles : merge);
+}
+
+template <int WARPS>
+static int launch_decode(const AttnParams& p, int n_splits, int nkv, int n_seqs, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_decode_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes(WARPS)) != cudaSuccess)
+      return ALOFA_ERR_LAUNCH;
+    prefer_max_shared(attention_decode_kernel<WARPS>);
+    configured = true;
+  }
+  launch_dep(attention_decode_kernel<WARPS>, dim3(n_splits, nkv, n_seqs), WARPS * 32, decode_smem_bytes(WARPS), stream, p);
+  return cudaGetLastError() == cudaSuccess ? ALOFA_OK : ALOFA_ERR_LAUNCH;
 }
 
 // Merge the splits of every (token, head) row in split order.  One block of HD
@@ -646,17 +666,10 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
     prefer_max_shared(attention_combine_kernel);
     configured = true;
   }
-  if (n_splits > 0 && nh / nkv <= 16 && split_keys == DECODE_SPLIT_KEYS) {
+  if (n_splits > 0 && nh / nkv <= 16 && (split_keys == 4 * BLOCK_N || split_keys == 2 * BLOCK_N)) {
     // decode tokens of small head groups: the key blocks of a split side by side on the warps
-    static bool decode_configured = false;
-    if (!decode_configured) {
-      if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes()) != cudaSuccess)
-        return ALOFA_ERR_LAUNCH;
-      prefer_max_shared(attention_decode_kernel);
-      decode_configured = true;
-    }
-    launch_dep(attention_decode_kernel, dim3(n_splits, nkv, n_seqs), 128, decode_smem_bytes(), stream, p);
-    if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    const int rc = split_keys == 4 * BLOCK_N ? launch_decode<4>(p, n_splits, nkv, n_seqs, stream) : launch_decode<2>(p, n_splits, nkv, n_seqs, stream);
+    if (rc != ALOFA_OK) return rc;
     if (n_splits > 1)
       launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
   } else if (n_splits > 0) {

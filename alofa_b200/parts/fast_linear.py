@@ -28,6 +28,10 @@ def _tile(tokens: int, features: int, gated: bool) -> int:
     256, so wide feature tiles are what pays)."""
     for bn in (16, 32, 64):
         if tokens <= bn:
+            # a very tall weight (an output head) fills the GPU several times over
+            # either way; wide tiles with the tokens on the M side stream it faster
+            if not gated and -(-features // 128) > 4 * SMS:
+                return -256
             return bn
     if gated:
         return -256  # 128 gate rows and their 128 up rows
