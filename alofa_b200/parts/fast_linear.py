@@ -46,10 +46,14 @@ def _ctas(tokens: int, features: int, tile: int, gated: bool) -> int:
     return -(-features // per_cta) * -(-tokens // 128)
 
 
-def _splits(ctas: int, depth: int) -> int:
+def _splits(ctas: int, depth: int, deferrable: bool = False) -> int:
     slices = -(-depth // K_SLICE)
-    if ctas >= SMS // 2 or slices < 2:
+    if slices < 2:
         return 1
+    if ctas >= SMS // 2:
+        # a deep product that does not fill the GPU once: two halves of the depth
+        # side by side, when the consumer adds the halves up for free
+        return 2 if deferrable and ctas < SMS and slices >= 32 else 1
     return max(1, min(slices, SMS // ctas))
 
 
@@ -70,7 +74,7 @@ def plan(linear):
         if x.data_ptr() % 16 or not x.is_contiguous():
             return False
         bn = _tile(tokens, linear.out_features, gated)
-        splits = ops.gemm_tc_splits(depth, _splits(_ctas(tokens, linear.out_features, bn, gated), depth))
+        splits = ops.gemm_tc_splits(depth, _splits(_ctas(tokens, linear.out_features, bn, gated), depth, defer and n_acc == 1))
         partial = None
         if splits > 1:
             partial = torch.empty((splits * n_acc, tokens, linear.out_features), dtype=torch.float32, device=x.device)

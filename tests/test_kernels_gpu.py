@@ -127,6 +127,19 @@ def test_norm_fused_adds_owed_partial_sums(ops, out_dtype):
     assert ops.norm_fused(out, dev(h), dev(w), 1e-6, dev(rows), dev(partial), splits, None)
     assert_close(out.float().cpu(), plain.rmsnorm((h.astype(np.float64) + partial.astype(np.float64).sum(axis=0))[rows], w, 1e-6), TOL[out_dtype], "gathered rows")
     assert not ops.norm_fused(torch.empty(2, 6, dtype=out_dtype, device="cuda"), dev(h[:, :6].copy()), dev(w[:6].copy()), 1e-6)  # width not a multiple of 4
+    # many rows take the warp-per-row form
+    many = rng.normal(size=(300, 200)).astype(np.float32)
+    part = rng.normal(size=(2, 300, 200)).astype(np.float32)
+    wm = (1 + 0.1 * rng.normal(size=200)).astype(np.float32)
+    hm = dev(many)
+    out = torch.empty(300, 200, dtype=out_dtype, device="cuda")
+    assert ops.norm_fused(out, hm, dev(wm), 1e-5, None, dev(part), 2, None)
+    total = many.astype(np.float64) + part.astype(np.float64).sum(axis=0)
+    assert_close(hm.cpu(), total, 1e-6, "stream after the sums (many rows)")
+    assert_close(out.float().cpu(), plain.rmsnorm(total, wm, 1e-5), TOL[out_dtype], "norm (many rows)")
+    out = torch.empty(300, 200, dtype=out_dtype, device="cuda")
+    assert ops.norm_fused(out, dev(many), dev(wm), 1e-5)
+    assert_close(out.float().cpu(), plain.rmsnorm(many, wm, 1e-5), TOL[out_dtype], "plain norm (many rows)")
 
 
 @pytest.mark.parametrize("hd", [16, 48, 64, 128])
