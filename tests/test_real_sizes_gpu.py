@@ -1,0 +1,66 @@
+"""The layer sizes of the benchmarked shape (hidden 896, 14 heads on 2, head 64,
+intermediate 4864, vocabulary 151936, tied head), two layers deep, against the
+plain implementation: whole prompt, decoded tail, and a mixed step.  These are
+the sizes the tensor-core kernels are tuned for (tiles of 128/256 with tails:
+1152 = 9 x 128, 4864 = 38 x 128, 151936 = 1187 x 128)."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+
+
+@pytest.fixture(scope="module")
+def shaped():
+    from alofa_b200.models.qwen2 import Qwen2Config, build_spec
+    from alofa_b200.parts import expected_tensors
+    from alofa_b200.weights.random_init import random_state
+
+    cfg = Qwen2Config(2, 896, 14, 2, 64, 4864, 151936, 1e-6, 1e6, True, 32768)
+    state = random_state(expected_tensors(build_spec(cfg)), 5, torch.bfloat16)
+    wts = {k: v.to(torch.float64).numpy() for k, v in state.items()}
+    pcfg = {"L": 2, "H": 896, "nh": 14, "nkv": 2, "hd": 64, "I": 4864, "V": 151936, "eps": 1e-6, "theta": 1e6, "tied": True, "window": None, "first_window_layer": 2}
+    rng = np.random.default_rng(0)
+    a = [int(t) for t in rng.integers(0, 151936, 150)]
+    b = [int(t) for t in rng.integers(0, 151936, 70)]
+    ref = {"a": plain.forward(a, wts, pcfg), "b": plain.forward(b, wts, pcfg)}
+    return cfg, state, {"a": a, "b": b}, ref
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_benchmark_layer_sizes_against_plain(shaped, dtype):
+    from alofa_b200.engine.loading import compute_dtype
+    from alofa_b200.engine.step import StepEntry, StepRunner
+    from alofa_b200.models.qwen2 import build_spec
+    from alofa_b200.parts.base import Runtime
+    from alofa_b200.parts.model import Model
+    from alofa_b200.weights.loader import load_state
+
+    cfg, state, toks, ref = shaped
+    model = Model(build_spec(cfg), Runtime(torch.device("cuda"), compute_dtype(dtype)))
+    model.load(load_state(model.tensors(), state, model.rt.dtype, model.rt.device))
+    runner = StepRunner(model, block_size=64, num_pages=8, max_requests=4, max_tokens=512, max_step_tokens=256)
+    a, b = toks["a"], toks["b"]
+    sa, sb = runner.admit(1), runner.admit(2)
+    got = {"a": [], "b": []}
+    got["a"].append(runner.forward([StepEntry(sa, a[:130], list(range(130)))]).cpu().numpy())  # a prompt portion past one 128-token tile
+    mixed = runner.forward([StepEntry(sa, a[130:131], [0]), StepEntry(sb, b[:67], list(range(67)))]).cpu().numpy()  # a decoded token beside a prompt
+    got["a"].append(mixed[:1])
+    got["b"].append(mixed[1:])
+    for i in range(131, 150):  # decoded one by one (CUDA graph of batch 1 in bfloat16)
+        got["a"].append(runner.forward([StepEntry(sa, a[i : i + 1], [0])]).cpu().numpy())
+    both = runner.forward([StepEntry(sb, b[67:68], [0])]).cpu().numpy()
+    got["b"].append(both)
+    got["b"].append(runner.forward([StepEntry(sb, b[68:], [0, 1])]).cpu().numpy())
+    runner.check_status()
+    for rid in ("a", "b"):
+        mine = np.concatenate(got[rid]).astype(np.float64)
+        want = ref[rid]
+        bound = TOL[dtype] * max(1.0, float(np.abs(want).max()))
+        diff = np.abs(mine - want)
+        assert diff.max() <= bound, f"{dtype} request {rid}: position {int(np.argmax(diff.max(axis=1) > bound))} differs by {diff.max():.3e} > {bound:.3e}"
+        assert (mine.argmax(axis=1) == want.argmax(axis=1)).mean() > 0.9
