@@ -332,6 +332,10 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * FEATS, t0 = blockIdx.y * 128;
+#ifdef ALOFA_GEMM_TIMING
+  const bool probe = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && args.stamps;
+  if (probe && threadIdx.x == 0) args.stamps[0] = clock64();
+#endif
   const int total_slices = (args.K + BK - 1) / BK;
   const int slice_begin = blockIdx.z * args.k_slices_per_split;
   const int n_slices = min(total_slices, slice_begin + args.k_slices_per_split) - slice_begin;
@@ -374,6 +378,9 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       for (int i = 0; i < n_slices; ++i) {
         const int s = i % stages;
         if (!mbar_wait(&full_bar[s], (i / stages) & 1, &abort_flag)) break;
+#ifdef ALOFA_GEMM_TIMING
+        if (probe && i == 0) args.stamps[2] = clock64();
+#endif
         tc_fence_after();
         const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
         const uint64_t desc_a = smem_desc_sw128(stage), desc_b = smem_desc_sw128(stage + A_BYTES);
@@ -390,7 +397,89 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
-    if (ok && t0 + q * 32 < args.T) {
+#ifdef ALOFA_GEMM_TIMING
+    if (probe && warp == 2 && lane == 0) args.stamps[3] = clock64();
+#endif
+    const bool staged = (args.N & 3) == 0 && !(GATED && gridDim.z > 1);
+    if (ok && staged && t0 + q * 32 < args.T) {
+      // The accumulator rows go through shared memory (the ring is idle now) so
+      // that global memory is written a whole row of 128 features at a time:
+      // each thread drops its row's values into a padded tile, then the warp
+      // walks the 32 rows with one 16-byte access per lane.
+      constexpr int PITCH = 132;  // floats per staged row: 128 + padding against bank conflicts
+      float* stage = reinterpret_cast<float*>(tiles) + (size_t)q * 32 * PITCH;
+      const bool split = gridDim.z > 1;
+      const int N = args.N;
+      const size_t plane = (size_t)args.T * N;
+#pragma unroll 1
+      for (int cb = 0; cb < FEATS; cb += 128) {
+        if (f0 + cb >= N) break;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128 && cb + c0 < FEATS; c0 += 16) {
+          const int f = f0 + cb + c0;
+          if (f >= N) break;
+          uint32_t r0[16], r1[16];
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb + c0);
+          tmem_ld16(taddr, r0);
+          if (GATED) tmem_ld16(taddr + FEATS, r1);
+          tmem_ld_wait();
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float a = __uint_as_float(r0[j]);
+            if (!split && args.bias && f + j < N) a += args.bias[f + j];
+            if (GATED) {
+              float u = __uint_as_float(r1[j]);
+              if (args.bias && f + j < N) u += args.bias[N + f + j];
+              a = __fdividef(a, 1.0f + __expf(-a)) * u;
+            }
+            v[j] = a;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(stage + lane * PITCH + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        }
+        __syncwarp();
+        const int f = f0 + cb + lane * 4;  // this lane's four features of every row
+        const bool f_ok = f < N && cb + lane * 4 < FEATS;  // N % 4 == 0: a group is inside or outside as a whole
+        const int rows = min(32, args.T - (t0 + q * 32));
+        if (f_ok) {
+          if (split) {
+            float* p = args.partial + (size_t)blockIdx.z * plane + (size_t)(t0 + q * 32) * N + f;
+#pragma unroll 4
+            for (int r = 0; r < rows; ++r) *reinterpret_cast<float4*>(p + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
+          } else if (EPI == EPI_RESIDUAL) {
+            float* o = (float*)args.out + (size_t)(t0 + q * 32) * N + f;
+#pragma unroll 1
+            for (int rb = 0; rb < 32; rb += 16) {  // sixteen rows at a time: all their loads in flight, then the stores
+              float4 b[16];
+#pragma unroll
+              for (int r = 0; r < 16; ++r)
+                if (rb + r < rows) b[r] = *reinterpret_cast<float4*>(o + (size_t)(rb + r) * N);
+#pragma unroll
+              for (int r = 0; r < 16; ++r)
+                if (rb + r < rows) {
+                  const float4 a = *reinterpret_cast<const float4*>(stage + (rb + r) * PITCH + lane * 4);
+                  *reinterpret_cast<float4*>(o + (size_t)(rb + r) * N) = make_float4(b[r].x + a.x, b[r].y + a.y, b[r].z + a.z, b[r].w + a.w);
+                }
+            }
+          } else if (args.out_bf16) {
+            bf16* o = (bf16*)args.out + (size_t)(t0 + q * 32) * N + f;
+#pragma unroll 4
+            for (int r = 0; r < rows; ++r) {
+              const float4 a = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
+              __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+              *reinterpret_cast<uint2*>(o + (size_t)r * N) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
+          } else {
+            float* o = (float*)args.out + (size_t)(t0 + q * 32) * N + f;
+#pragma unroll 4
+            for (int r = 0; r < rows; ++r) *reinterpret_cast<float4*>(o + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
+          }
+        }
+        __syncwarp();
+      }
+    } else if (ok && t0 + q * 32 < args.T) {
+      // widths that are no multiple of 4 (or gated partial sums): element-wise, straight from the registers
       const bool split = gridDim.z > 1;
       const bool t_ok = t < args.T;
       const int N = args.N;
@@ -486,12 +575,18 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       }
     }
   }
+#ifdef ALOFA_GEMM_TIMING
+  if (probe && warp == 2 && lane == 0) args.stamps[4] = clock64();
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+#ifdef ALOFA_GEMM_TIMING
+  if (probe && warp == 2 && lane == 0) args.stamps[5] = clock64();
+#endif
   if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
 }
 
