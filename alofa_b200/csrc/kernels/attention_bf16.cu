@@ -46,7 +46,7 @@ struct AttnParams {
   const int* block_table;  // [R, max_blocks]
   float* partial_o;      // split mode: [splits, T * nh, HD]
   float* partial_ml;     // split mode: [splits, T * nh, 2]
-  int max_blocks, page_size, nh, nkv, window, split_keys, n_rows_total, table_entries;
+  int max_blocks, page_size, nh, nkv, window, split_keys, n_splits, n_rows_total, table_entries;
   float scale_log2;      // scale * log2(e)
 };
 
@@ -158,7 +158,9 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
   const int kv_len = p.kv_len[seq];
   const int pos0 = kv_len - q_len;
   const int n_rows = q_len * g;
-  const int tile = SPLIT ? 0 : blockIdx.x;
+  // split mode: blockIdx.x = tile * n_splits + split (decode tokens have one tile)
+  const int tile = SPLIT ? (int)blockIdx.x / p.n_splits : (int)blockIdx.x;
+  const int split = SPLIT ? (int)blockIdx.x % p.n_splits : 0;
   const int row0 = tile * BLOCK_M;
   if (row0 >= n_rows) return;
   const int last_row = min(n_rows, row0 + BLOCK_M) - 1;
@@ -167,8 +169,8 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
   int k_lo = 0;
   if (p.window > 0) k_lo = max(0, pos0 + t_first - p.window + 1);
   if (SPLIT) {
-    k_lo = max(k_lo, (int)blockIdx.x * p.split_keys);
-    k_hi = min(k_hi, ((int)blockIdx.x + 1) * p.split_keys - 1);
+    k_lo = max(k_lo, split * p.split_keys);
+    k_hi = min(k_hi, (split + 1) * p.split_keys - 1);
     if (k_lo > k_hi) return;
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -332,12 +334,12 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
     const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
     const size_t out_row = (size_t)(row_begin + row / g) * p.nh + kvh * g + row % g;
     if (SPLIT) {
-      float* po = p.partial_o + ((size_t)blockIdx.x * p.n_rows_total + out_row) * HD;
+      float* po = p.partial_o + ((size_t)split * p.n_rows_total + out_row) * HD;
 #pragma unroll
       for (int d = 0; d < DTILES; ++d)
         *reinterpret_cast<float2*>(po + d * 8 + (lane & 3) * 2) = make_float2(o[d][half * 2], o[d][half * 2 + 1]);
       if ((lane & 3) == 0) {
-        float* ml = p.partial_ml + ((size_t)blockIdx.x * p.n_rows_total + out_row) * 2;
+        float* ml = p.partial_ml + ((size_t)split * p.n_rows_total + out_row) * 2;
         ml[0] = (m == -INFINITY) ? -INFINITY : m * p.scale_log2;
         ml[1] = l;
       }
@@ -589,13 +591,12 @@ static int launch_decode(const AttnParams& p, int n_splits, int nkv, int n_seqs,
 }
 
 // Merge the splits of every (token, head) row in split order.  One block of HD
-// threads per row; rows are decode tokens (one query position per request).
+// threads per row; a row's splits are those its visible keys fall into.
 __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                                         const int* __restrict__ kv_len, int nh, int window, int split_keys, int n_rows_total) {
-  const int row = blockIdx.x;       // token * nh + head; one token per request
+                                         const int* __restrict__ positions, int nh, int window, int split_keys, int n_rows_total) {
+  const int row = blockIdx.x;       // token * nh + head
   pdl_begin();
-  const int seq = row / nh;
-  const int P = kv_len[seq] - 1;
+  const int P = positions[row / nh];
   int k_lo = 0;
   if (window > 0) k_lo = max(0, P - window + 1);
   const int s_lo = k_lo / split_keys, s_hi = P / split_keys;
@@ -605,7 +606,7 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __
   const int d = threadIdx.x;
   for (int s = s_lo; s <= s_hi; ++s) {
     const float* ml = partial_ml + ((size_t)s * n_rows_total + row) * 2;
-    const float w = (ml[0] == -INFINITY) ? 0.f : exp2f(ml[0] - m);
+    const float w = (ml[0] == -INFINITY) ? 0.f : fast_exp2(ml[0] - m);
     l += ml[1] * w;
     acc += partial_o[((size_t)s * n_rows_total + row) * HD + d] * w;
   }
@@ -621,16 +622,18 @@ ALOFA_API int alofa_attention_head_dim() { return HD; }
 
 // max_kv_len: the most keys any request of this step has (sizes the shared copy of
 // block-table entries).  tiles: query tiles of the longest request = ceil(max_q_len * g / 64).  n_splits > 0
-// selects split mode (every request has exactly one token in this step and
-// g <= 64); partial_o / partial_ml must then hold n_splits planes.
-ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len,
+// selects split mode: the keys of a request (decode tokens) or of every query tile
+// (prompt portions) are spread over n_splits CTAs of split_keys keys each and merged by
+// attention_combine_kernel; partial_o / partial_ml must then hold n_splits planes.
+ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len, const int* positions,
                                    const int* block_table, int max_blocks, int page_size, int n_seqs, int n_tokens, int tiles, int nh, int nkv,
                                    int window, float scale, int n_splits, int split_keys, float* partial_o, float* partial_ml,
                                    int max_kv_len, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || tiles <= 0) return ALOFA_ERR_ARGUMENT;
-  if (n_splits > 0 && (nh / nkv > BLOCK_M || split_keys <= 0 || split_keys % BLOCK_N != 0 || !partial_o || !partial_ml || n_seqs != n_tokens))
-    return ALOFA_ERR_ARGUMENT;
+  if (n_splits > 0 && (split_keys <= 0 || split_keys % BLOCK_N != 0 || !partial_o || !partial_ml || !positions)) return ALOFA_ERR_ARGUMENT;
+  const bool decode_only = n_seqs == n_tokens;
+  if (n_splits > 0 && decode_only && nh / nkv > BLOCK_M) return ALOFA_ERR_ARGUMENT;
   AttnParams p;
   p.out = (bf16*)out;
   p.q = (const bf16*)q;
@@ -647,35 +650,45 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
   p.nkv = nkv;
   p.window = window;
   p.split_keys = split_keys;
+  p.n_splits = n_splits > 0 ? n_splits : 1;
   p.n_rows_total = n_tokens * nh;
   p.scale_log2 = scale * 1.4426950408889634f;
   // entries of a block table one CTA may touch: a split's keys, or up to the longest request
   const int reach = n_splits > 0 ? split_keys : max_kv_len;
   p.table_entries = reach / page_size + 2;
-  const size_t smem = attention_smem_bytes(n_splits > 0 ? SPLIT_STAGES : PREFILL_STAGES, p.table_entries);
+  const size_t smem = attention_smem_bytes((n_splits > 0 && decode_only) ? SPLIT_STAGES : PREFILL_STAGES, p.table_entries);
   if (smem > 200 * 1024) return ALOFA_ERR_ARGUMENT;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_bf16_kernel<false, PREFILL_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              200 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(attention_bf16_kernel<true, SPLIT_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_bf16_kernel<true, PREFILL_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              200 * 1024) != cudaSuccess)
       return ALOFA_ERR_LAUNCH;
     prefer_max_shared(attention_bf16_kernel<false, PREFILL_STAGES>);
     prefer_max_shared(attention_bf16_kernel<true, SPLIT_STAGES>);
+    prefer_max_shared(attention_bf16_kernel<true, PREFILL_STAGES>);
     prefer_max_shared(attention_combine_kernel);
     configured = true;
   }
-  if (n_splits > 0 && nh / nkv <= 16 && (split_keys == 4 * BLOCK_N || split_keys == 2 * BLOCK_N)) {
+  if (n_splits > 0 && decode_only && nh / nkv <= 16 && (split_keys == 4 * BLOCK_N || split_keys == 2 * BLOCK_N)) {
     // decode tokens of small head groups: the key blocks of a split side by side on the warps
     const int rc = split_keys == 4 * BLOCK_N ? launch_decode<4>(p, n_splits, nkv, n_seqs, stream) : launch_decode<2>(p, n_splits, nkv, n_seqs, stream);
     if (rc != ALOFA_OK) return rc;
     if (n_splits > 1)
-      launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
+      launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);
+  } else if (n_splits > 0 && !decode_only) {
+    // prompt portions: every query tile's keys split over n_splits CTAs, so that the tiles
+    // at the end of a long prompt do not set the pace
+    launch_dep(attention_bf16_kernel<true, PREFILL_STAGES>, dim3(tiles * n_splits, nkv, n_seqs), 128, smem, stream, p);
+    if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);
   } else if (n_splits > 0) {
     launch_dep(attention_bf16_kernel<true, SPLIT_STAGES>, dim3(n_splits, nkv, n_seqs), 128, smem, stream, p);
     if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
-    launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, kv_len, nh, window, split_keys, p.n_rows_total);
+    launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);
   } else {
     launch_dep(attention_bf16_kernel<false, PREFILL_STAGES>, dim3(tiles, nkv, n_seqs), 128, smem, stream, p);
   }

@@ -86,7 +86,7 @@ def _attention(head_dim: int):
     if lib is None:
         lib = load_library(f"alofa_attention_hd{head_dim}", ["kernels/attention_bf16.cu"], defines={"HEAD_DIM": head_dim})
         lib.alofa_attention_bf16.restype = _I
-        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P]
+        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P]
         _libs[key] = lib
     return lib
 
@@ -288,18 +288,19 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
     return True
 
 
-def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, block_table, page_size, n_seqs, max_q_len, nh, nkv, hd, window, scale,
+def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_table, page_size, n_seqs, max_q_len, nh, nkv, hd, window, scale,
                    n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0) -> None:
     """Causal GQA over the paged bf16 cache for a step's requests; with
-    ``n_splits`` > 0 (decode tokens only) the keys of each request are split
-    over several CTAs and merged."""
+    ``n_splits`` > 0 the keys of each request (decode tokens) or of each query
+    tile (prompt portions) are split over several CTAs and merged."""
     n = q.shape[0]
     bf = torch.bfloat16
     g = nh // nkv
     tiles = -(-(max_q_len * g) // 64)
     rc = _attention(hd).alofa_attention_bf16(
         _dev(out, "out", bf), _dev(q, "q", bf), _dev(k_cache, "k_cache", bf), _dev(v_cache, "v_cache", bf),
-        _dev(q_start, "q_start", torch.int32), _dev(kv_len, "kv_len", torch.int32), _dev(block_table, "block_table", torch.int32),
+        _dev(q_start, "q_start", torch.int32), _dev(kv_len, "kv_len", torch.int32), _dev(positions, "positions", torch.int32),
+        _dev(block_table, "block_table", torch.int32),
         block_table.shape[1], page_size, n_seqs, n, tiles, nh, nkv, int(window or 0), float(scale), n_splits, split_keys,
         _dev(partial_o, "partial_o", torch.float32) if partial_o is not None else None,
         _dev(partial_ml, "partial_ml", torch.float32) if partial_ml is not None else None,

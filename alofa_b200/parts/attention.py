@@ -114,6 +114,10 @@ class GQAttention(Part):
             ctx.set_pending(h, owed)
 
     SPLIT_KEYS = 256  # keys per CTA when a decode-only step splits each request's keys (four 64-key blocks, one per warp)
+    # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.
+    # Measured at 2,048-token prompts the round trip of the partial sums costs more than the
+    # long tiles' tail saves (4.9 ms against 4.5 ms for the step), so it is off.
+    PROMPT_SPLIT_KEYS = 0
 
     def attend(self, ctx, out, q, cache, group):
         """Attention of the step's rows over the cache: the tensor-core kernel
@@ -122,12 +126,17 @@ class GQAttention(Part):
             splits, po, pml = 0, None, None
             longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
             per_split = self.SPLIT_KEYS
+            if not ctx.decode_only:
+                per_split = self.PROMPT_SPLIT_KEYS or (1 << 30)
             if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):
                 splits = max(1, -(-longest // per_split))
+            elif not ctx.decode_only and longest > per_split:
+                splits = -(-longest // per_split)
+            if splits:
                 po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
                 pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
             ops.attention_bf16(
-                out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
+                out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, ctx.positions, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
                 self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest,
             )
             return

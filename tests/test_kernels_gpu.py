@@ -243,7 +243,7 @@ def attention_case(ops, dtype, hd, nh, nkv, lens, q_lens, page, window, rng, cra
             n_splits = -(-max(lens) // split_keys)
             po = torch.empty(n_splits, len(q_rows) * nh, hd, device="cuda")
             pml = torch.empty(n_splits, len(q_rows) * nh, 2, device="cuda")
-        ops.attention_bf16(out, q, k_cache, v_cache, dev(q_start), dev(np.array(lens, dtype=np.int32)), table, page, len(lens), max(q_lens),
+        ops.attention_bf16(out, q, k_cache, v_cache, dev(q_start), dev(np.array(lens, dtype=np.int32)), dev(np.array(positions, dtype=np.int32)), table, page, len(lens), max(q_lens),
                            nh, nkv, hd, window, 1.0 / np.sqrt(hd), n_splits, split_keys, po, pml)
         return out.float().cpu().numpy().astype(np.float64), np.stack(want)
     ops.paged_attention_generic(out, q, k_cache, v_cache, dev(np.array(positions, dtype=np.int32)), dev(np.array(seq_of, dtype=np.int32)),
@@ -327,6 +327,17 @@ def test_attention_bf16_split_keys(ops, hd, nh, nkv):
     # a single split writes the output itself
     got, want = attention_case(ops, BF16, hd, nh, nkv, lens=[200, 7], q_lens=[1, 1], page=16, window=None, rng=np.random.default_rng(1), fast=True, split_keys=256)
     assert_close(got, want, TOL[BF16], "one split")
+
+
+def test_attention_bf16_prompt_portions_with_split_keys(ops):
+    """Prompt portions (and decode tokens beside them) whose query tiles split
+    their keys over several CTAs."""
+    for hd, nh, nkv in ((64, 14, 2), (32, 3, 1), (128, 8, 8)):
+        for window in (None, 200):
+            rng = np.random.default_rng(hd)
+            lens, q_lens = [700, 37, 300, 129, 1, 450], [300, 37, 2, 1, 1, 450]
+            got, want = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=q_lens, page=16, window=window, rng=rng, fast=True, split_keys=192)
+            assert_close(got, want, TOL[BF16], f"prompt split hd={hd} window={window}")
 
 
 def test_attention_bf16_far_key_and_window_edge(ops):
