@@ -18,7 +18,6 @@ import torch
 
 from ..errors import AlofaError
 from ..parts.base import PagedKV, SlotState
-from .manager import GroupSpec
 
 
 @dataclass

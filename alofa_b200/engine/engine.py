@@ -19,8 +19,6 @@ from collections import OrderedDict
 from dataclasses import dataclass, field, replace
 from typing import Optional, Sequence
 
-import torch
-
 from ..config.engine_config import EngineConfig
 from ..errors import AlofaError
 from ..sampling.params import SamplingParams

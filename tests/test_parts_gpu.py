@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import plain_qwen2 as plain
-from gpu_util import assert_close, dev, rounded
+from gpu_util import assert_close, rounded
 
 pytestmark = pytest.mark.gpu
 
