@@ -22,6 +22,7 @@
 // library is built per head size.  Formulas: src/alofa/kernels/cpu/scalar.mojo:392-470,
 // paged addressing src/alofa/kernels/cpu/paged.mojo:249-336.
 #include "common.cuh"
+#include "tma.cuh"
 
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
@@ -48,6 +49,7 @@ struct AttnParams {
   float* partial_ml;     // split mode: [splits, T * nh, 2]
   int max_blocks, page_size, nh, nkv, window, split_keys, n_splits, n_rows_total, table_entries;
   float scale_log2;      // scale * log2(e)
+  int* status;           // set to 2 when a wait on a bulk copy gave up (may be null)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t smem, const void* gptr, bool pred) {
@@ -368,8 +370,22 @@ struct RowState {
   float o[DTILES][4];
 };
 
+// Shared-memory address of the 16-byte chunk at (row, col) of a 64-key tile.
+// Padded layout: rows of ROW elements (the cp.async path).  Swizzled layout (what a
+// TMA load with 128-byte swizzle leaves): sub-tiles of 64 dims, rows of 128 bytes,
+// the chunk index XOR-ed with the low bits of the row.
+template <bool SWIZZLED>
+__device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int col) {
+  if (SWIZZLED) {
+    const int sub = col >> 6, chunk = (col & 63) >> 3;
+    return base + sub * (BLOCK_N * 128) + row * 128 + ((chunk ^ (row & 7)) << 4);
+  }
+  return base + (row * ROW + col) * 2;
+}
+
 // One warp: 16 query rows against the 64 keys of one block held in shared tiles.
-__device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[KSTEPS][4], const bf16* kt, const bf16* vt, int j0, int lane,
+template <bool SWIZZLED>
+__device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[KSTEPS][4], uint32_t kt, uint32_t vt, int j0, int lane,
                                              int pos, int k_lo, int k_hi, int window, float scale_log2) {
   float s[BLOCK_N / 8][4];
 #pragma unroll
@@ -379,8 +395,7 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
 #pragma unroll
     for (int n2 = 0; n2 < BLOCK_N / 16; ++n2) {
       uint32_t kf[4];
-      const bf16* src = kt + (n2 * 16 + (lane & 7) + ((lane >> 4) << 3)) * ROW + ks * 16 + ((lane >> 3) & 1) * 8;
-      ldmatrix_x4(kf, (uint32_t)__cvta_generic_to_shared(src));
+      ldmatrix_x4(kf, tile_addr<SWIZZLED>(kt, n2 * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 16 + ((lane >> 3) & 1) * 8));
       mma_16816(s[2 * n2], qf[ks], kf[0], kf[1]);
       mma_16816(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
     }
@@ -439,8 +454,7 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
 #pragma unroll
     for (int d2 = 0; d2 < HD / 16; ++d2) {
       uint32_t vf[4];
-      const bf16* src = vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ROW + d2 * 16 + (lane >> 4) * 8;
-      ldmatrix_x4_trans(vf, (uint32_t)__cvta_generic_to_shared(src));
+      ldmatrix_x4_trans(vf, tile_addr<SWIZZLED>(vt, kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, d2 * 16 + (lane >> 4) * 8));
       mma_16816(st.o[2 * d2], pf[kk], vf[0], vf[1]);
       mma_16816(st.o[2 * d2 + 1], pf[kk], vf[2], vf[3]);
     }
@@ -449,18 +463,33 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
 
 constexpr int MERGE_ROW = HD + 4;  // floats per merged row in shared memory
 
-// WARPS warps, one 64-key block each: a split is WARPS * 64 keys.
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const AttnParams p) {
+// WARPS warps, one 64-key block each: a split is WARPS * 64 keys.  With TMA (pages
+// that hold whole 64-key blocks, head size 64 or 128) a warp's block arrives by two
+// bulk tensor copies - keys and values, 128-byte swizzled - issued by one lane and
+// awaited on an mbarrier; else by 16-byte cp.async copies into padded tiles.
+constexpr int TILE_BYTES_TMA = BLOCK_N * HD * 2;  // one dense tile
+
+template <int WARPS, bool TMA>
+__global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const AttnParams p, const __grid_constant__ CUtensorMap map_k,
+                                                                      const __grid_constant__ CUtensorMap map_v) {
   constexpr int DECODE_SPLIT_KEYS = WARPS * BLOCK_N;
   constexpr int THREADS = WARPS * 32;
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);       // [16][ROW]
-  bf16* k_tiles = q_tile + 16 * ROW;                      // [WARPS][64][ROW]
-  bf16* v_tiles = k_tiles + WARPS * BLOCK_N * ROW;        // [WARPS][64][ROW]
+  constexpr int TILE_ELEMS = TMA ? BLOCK_N * HD : BLOCK_N * ROW;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* aligned = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  bf16* k_tiles = reinterpret_cast<bf16*>(aligned);       // [WARPS] tiles of 64 keys
+  bf16* v_tiles = k_tiles + WARPS * TILE_ELEMS;           // [WARPS] tiles of 64 keys
+  bf16* q_tile = v_tiles + WARPS * TILE_ELEMS;            // [16][ROW]
   // the merge buffers reuse the key tiles once every warp is done with them
   float* merge_o = reinterpret_cast<float*>(k_tiles);     // [WARPS][16][MERGE_ROW]
   float* merge_ml = merge_o + WARPS * 16 * MERGE_ROW;     // [WARPS][16][2]
+  __shared__ uint64_t tile_bar[WARPS];
+  __shared__ int abort_flag;
+  if (TMA && (threadIdx.x & 31) == 0) {
+    if (threadIdx.x == 0) abort_flag = 0;
+    mbar_init(&tile_bar[threadIdx.x >> 5], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
   pdl_begin();
 
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -484,9 +513,23 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   // this warp's block of keys
   const int j0 = (split * WARPS + warp) * BLOCK_N;
   const bool has_keys = j0 <= k_hi && j0 + BLOCK_N - 1 >= k_lo;
-  bf16* kt = k_tiles + warp * BLOCK_N * ROW;
-  bf16* vt = v_tiles + warp * BLOCK_N * ROW;
-  if (has_keys) {
+  bf16* kt = k_tiles + warp * TILE_ELEMS;
+  bf16* vt = v_tiles + warp * TILE_ELEMS;
+  if (TMA) {
+    if (lane == 0) {
+      if (has_keys) {
+        // the block lies inside one page: its 64 rows are consecutive cache slots
+        const int e = j0 / p.page_size;
+        const int row0 = p.block_table[(size_t)seq * p.max_blocks + e] * p.page_size + (j0 - e * p.page_size);
+        mbar_expect_tx(&tile_bar[warp], 2 * TILE_BYTES_TMA);
+#pragma unroll
+        for (int sub = 0; sub < HD / 64; ++sub) {
+          tma_load_2d(reinterpret_cast<uint8_t*>(kt) + sub * BLOCK_N * 128, &map_k, &tile_bar[warp], kvh * HD + sub * 64, row0);
+          tma_load_2d(reinterpret_cast<uint8_t*>(vt) + sub * BLOCK_N * 128, &map_v, &tile_bar[warp], kvh * HD + sub * 64, row0);
+        }
+      }
+    }
+  } else if (has_keys) {
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
     for (int idx = lane; idx < BLOCK_N * CHUNKS; idx += 32) {
       const int r = idx / CHUNKS, c = idx % CHUNKS;
@@ -504,24 +547,28 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   }
   cp_async_commit();
   cp_async_wait<0>();
-  __syncthreads();  // the query tile was copied by all threads
+  __syncthreads();  // the query tile was copied by all threads (and the barriers are initialised)
+  bool arrived = true;
+  if (TMA && has_keys) arrived = mbar_wait(&tile_bar[warp], 0, &abort_flag);
 
   RowState st;
   st.m_lo = st.m_hi = -INFINITY;
   st.l_lo = st.l_hi = 0.f;
 #pragma unroll
   for (int d = 0; d < DTILES; ++d) st.o[d][0] = st.o[d][1] = st.o[d][2] = st.o[d][3] = 0.f;
-  if (has_keys) {
+  if (has_keys && arrived) {
     uint32_t qf[KSTEPS][4];
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
       const bf16* src = q_tile + (lane & 15) * ROW + ks * 16 + (lane >> 4) * 8;
       ldmatrix_x4(qf[ks], (uint32_t)__cvta_generic_to_shared(src));
     }
-    attend_block(st, qf, kt, vt, j0, lane, pos, k_lo, k_hi, p.window, p.scale_log2);
+    attend_block<TMA>(st, qf, (uint32_t)__cvta_generic_to_shared(kt), (uint32_t)__cvta_generic_to_shared(vt), j0, lane, pos, k_lo, k_hi,
+                      p.window, p.scale_log2);
   }
   // ---- merge the warps in warp order ---------------------------------------------------
   __syncthreads();  // every warp is done with the key tiles the merge buffers overlay
+  if (TMA && threadIdx.x == 0 && abort_flag && p.status) atomicExch(p.status, 2);
   st.l_lo += __shfl_xor_sync(0xffffffffu, st.l_lo, 1);
   st.l_lo += __shfl_xor_sync(0xffffffffu, st.l_lo, 2);
   st.l_hi += __shfl_xor_sync(0xffffffffu, st.l_hi, 1);
@@ -571,22 +618,25 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   }
 }
 
-static size_t decode_smem_bytes(int warps) {
-  const size_t tiles = (size_t)(2 * warps * BLOCK_N) * ROW * sizeof(bf16);
+static size_t decode_smem_bytes(int warps, bool tma) {
+  const size_t tile = tma ? (size_t)BLOCK_N * HD * sizeof(bf16) : (size_t)BLOCK_N * ROW * sizeof(bf16);
+  const size_t tiles = 2 * warps * tile;
   const size_t merge = (size_t)warps * 16 * MERGE_ROW * sizeof(float) + (size_t)warps * 32 * sizeof(float);
-  return (size_t)16 * ROW * sizeof(bf16) + (tiles > merge ? tiles : merge);
+  return 1024 + (tiles > merge ? tiles : merge) + (size_t)16 * ROW * sizeof(bf16);
 }
 
-template <int WARPS>
-static int launch_decode(const AttnParams& p, int n_splits, int nkv, int n_seqs, cudaStream_t stream) {
+template <int WARPS, bool TMA>
+static int launch_decode(const AttnParams& p, const CUtensorMap& map_k, const CUtensorMap& map_v, int n_splits, int nkv, int n_seqs,
+                         cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_decode_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem_bytes(WARPS)) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_decode_kernel<WARPS, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)decode_smem_bytes(WARPS, TMA)) != cudaSuccess)
       return ALOFA_ERR_LAUNCH;
-    prefer_max_shared(attention_decode_kernel<WARPS>);
+    prefer_max_shared(attention_decode_kernel<WARPS, TMA>);
     configured = true;
   }
-  launch_dep(attention_decode_kernel<WARPS>, dim3(n_splits, nkv, n_seqs), WARPS * 32, decode_smem_bytes(WARPS), stream, p);
+  launch_dep(attention_decode_kernel<WARPS, TMA>, dim3(n_splits, nkv, n_seqs), WARPS * 32, decode_smem_bytes(WARPS, TMA), stream, p, map_k, map_v);
   return cudaGetLastError() == cudaSuccess ? ALOFA_OK : ALOFA_ERR_LAUNCH;
 }
 
@@ -620,6 +670,7 @@ static size_t attention_smem_bytes(int stages, int table_entries) {
 
 ALOFA_API int alofa_attention_head_dim() { return HD; }
 
+// cache_slots: rows of k_cache / v_cache (token slots), for the tensor maps.
 // max_kv_len: the most keys any request of this step has (sizes the shared copy of
 // block-table entries).  tiles: query tiles of the longest request = ceil(max_q_len * g / 64).  n_splits > 0
 // selects split mode: the keys of a request (decode tokens) or of every query tile
@@ -628,7 +679,7 @@ ALOFA_API int alofa_attention_head_dim() { return HD; }
 ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len, const int* positions,
                                    const int* block_table, int max_blocks, int page_size, int n_seqs, int n_tokens, int tiles, int nh, int nkv,
                                    int window, float scale, int n_splits, int split_keys, float* partial_o, float* partial_ml,
-                                   int max_kv_len, cudaStream_t stream) {
+                                   int max_kv_len, long long cache_slots, int* status, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || tiles <= 0) return ALOFA_ERR_ARGUMENT;
   if (n_splits > 0 && (split_keys <= 0 || split_keys % BLOCK_N != 0 || !partial_o || !partial_ml || !positions)) return ALOFA_ERR_ARGUMENT;
@@ -637,6 +688,7 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
   AttnParams p;
   p.out = (bf16*)out;
   p.q = (const bf16*)q;
+  p.status = status;
   p.k_cache = (const bf16*)k_cache;
   p.v_cache = (const bf16*)v_cache;
   p.q_start = q_start;
@@ -675,7 +727,21 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
   }
   if (n_splits > 0 && decode_only && nh / nkv <= 16 && (split_keys == 4 * BLOCK_N || split_keys == 2 * BLOCK_N)) {
     // decode tokens of small head groups: the key blocks of a split side by side on the warps
-    const int rc = split_keys == 4 * BLOCK_N ? launch_decode<4>(p, n_splits, nkv, n_seqs, stream) : launch_decode<2>(p, n_splits, nkv, n_seqs, stream);
+    // pages that hold whole key blocks and rows of 128 or 256 bytes: bulk tensor copies
+    CUtensorMap map_k, map_v;
+    bool tma = (HD == 64 || HD == 128) && page_size % BLOCK_N == 0 && cache_slots > 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0;
+    if (tma)
+      tma = make_tensor_map_bf16(&map_k, k_cache, (uint64_t)cache_slots, (uint64_t)nkv * HD, BLOCK_N, 64) &&
+            make_tensor_map_bf16(&map_v, v_cache, (uint64_t)cache_slots, (uint64_t)nkv * HD, BLOCK_N, 64);
+    if (!tma) {
+      memset(&map_k, 0, sizeof(map_k));
+      memset(&map_v, 0, sizeof(map_v));
+    }
+    int rc;
+    if (split_keys == 4 * BLOCK_N)
+      rc = tma ? launch_decode<4, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<4, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
+    else
+      rc = tma ? launch_decode<2, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<2, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
     if (rc != ALOFA_OK) return rc;
     if (n_splits > 1)
       launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);

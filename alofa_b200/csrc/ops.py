@@ -86,7 +86,7 @@ def _attention(head_dim: int):
     if lib is None:
         lib = load_library(f"alofa_attention_hd{head_dim}", ["kernels/attention_bf16.cu"], defines={"HEAD_DIM": head_dim})
         lib.alofa_attention_bf16.restype = _I
-        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P]
+        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _P]
         _libs[key] = lib
     return lib
 
@@ -289,7 +289,7 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
 
 
 def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_table, page_size, n_seqs, max_q_len, nh, nkv, hd, window, scale,
-                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0) -> None:
+                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0, status=None) -> None:
     """Causal GQA over the paged bf16 cache for a step's requests; with
     ``n_splits`` > 0 the keys of each request (decode tokens) or of each query
     tile (prompt portions) are split over several CTAs and merged."""
@@ -304,7 +304,8 @@ def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_t
         block_table.shape[1], page_size, n_seqs, n, tiles, nh, nkv, int(window or 0), float(scale), n_splits, split_keys,
         _dev(partial_o, "partial_o", torch.float32) if partial_o is not None else None,
         _dev(partial_ml, "partial_ml", torch.float32) if partial_ml is not None else None,
-        int(max_kv_len) if max_kv_len else block_table.shape[1] * page_size, _stream(),
+        int(max_kv_len) if max_kv_len else block_table.shape[1] * page_size, k_cache.shape[0],
+        _dev(status, "status", torch.int32) if status is not None else None, _stream(),
     )
     _done(rc, "attention_bf16", f"hd={hd} nh={nh} nkv={nkv} splits={n_splits}")
     if n_splits > 0:

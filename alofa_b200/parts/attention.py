@@ -137,7 +137,7 @@ class GQAttention(Part):
                 pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
             ops.attention_bf16(
                 out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, ctx.positions, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
-                self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest,
+                self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest, ctx.status,
             )
             return
         ops.paged_attention_generic(
