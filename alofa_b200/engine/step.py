@@ -17,6 +17,7 @@ same layout and address every time, so a replay only needs the new metadata."""
 from __future__ import annotations
 
 from dataclasses import dataclass
+import os
 from typing import Optional, Sequence
 
 import numpy as np
@@ -26,9 +27,10 @@ from ..cache.manager import CacheManager, GroupSpec
 from ..cache.storage import CacheStorage, group_windows
 from ..csrc import ops
 from ..errors import AlofaError
-from ..parts.base import PagedKV
+from ..parts.base import Ineligible, PagedKV
 from ..parts.model import Model
 from .context import GroupView, Layout, StepContext
+from .program import DecodeProgram
 
 
 @dataclass
@@ -49,6 +51,7 @@ class DecodeGraph:
     logits: torch.Tensor
     tokens: torch.Tensor
     kernels: int
+    program: Optional[DecodeProgram] = None  # the step as one resident kernel, when the model and the sizes allow
 
 
 class StepRunner:
@@ -81,6 +84,10 @@ class StepRunner:
         self._layouts = {}
         self.cuda_graphs = cuda_graphs and on_gpu and model.graph_safe()
         self._graphs = {}
+        # Small decode steps as one resident kernel: ALOFA_DECODE_PROGRAM=1.  Off unless asked for:
+        # measured at the benchmark's sizes, a layer takes longer in the resident kernel (barriers over
+        # the grid and operand loads that cannot start before them) than as ten dependent launches.
+        self.decode_programs = self.cuda_graphs and os.environ.get("ALOFA_DECODE_PROGRAM", "0") == "1"
 
     # -- requests -----------------------------------------------------------
     def admit(self, request_id: int) -> int:
@@ -202,16 +209,37 @@ class StepRunner:
         is first run once outright (its cache writes are the same ones the
         replay repeats), which also loads every kernel before recording."""
         ctx.capturing = True
-        self.model.forward(ctx, self.storage.caches)
+        program = self._program(ctx)
+        if program is not None:
+            program.run()
+        else:
+            self.model.forward(ctx, self.storage.caches)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
         with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx, self.storage.caches)
+            if program is not None:
+                program.run()
+                logits = program.logits
+            else:
+                logits = self.model.forward(ctx, self.storage.caches)
             tokens = self._sample(ctx, logits, True)  # a replay may meet rows of any temperature
-        entry = DecodeGraph(graph, logits, tokens, ops.launch_count() - before)
+        entry = DecodeGraph(graph, logits, tokens, ops.launch_count() - before, program)
         self._graphs[ctx.n_seqs] = entry
         return entry
+
+    def _program(self, ctx: StepContext) -> Optional[DecodeProgram]:
+        """The decode step of this batch size as a program for the resident
+        kernel, or None when a part or a size rules it out."""
+        if not self.decode_programs:
+            return None
+        try:
+            program = DecodeProgram(ctx)
+            program.logits = self.model.emit(program, ctx, self.storage.caches)
+            program.finish()
+        except Ineligible:
+            return None
+        return program
 
     def forward(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; logits (fp32, on the device) at the wanted places in

@@ -19,7 +19,7 @@ import torch
 
 from ..csrc import ops
 from ..errors import AlofaError
-from .base import PagedKV, Part, TensorSpec, as_float32_vector, build_part, register_part
+from .base import Ineligible, PagedKV, Part, TensorSpec, as_float32_vector, build_part, register_part
 from .linear import RESIDUAL, STORE, Linear
 
 
@@ -112,6 +112,19 @@ class GQAttention(Part):
         owed = self.out(h, attn, defer=True)
         if owed is not None:
             ctx.set_pending(h, owed)
+
+    def emit(self, prog, ctx, x, h, cache, writes=True):
+        group = ctx.groups[cache.group]
+        table, rot = self.position.rotary_table()
+        if getattr(self.position, "apply", None) is not None or rot != self.hd or group.page_size % 64:
+            raise Ineligible("the program rotates whole heads from a table and reads pages that hold whole 64-key blocks")
+        lin = self.qkv if writes else self.q_only
+        q = prog.buf((ctx.n_tokens, self.q_dim), torch.bfloat16)
+        prog.rope_store(x, lin.weight, lin.bias, q, cache.k, cache.v, group.slot_map, ctx.positions, table, self.nh, self.nkv, self.hd, writes)
+        attn = prog.buf((ctx.n_tokens, self.q_dim), torch.bfloat16)
+        prog.attention(attn, q, cache.k, cache.v, ctx.kv_len, group.block_table, group.page_size, self.nh, self.nkv, self.hd,
+                       self.window, self.scale, ctx.max_context)
+        prog.linear(prog.rows(attn), self.out.weight, self.out.bias, prog.RESIDUAL, h)
 
     SPLIT_KEYS = 256  # keys per CTA when a decode-only step splits each request's keys (four 64-key blocks, one per warp)
     # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.

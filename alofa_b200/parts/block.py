@@ -52,4 +52,9 @@ class PrenormResidual(Part):
         self.feed_forward.forward(ctx, x, h)
 
 
+    def emit(self, prog, ctx, h, cache, writes=True):
+        self.mixer.emit(prog, ctx, self.mixer_norm.emit(prog, ctx, h), h, cache, writes)
+        self.feed_forward.emit(prog, ctx, self.feed_forward_norm.emit(prog, ctx, h), h)
+
+
 register_part("block", "prenorm_residual", PrenormResidual)

@@ -34,6 +34,9 @@ class TokenEmbedding(Part):
     def forward(self, ctx, h):
         ops.embed_gather(h, self.weight, ctx.token_ids, ctx.status)
 
+    def emit(self, prog, ctx, h):
+        prog.embed(h, self.weight, ctx.token_ids)
+
 
 class LinearHead(Part):
     family = "head"
@@ -62,6 +65,11 @@ class LinearHead(Part):
     def forward(self, ctx, x):
         logits = ctx.buf((x.shape[0], self.vocab), torch.float32)
         self.linear(logits, x)
+        return logits
+
+    def emit(self, prog, ctx, x):
+        logits = prog.buf((ctx.n_tokens, self.vocab), torch.float32)
+        prog.linear(x, self.linear.weight, None, prog.STORE_F32, logits)
         return logits
 
 

@@ -46,4 +46,10 @@ class GatedMLP(Part):
             ctx.set_pending(h, owed)
 
 
+    def emit(self, prog, ctx, x, h):
+        act = prog.buf((ctx.n_tokens, self.inter), torch.bfloat16)
+        prog.linear(x, self.gate_up.weight, None, prog.GATED, act)
+        prog.linear(prog.rows(act), self.down.weight, None, prog.RESIDUAL, h)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)

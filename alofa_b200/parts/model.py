@@ -64,6 +64,14 @@ class Model:
         ctx.pending = None
         return self.head.forward(ctx, x)
 
+    def emit(self, prog, ctx, caches: dict) -> torch.Tensor:
+        """The same step written into a decode program; the logits buffer."""
+        h = prog.buf((ctx.n_tokens, self.spec.hidden_size), torch.float32)
+        self.embedding.emit(prog, ctx, h)
+        for i, (layer, cache) in enumerate(self.run):
+            self.layers[layer].emit(prog, ctx, h, caches.get(cache), writes=(cache == i))
+        return self.head.emit(prog, ctx, self.final_norm.emit(prog, ctx, h, ctx.logit_rows))
+
 
 def expected_tensors(spec: ModelSpec) -> dict:
     """name -> TensorSpec of everything the model reads from a checkpoint."""

@@ -43,4 +43,10 @@ class RMSNorm(Part):
         return out
 
 
+    def emit(self, prog, ctx, h, rows=None):
+        """The operand "rows of h, normalised" (every row: a program's steps
+        want the logits of all their tokens)."""
+        return prog.normed(h, self.weight, self.eps)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
