@@ -26,6 +26,7 @@ class EngineConfig:
     max_wait_ticks: int = 8  # ticks after which a waiting request jumps the queue
     seed: int = 1234  # default sampling seed
     cuda_graphs: bool = True  # replay decode-only steps as CUDA graphs
+    overlap_steps: bool = True  # launch a step before the host has read the tokens of the one before (they are fed on the device)
 
     def validate(self) -> None:
         def need(ok, what, detail):

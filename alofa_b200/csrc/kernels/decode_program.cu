@@ -84,6 +84,8 @@ struct alignas(128) Phase {
   const int* block_table;    // [T, max_blocks]
   const int* kv_len;         // [T]
   const int* ids;            // [T] token ids (embedding)
+  const int* token_src;      // [T] or null: -1 takes ids[t], r >= 0 takes fed[r]
+  const int* fed;            // tokens the step before sampled
   const float* rope_table;   // [max_pos, HD / 2, 2]
   float* partial_o;          // [n_splits, T * nh, HD]
   float* partial_ml;         // [n_splits, T * nh, 2]
@@ -141,7 +143,8 @@ __device__ void embed_phase(const Phase& ph, int* status) {
   float* h = reinterpret_cast<float*>(ph.out);
   const bf16* table = reinterpret_cast<const bf16*>(ph.w);
   for (int t = blockIdx.x; t < ph.T; t += gridDim.x) {
-    const int id = ph.ids[t];
+    int id = ph.ids[t];
+    if (ph.token_src && ph.token_src[t] >= 0) id = ph.fed[ph.token_src[t]];
     const bool ok = id >= 0 && id < ph.vocab;
     if (!ok && threadIdx.x == 0) atomicCAS(status, 0, 1);
     const bf16* row = table + (size_t)(ok ? id : 0) * ph.hidden;
@@ -829,7 +832,8 @@ ALOFA_API long long alofa_program_smem_bytes(const void* phases, int n) {
   return (long long)(most + 1024);
 }
 
-ALOFA_API int alofa_program_embed(void* phase, void* h, const void* table, const int* ids, int T, int hidden, int vocab) {
+ALOFA_API int alofa_program_embed(void* phase, void* h, const void* table, const int* ids, const int* token_src, const int* fed, int T,
+                                  int hidden, int vocab) {
   if (T <= 0 || T > 16) return ALOFA_ERR_ARGUMENT;
   Phase ph;
   memset(&ph, 0, sizeof(ph));
@@ -840,6 +844,8 @@ ALOFA_API int alofa_program_embed(void* phase, void* h, const void* table, const
   ph.out = h;
   ph.w = (const bf16*)table;
   ph.ids = ids;
+  ph.token_src = token_src;
+  ph.fed = fed;
   memcpy(phase, &ph, sizeof(ph));
   return ALOFA_OK;
 }

@@ -18,25 +18,29 @@
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_gather_kernel(float* __restrict__ out, const TW* __restrict__ table,
-                                    const int* __restrict__ ids, int hidden, int vocab, int* status) {
+                                    const int* __restrict__ ids, const int* __restrict__ src, const int* __restrict__ fed,
+                                    int hidden, int vocab, int* status) {
   pdl_begin();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  if (src && src[t] >= 0) id = fed[src[t]];  // the token an earlier step sampled, still on the device
   const bool ok = id >= 0 && id < vocab;
   if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
   const TW* row = table + (size_t)(ok ? id : 0) * hidden;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[(size_t)t * hidden + c] = ok ? to_f(row[c]) : 0.f;
 }
 
-ALOFA_API int alofa_embed_gather(void* out, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
-                                 int table_bf16, int* status, cudaStream_t stream) {
+// src (optional): per token, -1 to take ids[t], else the row of `fed` (tokens
+// sampled by the step before, on the device) that holds the id.
+ALOFA_API int alofa_embed_gather(void* out, const void* table, const int* ids, const int* src, const int* fed, int n_tokens, int hidden,
+                                 int vocab, int table_bf16, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
   ALOFA_PREFER_MAX_SHARED(embed_gather_kernel<bf16>);
   ALOFA_PREFER_MAX_SHARED(embed_gather_kernel<float>);
   if (table_bf16)
-    launch_dep(embed_gather_kernel<bf16>, n_tokens, 256, 0, stream, (float*)out, (const bf16*)table, ids, hidden, vocab, status);
+    launch_dep(embed_gather_kernel<bf16>, n_tokens, 256, 0, stream, (float*)out, (const bf16*)table, ids, src, fed, hidden, vocab, status);
   else
-    launch_dep(embed_gather_kernel<float>, n_tokens, 256, 0, stream, (float*)out, (const float*)table, ids, hidden, vocab, status);
+    launch_dep(embed_gather_kernel<float>, n_tokens, 256, 0, stream, (float*)out, (const float*)table, ids, src, fed, hidden, vocab, status);
   return launch_status();
 }
 

@@ -36,7 +36,7 @@ def _generic():
     if lib is None:
         lib = load_library("alofa_generic", ["kernels/generic.cu"])
         sigs = {
-            "alofa_embed_gather": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+            "alofa_embed_gather": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P],
             "alofa_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
             "alofa_gemm_generic": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_rope_store": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -113,7 +113,7 @@ def program_library(head_dim: int):
         lib.alofa_program_splits.restype = _I
         lib.alofa_program_splits.argtypes = [_I]
         lib.alofa_program_embed.restype = _I
-        lib.alofa_program_embed.argtypes = [_P, _P, _P, _P, _I, _I, _I]
+        lib.alofa_program_embed.argtypes = [_P, _P, _P, _P, _P, _P, _I, _I, _I]
         lib.alofa_program_linear.restype = _I
         lib.alofa_program_linear.argtypes = [_P, _I, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I]
         lib.alofa_program_attention.restype = _I
@@ -187,12 +187,16 @@ def _done(rc: int, what: str, detail: str = "") -> None:
     raise AlofaError("state", f"{what}: the CUDA runtime refused the launch", detail + " " + str(torch.cuda.get_device_name()))
 
 
-def embed_gather(out, table, ids, status=None) -> None:
-    """out[t] = table[ids[t]] widened to fp32; out [T, H] fp32."""
+def embed_gather(out, table, ids, status=None, src=None, fed=None) -> None:
+    """out[t] = table[ids[t]] widened to fp32; out [T, H] fp32.  With ``src``
+    and ``fed`` (int32 on the device) token t is ``fed[src[t]]`` where
+    ``src[t] >= 0``: a token the step before sampled, never seen by the host."""
     n, hidden = out.shape
     _done(
         _generic().alofa_embed_gather(
-            _dev(out, "out", torch.float32), _dev(table, "table"), _dev(ids, "ids", torch.int32), n, hidden, table.shape[0],
+            _dev(out, "out", torch.float32), _dev(table, "table"), _dev(ids, "ids", torch.int32),
+            _dev(src, "src", torch.int32) if src is not None else None, _dev(fed, "fed", torch.int32) if src is not None else None,
+            n, hidden, table.shape[0],
             _is_bf16(table, "table"), _dev(status, "status", torch.int32) if status is not None else None, _stream(),
         ),
         "embed_gather",

@@ -48,6 +48,7 @@ class Layout:
             at += (count + 3) // 4 * 4  # 16-byte aligned fields
 
         add("token_ids", n_tokens)
+        add("token_src", n_tokens)  # -1: the id above; r >= 0: row r of the tokens the step before sampled
         add("positions", n_tokens)
         add("seq_of_token", n_tokens)
         add("q_start", n_seqs + 1)
@@ -78,6 +79,8 @@ class StepContext:
             return dev_meta[at : at + count]
 
         self.token_ids = view("token_ids")
+        self.token_src = view("token_src")
+        self.fed_tokens = None  # int32 on the device: the tokens the step before sampled (set by the step runner)
         self.positions = view("positions")
         self.seq_of_token = view("seq_of_token")
         self.q_start = view("q_start")

@@ -16,6 +16,8 @@ from __future__ import annotations
 
 import time
 from collections import OrderedDict
+
+import torch
 from dataclasses import dataclass, field, replace
 from typing import Optional, Sequence
 
@@ -40,8 +42,29 @@ class Request:
     preemptions: int = 0
 
 
+@dataclass
+class InFlight:
+    """A step that was launched and whose tokens the host has not read yet."""
+
+    owners: list        # the requests whose next token each wanted row yields, in row order
+    epochs: list        # their preemption counts at launch: a request preempted since is skipped
+    row_of: dict        # request id -> row
+    host: "torch.Tensor"  # pinned; the tokens arrive here
+    event: "torch.cuda.Event"
+    finishing: list     # requests the scheduler ended with this step
+    kind: str
+    rows: int
+    t0: float
+
+
 class Engine:
-    """One model on one GPU, serving token-id requests."""
+    """One model on one GPU, serving token-id requests.
+
+    Steps overlap: when every request of a step samples by temperature alone,
+    the step is launched with its decoded tokens taken on the device from the
+    step before, and only then does the host read that earlier step's tokens.
+    The host's bookkeeping thus runs beside the GPU.  A request that meets a
+    stop token is seen one step late; the extra row it ran is dropped."""
 
     def __init__(self, model=None, dtype: Optional[str] = None, config: Optional[EngineConfig] = None, device=None, admission: str = "committed", trace_out=None, _loaded=None, **overrides):
         cfg = replace(config) if config is not None else EngineConfig()
@@ -79,6 +102,11 @@ class Engine:
         self._trace = open(trace_out, "w") if trace_out else None
         if self._trace:
             self._trace.write(format_config(self.sched_config) + "\n")
+        self._inflight: Optional[InFlight] = None
+        self._pinned = [torch.zeros(max(step_tokens, 1), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._pin_flip = 0
+        self.overlap = bool(cfg.overlap_steps) and self.runner.feeds_tokens
+        self.marks = []  # (time a step's tokens reached the host, kind, rows)
         self.counters = {"ticks": 0, "rows_run": 0, "prefill_rows": 0, "decode_rows": 0, "preempt_total": 0, "steps_prefill": 0, "steps_decode": 0}
         self.timings = {"prefill_ms": [], "decode_ms": []}
 
@@ -120,7 +148,7 @@ class Engine:
         self._cancels.append(request_id)
 
     def has_work(self) -> bool:
-        return bool(self._pending or self._live)
+        return bool(self._pending or self._live or self._inflight is not None)
 
     def pop_finished(self) -> list:
         """(request id, generated token ids) of requests that ended since the last call."""
@@ -154,23 +182,53 @@ class Engine:
             req.output.clear()
             req.rng = SplitMix64(req.params.seed)
             req.preemptions += 1
-        entries, owners = [], []
+        # who runs: decoded tokens first, then prompt portions
+        plan = []  # (request, prompt range or None, samples)
         for rid in act.decode:
-            req = self._live[rid]
-            entries.append(self._entry(req, [req.output[-1]], True))
-            owners.append(req)
+            req = self._live.get(rid)
+            if req is not None:
+                plan.append((req, None, True))
         for rid, start, end in act.prefill:
             req = self._live[rid]
             if req.slot is None:
                 req.slot = self.runner.admit(rid)
-            last = end == len(req.prompt)
-            entries.append(self._entry(req, req.prompt[start:end], last))
-            if last:
-                owners.append(req)
+            plan.append((req, (start, end), end == len(req.prompt)))
+        owners = [req for req, _, samples in plan if samples]
+        overlap = self.overlap and bool(plan) and all(req.params.plain() for req in owners)
+        if not overlap:
+            self._settle()  # every token is on the host before this step is put together
+        fl = self._inflight
+        entries = []
+        for req, span, samples in plan:
+            if span is not None:
+                entries.append(self._entry(req, req.prompt[span[0] : span[1]], samples))
+            elif req.done or req.id not in self._live:
+                owners.remove(req)  # ended by a stop token that settling has just shown
+            elif fl is not None and fl.row_of.get(req.id, -1) >= 0 and fl.epochs[fl.row_of[req.id]] == req.preemptions:
+                entry = self._entry(req, [0], True)
+                entry.feed = fl.row_of[req.id]  # its token is still on the device
+                entries.append(entry)
+            else:
+                entries.append(self._entry(req, [req.output[-1]], True))
         if entries:
-            self._run(entries, owners, bool(act.prefill))
-        for rid in act.finished:
-            self._finish(rid)
+            kind = "prefill" if act.prefill else "decode"
+            if overlap:
+                launched = self._launch(entries, owners, kind, list(act.finished))
+                for rid in act.finished:  # their pages come back now (the stream keeps later users behind this step) ...
+                    req = self._live.get(rid)
+                    if req is not None and req.slot is not None:
+                        self.runner.release(req.slot)
+                        req.slot = None
+                self._settle()
+                self._inflight = launched  # ... and their last tokens with this step's
+            else:
+                self._launch_and_wait(entries, owners, kind)
+                for rid in act.finished:
+                    self._finish(rid)
+        else:
+            self._settle()
+            for rid in act.finished:
+                self._finish(rid)
         return act
 
     def _entry(self, req: Request, tokens, sample: bool) -> StepEntry:
@@ -180,32 +238,71 @@ class Engine:
         u = req.rng.next_uniform() if p.temperature > 0.0 else 0.0
         return StepEntry(req.slot, tokens, (len(tokens) - 1,), p.temperature, u)
 
-    def _run(self, entries, owners, has_prefill: bool) -> None:
-        rows = sum(len(e.tokens) for e in entries)
+    def _launch(self, entries, owners, kind: str, finishing: list) -> InFlight:
+        """Run a step whose rows all sample by temperature alone; its tokens
+        are copied to pinned memory behind it and read by :meth:`_settle`."""
         t0 = time.perf_counter()
-        tokens = self._sample_step(entries, owners)
-        picked = tokens.tolist() if tokens is not None else []
-        ms = (time.perf_counter() - t0) * 1e3
-        self.counters["rows_run"] += rows
-        kind = "prefill" if has_prefill else "decode"
-        self.counters[f"steps_{kind}"] += 1
-        self.counters[f"{kind}_rows"] += rows
-        self.timings[f"{kind}_ms"].append(ms)
-        for req, tok in zip(owners, picked):
-            req.output.append(int(tok))
-            if int(tok) in req.params.stop_token_ids and len(req.output) < req.params.max_new_tokens:
-                self._ended.append(req.id)  # tells the scheduler on the next tick
-                self._finish(req.id)
+        rows = sum(len(e.tokens) for e in entries)
+        ctx, logits, tokens = self.runner.forward_sampled(entries)
+        host = self._pinned[self._pin_flip]
+        self._pin_flip ^= 1
+        n = len(owners)
+        if n:
+            host[:n].copy_(tokens[:n], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return InFlight(owners, [r.preemptions for r in owners], {r.id: i for i, r in enumerate(owners)}, host, event, finishing, kind, rows, t0)
 
-    def _sample_step(self, entries, owners):
+    def _settle(self) -> None:
+        """Read the tokens of the step in flight, if any, and act on them."""
+        fl = self._inflight
+        if fl is None:
+            return
+        self._inflight = None
+        fl.event.synchronize()
+        picked = fl.host[: len(fl.owners)].tolist()
+        self._account(fl.kind, fl.rows, fl.t0)
+        for req, epoch, tok in zip(fl.owners, fl.epochs, picked):
+            if req.done or req.preemptions != epoch or req.id not in self._live:
+                continue  # cancelled, preempted, or ended a step earlier: the row is dropped
+            self._take(req, int(tok))
+        for rid in fl.finishing:
+            self._finish(rid)
+
+    def _launch_and_wait(self, entries, owners, kind: str) -> None:
         from ..sampling.sampler import sample_rows
 
+        t0 = time.perf_counter()
+        rows = sum(len(e.tokens) for e in entries)
         ctx, logits, tokens = self.runner.forward_sampled(entries)
-        if logits is None:
-            return None
-        if not all(req.params.plain() for req in owners):
-            tokens = sample_rows(ctx, logits, owners)
-        return tokens.cpu()
+        picked = []
+        if logits is not None:
+            if not all(req.params.plain() for req in owners):
+                tokens = sample_rows(ctx, logits, owners)
+            picked = tokens.cpu().tolist()
+        self._account(kind, rows, t0)
+        for req, tok in zip(owners, picked):
+            self._take(req, int(tok))
+
+    def _take(self, req: Request, tok: int) -> None:
+        req.output.append(tok)
+        if tok in req.params.stop_token_ids and len(req.output) < req.params.max_new_tokens:
+            self._ended.append(req.id)  # tells the scheduler on the next tick
+            self._finish(req.id)
+
+    def _account(self, kind: str, rows: int, t0: float) -> None:
+        """Book a step whose tokens have just reached the host.  Its time runs
+        from its launch or, if later, from the arrival of the step before: the
+        times of overlapping steps then add up to the wall clock."""
+        now = time.perf_counter()
+        start = max(t0, self.marks[-1][0]) if self.marks else t0
+        self.counters["rows_run"] += rows
+        self.counters[f"steps_{kind}"] += 1
+        self.counters[f"{kind}_rows"] += rows
+        self.timings[f"{kind}_ms"].append((now - start) * 1e3)
+        self.marks.append((now, kind, rows))
+        if len(self.marks) > 4096:
+            del self.marks[:2048]
 
     def _finish(self, rid: int) -> None:
         req = self._live.pop(rid, None)

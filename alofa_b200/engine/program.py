@@ -71,11 +71,13 @@ class DecodeProgram:
             raise Ineligible("a plain operand is bfloat16")
         return Operand(x)
 
-    def embed(self, h, table, ids) -> None:
+    def embed(self, h, table, ids, src=None, fed=None) -> None:
+        """h[t] = table[ids[t]], or table[fed[src[t]]] where src[t] >= 0."""
         if table.dtype != torch.bfloat16:
             raise Ineligible("the embedding table is not bfloat16")
-        self._keep += [h, table, ids]
-        self._add(lambda lib, ph: lib.alofa_program_embed(ph, h.data_ptr(), table.data_ptr(), ids.data_ptr(), self.n, table.shape[1], table.shape[0]))
+        self._keep += [h, table, ids, src, fed]
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        self._add(lambda lib, ph: lib.alofa_program_embed(ph, h.data_ptr(), table.data_ptr(), ids.data_ptr(), ptr(src), ptr(fed), self.n, table.shape[1], table.shape[0]))
 
     def linear(self, x: Operand, weight, bias, epi: int, out: torch.Tensor) -> None:
         """out = x W^T (+ bias) with epilogue ``epi`` (STORE_BF16, STORE_F32,

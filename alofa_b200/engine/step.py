@@ -43,6 +43,7 @@ class StepEntry:
     want: Sequence[int] = ()
     temperature: float = 0.0  # used when the step samples
     uniform: float = 0.0
+    feed: int = -1  # >= 0: the (one) token is row `feed` of what the step before sampled; `tokens` holds a placeholder
 
 
 @dataclass
@@ -81,6 +82,9 @@ class StepRunner:
         self._host_event = [None, None]
         self._flip = 0
         self._status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        # the tokens of the last sampled step stay here, where the next step's embedding can read them
+        self._fed = torch.zeros(max(max_step_tokens, 1), dtype=torch.int32, device=self.rt.device)
+        self.feeds_tokens = bool(getattr(model.embedding, "reads_fed_tokens", False))
         self._layouts = {}
         self.cuda_graphs = cuda_graphs and on_gpu and model.graph_safe()
         self._graphs = {}
@@ -157,6 +161,16 @@ class StepRunner:
         host = host_t.numpy()
         at, n = layout.fields["token_ids"]
         host[at : at + n] = tokens
+        at, n = layout.fields["token_src"]
+        host[at : at + n] = -1
+        if self.feeds_tokens:
+            row = 0
+            for e, count in zip(entries, counts):
+                if e.feed >= 0:
+                    if count != 1:
+                        raise AlofaError("invalid_argument", "a fed-back token stands alone in its entry")
+                    host[at + row] = e.feed
+                row += int(count)
         if n_out:
             at, n = layout.fields["temperature"]
             host[at : at + n].view(np.float32)[:] = np.repeat(np.fromiter((e.temperature for e in entries), dtype=np.float32, count=n_seqs), want_counts)
@@ -169,6 +183,7 @@ class StepRunner:
             ev.record()
             self._host_event[flip] = ev
         ctx = StepContext(self.rt, layout, self._dev_meta, host, self._group_shapes, self._status)
+        ctx.fed_tokens = self._fed if self.feeds_tokens else None
         ctx.max_q_len, ctx.max_kv_len = max_q, max_kv
         ctx.decode_only = max_q == 1
         ctx.max_context = self.max_tokens
@@ -198,8 +213,9 @@ class StepRunner:
         return logits, tokens
 
     def _sample(self, ctx: StepContext, logits: torch.Tensor, any_hot: bool) -> torch.Tensor:
-        """One token per wanted row by temperature alone (0 = the largest logit)."""
-        tokens = torch.empty(ctx.n_out, dtype=torch.int32, device=self.rt.device)
+        """One token per wanted row by temperature alone (0 = the largest logit),
+        left where the next step can take them as its input."""
+        tokens = self._fed[: ctx.n_out]
         scratch = ctx.buf((2 * ctx.n_out * ops.ARGMAX_PARTS,), torch.float32)
         ops.sample(tokens, logits, ctx.temperature, ctx.uniform, scratch, any_hot)
         return tokens

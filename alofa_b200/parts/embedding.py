@@ -18,6 +18,7 @@ from .linear import STORE, Linear
 class TokenEmbedding(Part):
     family = "embedding"
     graph_safe = True
+    reads_fed_tokens = True  # honours ctx.token_src: a step may be launched before the host has seen its tokens
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -32,10 +33,10 @@ class TokenEmbedding(Part):
         self.weight = state[self.prefix + "weight"]
 
     def forward(self, ctx, h):
-        ops.embed_gather(h, self.weight, ctx.token_ids, ctx.status)
+        ops.embed_gather(h, self.weight, ctx.token_ids, ctx.status, ctx.token_src if ctx.fed_tokens is not None else None, ctx.fed_tokens)
 
     def emit(self, prog, ctx, h):
-        prog.embed(h, self.weight, ctx.token_ids)
+        prog.embed(h, self.weight, ctx.token_ids, ctx.token_src if ctx.fed_tokens is not None else None, ctx.fed_tokens)
 
 
 class LinearHead(Part):

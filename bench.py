@@ -216,13 +216,17 @@ def run(args) -> dict:
     e2e_new = max(8, min(64, args.steps))
     prompts = [prompt(PROMPT_LEN) for _ in range(args.batch)]
     engine.generate(prompts, max_new_tokens=e2e_new)  # the same run once untimed: records the CUDA graphs it uses
-    engine.timings["decode_ms"].clear()
+    engine.marks.clear()
     rows_before = engine.counters["decode_rows"]
     t0 = time.perf_counter()
     outs = engine.generate(prompts, max_new_tokens=e2e_new)
     wall = time.perf_counter() - t0
-    decode_wall = sum(engine.timings["decode_ms"]) * 1e-3
-    decode_rows = engine.counters["decode_rows"] - rows_before
+    # wall clock of the decoding part: from the arrival of the last step that held a prompt portion
+    # to the arrival of the last tokens, scheduler and bookkeeping included
+    last_prefill = max((t for t, kind, _ in engine.marks if kind == "prefill"), default=t0)
+    decode_wall = max((t for t, kind, _ in engine.marks if kind == "decode"), default=last_prefill) - last_prefill
+    decode_rows = sum(rows for t, kind, rows in engine.marks if kind == "decode" and t > last_prefill)
+    assert decode_rows <= engine.counters["decode_rows"] - rows_before
     e2e_value = decode_rows / decode_wall if decode_wall > 0 else None
     from alofa_b200.engine.context import Layout
 

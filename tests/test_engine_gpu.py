@@ -129,6 +129,40 @@ def test_stop_token_cancel_and_refusals(model_folders):
         eng.add_request(tiny.tokens("A", 100), SamplingParams(temperature=0.0, max_new_tokens=100))  # longer than the context window
 
 
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "bfloat16")])
+def test_overlapped_steps_give_the_same_tokens(model_folders, name, dtype):
+    """Steps launched before the host has read the tokens of the step before
+    (fed on the device) against steps run one after the other: greedy with a
+    stop token that ends requests early, temperature sampling, more requests
+    than slots, and a pool so small that requests are preempted."""
+    from alofa_b200.sampling.params import SamplingParams
+
+    prompts = [tiny.tokens(name, n, seed=i) for i, n in enumerate([5, 17, 33, 1, 9, 26, 3])]
+    probe = engine(model_folders[name], dtype, overlap_steps=False).generate(prompts, max_new_tokens=12)
+    stop = probe[1][4]  # a token that some requests meet on their way
+    cases = {
+        "greedy with a stop": dict(max_new_tokens=12, eos_token_id=stop),
+        "temperature": dict(sampling=SamplingParams(temperature=0.8, seed=5, max_new_tokens=10, stop_token_ids=(stop,))),
+    }
+    for what, kw in cases.items():
+        runs = {}
+        for overlap in (True, False):
+            eng = engine(model_folders[name], dtype, overlap_steps=overlap)
+            runs[overlap] = eng.generate(prompts, **kw)
+            stats = eng.stats()
+            assert stats["defects"] == 0 and stats["live"] == 0 and all(u == 0 for u in stats["used_pages"]) and not eng.has_work()
+            assert eng.overlap == overlap
+        assert runs[True] == runs[False], what
+        if "stop" in what:
+            assert any(len(out) < 12 for out in runs[True]), "the stop token was meant to end a request early"
+    tight = dict(capacity_blocks=7, admission="optimistic", max_tokens=256, token_budget=64, max_chunk=32)
+    a = engine(model_folders[name], dtype, overlap_steps=True, **tight)
+    b = engine(model_folders[name], dtype, overlap_steps=False, **tight)
+    long_prompts = [tiny.tokens(name, n, seed=i) for i, n in enumerate([30, 31, 29])]
+    assert a.generate(long_prompts, max_new_tokens=20) == b.generate(long_prompts, max_new_tokens=20)
+    assert a.stats()["preempt_total"] > 0 and a.stats()["defects"] == 0 and a.stats()["free_pages"] == [7] * len(a.stats()["free_pages"])
+
+
 def test_scheduler_trace_of_a_run_replays(model_folders, tmp_path):
     from alofa_b200.engine.scheduler import replay_trace
 
