@@ -40,6 +40,8 @@ struct AttnParams {
   int* status;           // set to 2 when a wait on a bulk copy gave up (may be null)
 };
 
+#include "attention_prefill_tc.cuh"
+
 // Copy keys [j0, j0 + 64) of one KV head, keys and values, into shared tiles
 // [64][ROW]; rows past j_end (exclusive) or before j_begin are zero-filled.
 // `table` is the shared copy of the request's block-table entries from entry
@@ -616,6 +618,15 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
     if (cudaGetLastError() != cudaSuccess) return ALOFA_ERR_LAUNCH;
     launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);
   } else {
+    // prompt portions: the tcgen05 kernel where the head size and the pages are its own
+    // (ALOFA_ATTENTION_TC=0 keeps the mma.sync kernel), else mma.sync
+    static int use_tc = -1;
+    if (use_tc < 0) {
+      const char* env = getenv("ALOFA_ATTENTION_TC");
+      use_tc = (env && env[0] == '0') ? 0 : 1;
+    }
+    int rc = ALOFA_OK;
+    if (use_tc && !decode_only && launch_prefill_tc(p, k_cache, v_cache, cache_slots, tiles, nkv, n_seqs, max_kv_len, stream, &rc)) return rc;
     launch_dep(attention_bf16_kernel<false, PREFILL_STAGES>, dim3(tiles, nkv, n_seqs), 128, smem, stream, p);
   }
   return launch_status();

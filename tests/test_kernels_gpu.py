@@ -371,6 +371,50 @@ def test_attention_bf16_far_key_and_window_edge(ops):
                 assert_close(got, want, TOL[BF16], f"window {window} offset {offset} split {split}")
 
 
+@pytest.mark.parametrize("hd, nh, nkv", [(64, 14, 2), (64, 3, 3), (128, 8, 2), (128, 5, 1)])
+def test_attention_prompt_portions_on_tcgen05(ops, hd, nh, nkv):
+    """Prompt portions with pages of 64 and 128 keys (the tcgen05 kernel's
+    shapes): long portions that wrap its ring of key blocks, portions that
+    start mid-sequence, row counts that are no multiple of its 128-row tile,
+    a decode token beside them, windows shorter and longer than a key block;
+    and a far key and a window's edge made to stand out in a long portion."""
+    for page in (64, 128):
+        for window in (None, 70, 333):
+            rng = np.random.default_rng(hd + page)
+            lens, q_lens = [1000, 130, 64, 777, 129], [700, 130, 1, 777, 2]
+            got, want = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=q_lens, page=page, window=window, rng=rng, fast=True)
+            assert_close(got, want, TOL[BF16], f"hd={hd} page={page} window={window}")
+    for far in (0, 127, 128, 500, 895):
+        rng = np.random.default_rng(far)
+
+        def craft(qs, ks, vs, far=far):
+            direction = rng.normal(size=hd)
+            direction /= np.linalg.norm(direction)
+            qs[0][-1, :] = np.tile(12.0 * direction, nh)
+            qs[0][-300, :] = np.tile(12.0 * direction, nh)
+            ks[0][far, :] = np.tile(12.0 * direction, nkv)
+            vs[0][far, :] = 100.0
+
+        got, want = attention_case(ops, BF16, hd, nh, nkv, lens=[900], q_lens=[400], page=64, window=None, rng=rng, craft=craft, fast=True)
+        assert (np.abs(want[-1]).min() > 90.0) and ((np.abs(want[-300]).min() > 90.0) == (far <= 600))
+        # the two rows made for it; rows that see the value of 100 by chance are only as exact as
+        # bfloat16 weights times 100 can be, which the bound of the random cases does not describe
+        assert_close(got[[-1, -300]], want[[-1, -300]], TOL[BF16], f"far key at {far}")
+    for window in (1, 128, 129, 200):
+        for offset, seen in ((window - 1, True), (window, False)):
+            rng = np.random.default_rng(window)
+
+            def craft(qs, ks, vs, offset=offset):
+                direction = np.ones(hd) / np.sqrt(hd)
+                qs[0][-1, :] = np.tile(14.0 * direction, nh)
+                ks[0][599 - offset, :] = np.tile(14.0 * direction, nkv)
+                vs[0][599 - offset, :] = 50.0
+
+            got, want = attention_case(ops, BF16, hd, nh, nkv, lens=[600], q_lens=[300], page=64, window=window, rng=rng, craft=craft, fast=True)
+            assert (np.abs(want[-1]).min() > 45.0) == seen
+            assert_close(got[-1:], want[-1:], TOL[BF16], f"window {window} offset {offset}")
+
+
 def test_attention_rows_do_not_depend_on_the_batch(ops):
     """The same query gives the same bits alone or among other requests, and
     whatever the page size and the pages are."""
