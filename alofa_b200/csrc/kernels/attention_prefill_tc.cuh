@@ -46,9 +46,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 // Descriptor of an MN-major operand with 128-byte swizzle: rows (depth index)
 // of 128 bytes, 8-row groups 1024 bytes apart, 64-wide panels `panel_bytes` apart.
 __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t panel_bytes) {

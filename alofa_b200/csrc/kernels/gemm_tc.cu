@@ -229,6 +229,97 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
 }
 
+// The epilogue of a 128-token tile whose width is a multiple of 4: warp q owns
+// rows [32q, 32q + 32) of the accumulator at `tmem_acc`; `staging` holds
+// 4 x 32 rows of 132 floats.  `release` (optional, 128 arrivals) is signalled
+// once the accumulator has been read out.
+template <int BNF, int EPI>
+__device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uint32_t tmem_base, float* staging, int q, int lane, int f0, int t0,
+                                                       int n_splits, int split_index, uint64_t* release) {
+  constexpr bool GATED = EPI == EPI_GATED;
+  constexpr int FEATS = GATED ? BNF / 2 : BNF;
+  // The accumulator rows go through shared memory so
+  // that global memory is written a whole row of 128 features at a time:
+  // each thread drops its row's values into a padded tile, then the warp
+  // walks the 32 rows with one 16-byte access per lane.
+  constexpr int PITCH = 132;  // floats per staged row: 128 + padding against bank conflicts
+  float* stage = staging + (size_t)q * 32 * PITCH;
+  const bool split = n_splits > 1;
+  const int N = args.N;
+  const size_t plane = (size_t)args.T * N;
+#pragma unroll 1
+  for (int cb = 0; cb < FEATS; cb += 128) {
+    if (f0 + cb >= N) break;
+#pragma unroll 1
+    for (int c0 = 0; c0 < 128 && cb + c0 < FEATS; c0 += 16) {
+      const int f = f0 + cb + c0;
+      if (f >= N) break;
+      uint32_t r0[16], r1[16];
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb + c0);
+      tmem_ld16(taddr, r0);
+      if (GATED) tmem_ld16(taddr + FEATS, r1);
+      tmem_ld_wait();
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float a = __uint_as_float(r0[j]);
+        if (!split && args.bias && f + j < N) a += args.bias[f + j];
+        if (GATED) {
+          float u = __uint_as_float(r1[j]);
+          if (args.bias && f + j < N) u += args.bias[N + f + j];
+          a = __fdividef(a, 1.0f + __expf(-a)) * u;
+        }
+        v[j] = a;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(stage + lane * PITCH + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+    if (release && (cb + 128 >= FEATS || f0 + cb + 128 >= N)) {  // the accumulator is read out: the next tile but one may have it
+      tc_fence_before();
+      mbar_arrive(release);
+    }
+    __syncwarp();
+    const int f = f0 + cb + lane * 4;  // this lane's four features of every row
+    const bool f_ok = f < N && cb + lane * 4 < FEATS;  // N % 4 == 0: a group is inside or outside as a whole
+    const int rows = min(32, args.T - (t0 + q * 32));
+    if (f_ok) {
+      if (split) {
+        float* p = args.partial + (size_t)split_index * plane + (size_t)(t0 + q * 32) * N + f;
+#pragma unroll 4
+        for (int r = 0; r < rows; ++r) *reinterpret_cast<float4*>(p + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
+      } else if (EPI == EPI_RESIDUAL) {
+        float* o = (float*)args.out + (size_t)(t0 + q * 32) * N + f;
+#pragma unroll 1
+        for (int rb = 0; rb < 32; rb += 16) {  // sixteen rows at a time: all their loads in flight, then the stores
+          float4 b[16];
+#pragma unroll
+          for (int r = 0; r < 16; ++r)
+            if (rb + r < rows) b[r] = *reinterpret_cast<float4*>(o + (size_t)(rb + r) * N);
+#pragma unroll
+          for (int r = 0; r < 16; ++r)
+            if (rb + r < rows) {
+              const float4 a = *reinterpret_cast<const float4*>(stage + (rb + r) * PITCH + lane * 4);
+              *reinterpret_cast<float4*>(o + (size_t)(rb + r) * N) = make_float4(b[r].x + a.x, b[r].y + a.y, b[r].z + a.z, b[r].w + a.w);
+            }
+        }
+      } else if (args.out_bf16) {
+        bf16* o = (bf16*)args.out + (size_t)(t0 + q * 32) * N + f;
+#pragma unroll 4
+        for (int r = 0; r < rows; ++r) {
+          const float4 a = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
+          __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
+          *reinterpret_cast<uint2*>(o + (size_t)r * N) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
+      } else {
+        float* o = (float*)args.out + (size_t)(t0 + q * 32) * N + f;
+#pragma unroll 4
+        for (int r = 0; r < rows; ++r) *reinterpret_cast<float4*>(o + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
+      }
+    }
+    __syncwarp();
+  }
+}
+
 // ---------------------------------------------------------------------------
 // The same product with the tokens as the M operand, for prompt portions:
 // one CTA owns 128 tokens and BNF weight rows (features; for EPI_GATED the
@@ -328,82 +419,7 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #endif
     const bool staged = (args.N & 3) == 0 && !(GATED && gridDim.z > 1);
     if (ok && staged && t0 + q * 32 < args.T) {
-      // The accumulator rows go through shared memory (the ring is idle now) so
-      // that global memory is written a whole row of 128 features at a time:
-      // each thread drops its row's values into a padded tile, then the warp
-      // walks the 32 rows with one 16-byte access per lane.
-      constexpr int PITCH = 132;  // floats per staged row: 128 + padding against bank conflicts
-      float* stage = reinterpret_cast<float*>(tiles) + (size_t)q * 32 * PITCH;
-      const bool split = gridDim.z > 1;
-      const int N = args.N;
-      const size_t plane = (size_t)args.T * N;
-#pragma unroll 1
-      for (int cb = 0; cb < FEATS; cb += 128) {
-        if (f0 + cb >= N) break;
-#pragma unroll 1
-        for (int c0 = 0; c0 < 128 && cb + c0 < FEATS; c0 += 16) {
-          const int f = f0 + cb + c0;
-          if (f >= N) break;
-          uint32_t r0[16], r1[16];
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb + c0);
-          tmem_ld16(taddr, r0);
-          if (GATED) tmem_ld16(taddr + FEATS, r1);
-          tmem_ld_wait();
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float a = __uint_as_float(r0[j]);
-            if (!split && args.bias && f + j < N) a += args.bias[f + j];
-            if (GATED) {
-              float u = __uint_as_float(r1[j]);
-              if (args.bias && f + j < N) u += args.bias[N + f + j];
-              a = __fdividef(a, 1.0f + __expf(-a)) * u;
-            }
-            v[j] = a;
-          }
-#pragma unroll
-          for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(stage + lane * PITCH + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        }
-        __syncwarp();
-        const int f = f0 + cb + lane * 4;  // this lane's four features of every row
-        const bool f_ok = f < N && cb + lane * 4 < FEATS;  // N % 4 == 0: a group is inside or outside as a whole
-        const int rows = min(32, args.T - (t0 + q * 32));
-        if (f_ok) {
-          if (split) {
-            float* p = args.partial + (size_t)blockIdx.z * plane + (size_t)(t0 + q * 32) * N + f;
-#pragma unroll 4
-            for (int r = 0; r < rows; ++r) *reinterpret_cast<float4*>(p + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
-          } else if (EPI == EPI_RESIDUAL) {
-            float* o = (float*)args.out + (size_t)(t0 + q * 32) * N + f;
-#pragma unroll 1
-            for (int rb = 0; rb < 32; rb += 16) {  // sixteen rows at a time: all their loads in flight, then the stores
-              float4 b[16];
-#pragma unroll
-              for (int r = 0; r < 16; ++r)
-                if (rb + r < rows) b[r] = *reinterpret_cast<float4*>(o + (size_t)(rb + r) * N);
-#pragma unroll
-              for (int r = 0; r < 16; ++r)
-                if (rb + r < rows) {
-                  const float4 a = *reinterpret_cast<const float4*>(stage + (rb + r) * PITCH + lane * 4);
-                  *reinterpret_cast<float4*>(o + (size_t)(rb + r) * N) = make_float4(b[r].x + a.x, b[r].y + a.y, b[r].z + a.z, b[r].w + a.w);
-                }
-            }
-          } else if (args.out_bf16) {
-            bf16* o = (bf16*)args.out + (size_t)(t0 + q * 32) * N + f;
-#pragma unroll 4
-            for (int r = 0; r < rows; ++r) {
-              const float4 a = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
-              __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
-              *reinterpret_cast<uint2*>(o + (size_t)r * N) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-            }
-          } else {
-            float* o = (float*)args.out + (size_t)(t0 + q * 32) * N + f;
-#pragma unroll 4
-            for (int r = 0; r < rows; ++r) *reinterpret_cast<float4*>(o + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
-          }
-        }
-        __syncwarp();
-      }
+      tokens_epilogue_staged<BNF, EPI>(args, tmem_base, reinterpret_cast<float*>(tiles), q, lane, f0, t0, (int)gridDim.z, (int)blockIdx.z, nullptr);
     } else if (ok && t0 + q * 32 < args.T) {
       // widths that are no multiple of 4 (or gated partial sums): element-wise, straight from the registers
       const bool split = gridDim.z > 1;
@@ -517,6 +533,132 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 }
 
 // ---------------------------------------------------------------------------
+// The same, persistent: one CTA per SM works through the tiles of a wide
+// product (tile = 128 tokens x 256 weight rows; width a multiple of 4, depth
+// unsplit).  The ring of stages runs on across tiles, and the accumulator has
+// two homes in tensor memory that the MMA warp fills in turn, so the epilogue
+// of one tile (tensor memory -> registers -> shared memory -> global) runs
+// beside the MMAs of the next.  Tiles are taken feature-tile first, so CTAs
+// that run side by side read the same tokens and neighbouring weights.
+// ---------------------------------------------------------------------------
+constexpr int PERSISTENT_STAGES = 3;
+constexpr int STAGING_BYTES = 4 * 32 * 132 * 4;  // the epilogue's padded rows
+
+template <int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args) {
+  constexpr int BNF = 256;
+  constexpr bool GATED = EPI == EPI_GATED;
+  constexpr int FEATS = GATED ? BNF / 2 : BNF;
+  constexpr uint32_t A_BYTES = 128 * BK * 2;
+  constexpr uint32_t B_BYTES = BNF * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BNF >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* staging = reinterpret_cast<float*>(tiles + (size_t)PERSISTENT_STAGES * STAGE_BYTES);
+  __shared__ uint64_t full_bar[PERSISTENT_STAGES], empty_bar[PERSISTENT_STAGES], acc_full[2], acc_free[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_ftiles = (args.N + FEATS - 1) / FEATS, n_ttiles = (args.T + 127) / 128;
+  const int n_tiles = n_ftiles * n_ttiles;
+  const int n_slices = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < PERSISTENT_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_free[b], 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) tmem_alloc(&tmem_base_smem, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  pdl_begin();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;  // slices asked for so far, over all tiles
+      for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int f0 = (tile % n_ftiles) * FEATS, t0 = (tile / n_ftiles) * 128;
+        for (int i = 0; i < n_slices; ++i, ++it) {
+          const int s = it % PERSISTENT_STAGES;
+          if (it >= PERSISTENT_STAGES && !mbar_wait(&empty_bar[s], ((it / PERSISTENT_STAGES) - 1) & 1, &abort_flag)) break;
+          uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          tma_load_2d(stage, &map_x, &full_bar[s], i * BK, t0);
+          if (GATED) {
+            tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], i * BK, f0);
+            tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], i * BK, args.N + f0);
+          } else {
+            tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], i * BK, f0);
+          }
+        }
+        if (abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int it = 0, j = 0;  // slices consumed; tiles of this CTA so far
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+        const int buf = j & 1;
+        if (j >= 2) ok = mbar_wait(&acc_free[buf], ((j >> 1) - 1) & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        for (int i = 0; i < n_slices; ++i, ++it) {
+          const int s = it % PERSISTENT_STAGES;
+          ok = mbar_wait(&full_bar[s], (it / PERSISTENT_STAGES) & 1, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const uint64_t desc_a = smem_desc_sw128(stage), desc_b = smem_desc_sw128(stage + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_base + buf * BNF, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int j = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+      const int buf = j & 1;
+      const int f0 = (tile % n_ftiles) * FEATS, t0 = (tile / n_ftiles) * 128;
+      bool ok = mbar_wait(&acc_full[buf], (j >> 1) & 1, &abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      if (t0 + q * 32 < args.T) {
+        tokens_epilogue_staged<BNF, EPI>(args, tmem_base + buf * BNF, staging, q, lane, f0, t0, 1, 0, &acc_free[buf]);
+      } else {
+        tc_fence_before();
+        mbar_arrive(&acc_free[buf]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
+}
+
+// ---------------------------------------------------------------------------
 // Second stage of split-K: add the partial sums in split order, then the
 // epilogue.  partial [splits, n_acc, T, N].
 // ---------------------------------------------------------------------------
@@ -610,6 +752,31 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
     configured = true;
   }
   dim3 grid((args.N + FEATS - 1) / FEATS, (args.T + 127) / 128, splits);
+  if (BNF == 256 && splits == 1 && (args.N & 3) == 0 && args.T > 128 && args.K <= 2048) {
+    // More tiles than SMs and a shallow depth, where a tile's epilogue is a large share of its
+    // time: one resident CTA per SM works through the tiles, epilogues beside MMAs.  (Deep
+    // products measured faster as two CTAs per SM, which keep four stages in flight per SM.)
+    static int sms = 0, persistent = -1;
+    if (persistent < 0) {
+      const char* env = getenv("ALOFA_GEMM_PERSISTENT");
+      persistent = (env && env[0] == '0') ? 0 : 1;
+      int device = 0;
+      if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 0;
+    }
+    const int n_tiles = (int)(grid.x * grid.y);
+    if (persistent && sms > 0 && n_tiles > sms) {
+      static bool configured_p = false;
+      constexpr size_t SMEM_P = (size_t)PERSISTENT_STAGES * STAGE + STAGING_BYTES + 1024;
+      if (!configured_p) {
+        if (cudaFuncSetAttribute(gemm_tc_tokens_persistent_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_P) != cudaSuccess)
+          return ALOFA_ERR_LAUNCH;
+        prefer_max_shared(gemm_tc_tokens_persistent_kernel<EPI>);
+        configured_p = true;
+      }
+      launch_dep(gemm_tc_tokens_persistent_kernel<EPI>, dim3(sms), NUM_THREADS, SMEM_P, stream, mw, mx, args);
+      return launch_status();
+    }
+  }
   launch_dep(gemm_tc_tokens_kernel<BNF, EPI>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
   return launch_status();
 }
