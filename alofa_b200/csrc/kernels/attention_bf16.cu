@@ -18,6 +18,10 @@
 // key index alone); the partial (output, maximum, sum) triples are merged by
 // attention_combine_kernel in split order.
 //
+// Prompt portions go to the tcgen05 kernel of attention_prefill_tc.cuh instead
+// when the head size is 64 or 128 and a page holds whole 64-key blocks; decode
+// tokens of small head groups to attention_decode_kernel below.
+//
 // HEAD_DIM is a compile-time constant (a multiple of 16 up to 128): the
 // library is built per head size.  Formulas: src/alofa/kernels/cpu/scalar.mojo:392-470,
 // paged addressing src/alofa/kernels/cpu/paged.mojo:249-336.
