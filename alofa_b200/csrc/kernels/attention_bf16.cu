@@ -536,7 +536,18 @@ static size_t attention_smem_bytes(int stages, int table_entries) {
 
 ALOFA_API int alofa_attention_head_dim() { return HD; }
 
+// Merge the splits a launch with do_combine = 0 left behind: out [T, nh, HD] bf16.
+ALOFA_API int alofa_attention_combine(void* out, const float* partial_o, const float* partial_ml, const int* positions, int n_tokens, int nh,
+                                      int window, int split_keys, cudaStream_t stream) {
+  if (n_tokens <= 0) return ALOFA_OK;
+  if (!partial_o || !partial_ml || !positions || split_keys <= 0) return ALOFA_ERR_ARGUMENT;
+  launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, n_tokens * nh);
+  return launch_status();
+}
+
 // cache_slots: rows of k_cache / v_cache (token slots), for the tensor maps.
+// do_combine = 0 (decode tokens in splits only): the splits are left in partial_o / partial_ml
+// for the consumer to merge (alofa_attention_combine, or a product that merges them as it reads).
 // max_kv_len: the most keys any request of this step has (sizes the shared copy of
 // block-table entries).  tiles: query tiles of the longest request = ceil(max_q_len * g / 64).  n_splits > 0
 // selects split mode: the keys of a request (decode tokens) or of every query tile
@@ -545,7 +556,7 @@ ALOFA_API int alofa_attention_head_dim() { return HD; }
 ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len, const int* positions,
                                    const int* block_table, int max_blocks, int page_size, int n_seqs, int n_tokens, int tiles, int nh, int nkv,
                                    int window, float scale, int n_splits, int split_keys, float* partial_o, float* partial_ml,
-                                   int max_kv_len, long long cache_slots, int* status, cudaStream_t stream) {
+                                   int max_kv_len, long long cache_slots, int* status, int do_combine, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || tiles <= 0) return ALOFA_ERR_ARGUMENT;
   if (n_splits > 0 && (split_keys <= 0 || split_keys % BLOCK_N != 0 || !partial_o || !partial_ml || !positions)) return ALOFA_ERR_ARGUMENT;
@@ -609,7 +620,7 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
     else
       rc = tma ? launch_decode<2, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<2, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
     if (rc != ALOFA_OK) return rc;
-    if (n_splits > 1)
+    if (n_splits > 1 && do_combine)
       launch_dep(attention_combine_kernel, n_tokens * nh, HD, 0, stream, (bf16*)out, partial_o, partial_ml, positions, nh, window, split_keys, p.n_rows_total);
   } else if (n_splits > 0 && !decode_only) {
     // prompt portions: every query tile's keys split over n_splits CTAs, so that the tiles

@@ -25,6 +25,7 @@
 #include "tma.cuh"
 
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED = 2 };
+enum { B_ROWS = 0, B_MERGED_SPLITS = 1 };
 
 constexpr int BM = 128;        // features per CTA (UMMA M)
 constexpr int BK = 64;         // k-slice: 64 bf16 = one 128-byte swizzle row
@@ -41,13 +42,91 @@ struct GemmArgs {
   int k_slices_per_split;
   int out_bf16;
   int* status;
+  // The token operand of the weights-on-M kernel need not lie in memory as rows: the
+  // epilogue warps, idle while the MMAs run, can make each k-slice of it in shared memory.
+  int b_kind;               // B_ROWS: rows of x by TMA; B_MERGED_SPLITS: made from the key splits of decode attention
+  const float* b_src;       // merged splits: partial outputs [splits, T * heads, head_dim]
+  const float* b_ml;        // merged splits: (maximum, sum) [splits, T * heads, 2]
+  const int* b_positions;   // merged splits: position of each token
+  int b_heads, b_head_dim, b_window, b_split_keys;
 #ifdef ALOFA_GEMM_TIMING
   long long* stamps;  // [8] clock64 of CTA (0,0,0): start, after setup, first data, accumulator done, epilogue done, end
 #endif
 };
 
-template <int BN, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// ---------------------------------------------------------------------------
+// A token operand that is computed, not loaded: eight consecutive depth entries
+// for token t from depth k0 on, as packed bfloat16.  All loads of a chunk are
+// issued before any is used, so a chunk costs one trip to L2.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 packed;
+  __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+  __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+  packed.x = *reinterpret_cast<uint32_t*>(&h0);
+  packed.y = *reinterpret_cast<uint32_t*>(&h1);
+  packed.z = *reinterpret_cast<uint32_t*>(&h2);
+  packed.w = *reinterpret_cast<uint32_t*>(&h3);
+  return packed;
+}
+
+// B_MERGED_SPLITS: the attention output of a decode token whose keys were split
+// over CTAs - (output, maximum, sum) per split, merged in split order exactly as
+// attention_combine_kernel does.  Up to MERGE_MAX splits.
+constexpr int MERGE_MAX = 16;
+__device__ __forceinline__ uint4 merged_splits8(const GemmArgs& a, int t, int k0, int P) {
+  const int head = k0 / a.b_head_dim, d = k0 - head * a.b_head_dim;
+  const int rows = a.T * a.b_heads, row = t * a.b_heads + head;
+  const int k_lo = a.b_window > 0 ? max(0, P - a.b_window + 1) : 0;
+  const int s_lo = k_lo / a.b_split_keys, n = P / a.b_split_keys - s_lo + 1;  // splits that hold keys of this token
+  float2 ml[MERGE_MAX];
+  float4 lo[MERGE_MAX / 2], hi[MERGE_MAX / 2];
+#pragma unroll
+  for (int i = 0; i < MERGE_MAX; ++i)
+    ml[i] = i < n ? *reinterpret_cast<const float2*>(a.b_ml + ((size_t)(s_lo + i) * rows + row) * 2) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+  for (int i = 0; i < MERGE_MAX / 2; ++i) {
+    const float* src = a.b_src + ((size_t)(s_lo + (i < n ? i : 0)) * rows + row) * a.b_head_dim + d;
+    lo[i] = *reinterpret_cast<const float4*>(src);
+    hi[i] = *reinterpret_cast<const float4*>(src + 4);
+  }
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MERGE_MAX; ++i) m = fmaxf(m, ml[i].x);
+  float l = 0.f, v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  auto add = [&](float2 mls, float4 x, float4 y) {
+    float w;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(w) : "f"(mls.x - m));
+    if (mls.x == -INFINITY) w = 0.f;
+    l += mls.y * w;
+    v[0] += x.x * w, v[1] += x.y * w, v[2] += x.z * w, v[3] += x.w * w;
+    v[4] += y.x * w, v[5] += y.y * w, v[6] += y.z * w, v[7] += y.w * w;
+  };
+#pragma unroll
+  for (int i = 0; i < MERGE_MAX / 2; ++i) add(ml[i], lo[i], hi[i]);
+  if (n > MERGE_MAX / 2) {  // a second trip for the rest
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX / 2; ++i) {
+      const int s = MERGE_MAX / 2 + i;
+      const float* src = a.b_src + ((size_t)(s_lo + (s < n ? s : 0)) * rows + row) * a.b_head_dim + d;
+      lo[i] = *reinterpret_cast<const float4*>(src);
+      hi[i] = *reinterpret_cast<const float4*>(src + 4);
+    }
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX / 2; ++i) add(ml[MERGE_MAX / 2 + i], lo[i], hi[i]);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = v[j] / l;
+  return pack8(v);
+}
+
+// COMPUTED: the token operand is made by the epilogue warps (GemmArgs::b_kind); a variant of
+// its own, so that the plain kernel keeps its small register count and the next kernel's
+// CTAs can become resident beside it under programmatic dependent launch.
+template <int BN, int EPI, bool COMPUTED = false>
+__global__ void __launch_bounds__(NUM_THREADS, COMPUTED ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args, const int stages) {
   constexpr int N_ACC = (EPI == EPI_GATED) ? 2 : 1;
   constexpr uint32_t A_BYTES = BM * BK * 2;
@@ -75,10 +154,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int slice_end = min(total_slices, slice_begin + args.k_slices_per_split);
   const int n_slices = slice_end - slice_begin;
 
+  constexpr bool computed_b = COMPUTED;
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], computed_b ? 1 + 128 : 1);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&acc_bar, 1);
@@ -89,6 +169,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
+  // the position of this thread's token, for a merged-splits operand: written with the step's
+  // metadata before any kernel of the step ran, so it may be read ahead of the wait below
+  int token_pos = 0;
+  if (COMPUTED && args.b_kind == B_MERGED_SPLITS && warp >= 2) {
+    const int t = t0 + ((threadIdx.x - 64) >> 3);
+    if (t < args.T) token_pos = args.b_positions[t];
+  }
   pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
 #ifdef ALOFA_GEMM_TIMING
   if (probe && threadIdx.x == 0) args.stamps[1] = clock64();
@@ -101,11 +188,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int s = i % stages;
         if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1, &abort_flag)) break;
         uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], computed_b ? N_ACC * A_BYTES : STAGE_BYTES);
         const int k = (slice_begin + i) * BK;
         tma_load_2d(stage, &map_w, &full_bar[s], k, f0);
         if (N_ACC == 2) tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, args.N + f0);
-        tma_load_2d(stage + N_ACC * A_BYTES, &map_x, &full_bar[s], k, t0);
+        if (!computed_b) tma_load_2d(stage + N_ACC * A_BYTES, &map_x, &full_bar[s], k, t0);
       }
     }
   } else if (warp == 1) {
@@ -139,6 +226,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int q = warp & 3;
     const int f = f0 + q * 32 + lane;
     const bool f_ok = f < args.N;
+    if constexpr (COMPUTED) {
+      // First the token operand, slice by slice: rows of 128 bytes, 16-byte chunk c of row r at
+      // c ^ (r & 7).  The host allows this for tiles of 16 tokens only: one chunk per thread.
+      const int tid = threadIdx.x - 64;
+      const int r = tid >> 3, c = tid & 7, t = t0 + r;
+      const uint32_t at = r * 128 + ((c ^ (r & 7)) << 4);
+      for (int i = 0; i < n_slices; ++i) {
+        const int s = i % stages;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (t < args.T && (slice_begin + i) * BK + c * 8 < args.K) v = merged_splits8(args, t, (slice_begin + i) * BK + c * 8, token_pos);
+        if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1, &abort_flag)) break;
+        *reinterpret_cast<uint4*>(tiles + (size_t)s * STAGE_BYTES + N_ACC * A_BYTES + at) = v;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&full_bar[s]);
+      }
+    }
     bool ok = n_slices > 0 ? mbar_wait(&acc_bar, 0, &abort_flag) : true;
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
@@ -726,6 +829,21 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
     configured = true;
   }
   dim3 grid((args.N + BM - 1) / BM, (args.T + BN - 1) / BN, splits);
+  if (args.b_kind != B_ROWS) {
+    if constexpr (BN == 16 && EPI == EPI_RESIDUAL) {
+      static bool configured_c = false;
+      if (!configured_c) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
+          return ALOFA_ERR_LAUNCH;
+        prefer_max_shared(gemm_tc_kernel<BN, EPI, true>);
+        configured_c = true;
+      }
+      launch_dep(gemm_tc_kernel<BN, EPI, true>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
+      return launch_status();
+    } else {
+      return ALOFA_ERR_ARGUMENT;  // a computed operand feeds residual products of up to 16 tokens
+    }
+  }
   launch_dep(gemm_tc_kernel<BN, EPI>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
   return launch_status();
 }
@@ -809,9 +927,19 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 // reduce kernel after (else the caller's next kernel adds the partials up).
 // Returns ALOFA_ERR_ARGUMENT for sizes this kernel does not take (K % 8 != 0,
 // pointers not 16-byte aligned).
+// b_kind = B_MERGED_SPLITS (residual products of up to 16 tokens only): x is ignored and the
+// token operand is computed in the kernel from the attention output of decode tokens still in
+// key splits (b_src partial outputs, b_ml maxima and sums, b_positions; heads * head_dim == K).
 ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float* bias, float* partial, int T, int N, int K, int epi, int out_bf16,
-                            int bn, int splits, int do_reduce, int* status, cudaStream_t stream) {
+                            int bn, int splits, int do_reduce, int* status, int b_kind, const float* b_src, const float* b_ml,
+                            const int* b_positions, int b_heads, int b_head_dim, int b_window, int b_split_keys, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return ALOFA_OK;
+  if (b_kind != B_ROWS) {
+    if (bn <= 0 || !b_src || ((uintptr_t)b_src & 15) || (K % 8) != 0) return ALOFA_ERR_ARGUMENT;
+    if (b_kind != B_MERGED_SPLITS || !b_ml || !b_positions || b_heads * b_head_dim != K || b_head_dim % 8 || b_split_keys <= 0) return ALOFA_ERR_ARGUMENT;
+    if (bn != 16 || epi != EPI_RESIDUAL) return ALOFA_ERR_ARGUMENT;  // one 16-byte chunk of a k-slice per epilogue thread
+    x = w;  // any mapped address: the map of x is made but never used
+  }
   if (K <= 0 || (K % 8) != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ALOFA_ERR_ARGUMENT;
   if (epi == EPI_RESIDUAL && out_bf16) return ALOFA_ERR_ARGUMENT;
   const int total_slices = (K + BK - 1) / BK;
@@ -841,6 +969,14 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;  // no empty split
   args.out_bf16 = out_bf16;
   args.status = status;
+  args.b_kind = b_kind;
+  args.b_src = b_src;
+  args.b_ml = b_ml;
+  args.b_positions = b_positions;
+  args.b_heads = b_heads;
+  args.b_head_dim = b_head_dim;
+  args.b_window = b_window;
+  args.b_split_keys = b_split_keys;
 #ifdef ALOFA_GEMM_TIMING
   args.stamps = (long long*)status;  // the timing build reuses the status pointer for its stamps
   args.status = nullptr;

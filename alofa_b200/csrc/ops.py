@@ -71,7 +71,7 @@ def _gemm_tc():
     if lib is None:
         lib = load_library("alofa_gemm_tc", ["kernels/gemm_tc.cu"])
         lib.alofa_gemm_tc.restype = _I
-        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P]
+        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P]
         lib.alofa_splitk_reduce.restype = _I
         lib.alofa_splitk_reduce.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _P]
         lib.alofa_gemm_tc_splits.restype = _I
@@ -86,7 +86,9 @@ def _attention(head_dim: int):
     if lib is None:
         lib = load_library(f"alofa_attention_hd{head_dim}", ["kernels/attention_bf16.cu"], defines={"HEAD_DIM": head_dim})
         lib.alofa_attention_bf16.restype = _I
-        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _P]
+        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _I, _P]
+        lib.alofa_attention_combine.restype = _I
+        lib.alofa_attention_combine.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _P]
         _libs[key] = lib
     return lib
 
@@ -155,8 +157,28 @@ def _elementwise():
     return lib
 
 
+_bound_stream = None  # the stream handle of the step in progress, looked up once per step
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _bound_stream if _bound_stream is not None else torch.cuda.current_stream().cuda_stream
+
+
+class bound_stream:
+    """Within the block, every launch of this module goes to the stream that is
+    current on entry, without asking torch for it at each launch (the lookup
+    costs as much as a launch).  The caller must not switch streams inside."""
+
+    def __enter__(self):
+        global _bound_stream
+        self._before = _bound_stream
+        _bound_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _bound_stream
+        _bound_stream = self._before
+        return False
 
 
 def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
@@ -315,21 +337,38 @@ def gemm_tc_splits(k: int, splits: int) -> int:
     return _gemm_tc().alofa_gemm_tc_splits(k, splits)
 
 
-def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True) -> bool:
+B_ROWS, B_MERGED_SPLITS = 0, 1
+
+
+def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True, computed=None) -> bool:
     """Tensor-core product ``out = x @ w.T`` (bf16 operands, fp32 sums) with
     the epilogue fused.  Returns False, having launched nothing, when the
-    kernel does not take these sizes (depth not a multiple of 8, unaligned)."""
-    m, k = x.shape
+    kernel does not take these sizes (depth not a multiple of 8, unaligned).
+
+    ``computed`` (residual products with ``bn`` = 16 only) replaces ``x`` by
+    rows the kernel makes as it goes: ``(B_MERGED_SPLITS, partial_o,
+    partial_ml, positions, heads, head_dim, window, split_keys)``, the
+    attention output of decode tokens whose key splits are not merged yet."""
     n = out.shape[1]
     rows_w = 2 * n if epi == EPI_GATED else n
-    if w.shape != (rows_w, k) or out.shape[0] != m or (bias is not None and bias.shape[0] != rows_w):
-        raise AlofaError("invalid_argument", "gemm sizes disagree", f"out={tuple(out.shape)} x={tuple(x.shape)} w={tuple(w.shape)} epi={epi}")
+    k = w.shape[1]
+    m = out.shape[0]
+    if w.shape[0] != rows_w or (x is not None and tuple(x.shape) != (m, k)) or (bias is not None and bias.shape[0] != rows_w):
+        raise AlofaError("invalid_argument", "gemm sizes disagree", f"out={tuple(out.shape)} w={tuple(w.shape)} epi={epi}")
+    f32 = torch.float32
+    b_kind, b_src, b_ml, b_pos, heads, hd, window, split_keys = B_ROWS, None, None, None, 0, 0, 0, 0
+    if computed is not None:
+        b_kind, po, pml, positions, heads, hd, window, split_keys = computed
+        b_src, b_ml, b_pos, window = _dev(po, "partial_o", f32), _dev(pml, "partial_ml", f32), _dev(positions, "positions", torch.int32), int(window or 0)
+    elif x is None:
+        raise AlofaError("invalid_argument", "gemm without a token operand")
     rc = _gemm_tc().alofa_gemm_tc(
-        _dev(out, "out"), _dev(x, "x", torch.bfloat16), _dev(w, "w", torch.bfloat16),
-        _dev(bias, "bias", torch.float32) if bias is not None else None,
-        _dev(partial, "partial", torch.float32) if partial is not None else None,
+        _dev(out, "out"), _dev(x, "x", torch.bfloat16) if x is not None else None, _dev(w, "w", torch.bfloat16),
+        _dev(bias, "bias", f32) if bias is not None else None,
+        _dev(partial, "partial", f32) if partial is not None else None,
         m, n, k, epi, _is_bf16(out, "out"), bn, splits, 1 if reduce else 0,
-        _dev(status, "status", torch.int32) if status is not None else None, _stream(),
+        _dev(status, "status", torch.int32) if status is not None else None,
+        b_kind, b_src, b_ml, b_pos, heads, hd, window, split_keys, _stream(),
     )
     if rc == 1:
         return False
@@ -340,10 +379,12 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
 
 
 def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_table, page_size, n_seqs, max_q_len, nh, nkv, hd, window, scale,
-                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0, status=None) -> None:
+                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0, status=None, combine: bool = True) -> None:
     """Causal GQA over the paged bf16 cache for a step's requests; with
     ``n_splits`` > 0 the keys of each request (decode tokens) or of each query
-    tile (prompt portions) are split over several CTAs and merged."""
+    tile (prompt portions) are split over several CTAs and merged - unless
+    ``combine`` is False (decode tokens only): then ``partial_o`` / ``partial_ml``
+    keep the splits for :func:`attention_combine` or a product that merges them."""
     n = q.shape[0]
     bf = torch.bfloat16
     g = nh // nkv
@@ -356,11 +397,20 @@ def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_t
         _dev(partial_o, "partial_o", torch.float32) if partial_o is not None else None,
         _dev(partial_ml, "partial_ml", torch.float32) if partial_ml is not None else None,
         int(max_kv_len) if max_kv_len else block_table.shape[1] * page_size, k_cache.shape[0],
-        _dev(status, "status", torch.int32) if status is not None else None, _stream(),
+        _dev(status, "status", torch.int32) if status is not None else None, 1 if combine else 0, _stream(),
     )
     _done(rc, "attention_bf16", f"hd={hd} nh={nh} nkv={nkv} splits={n_splits}")
-    if n_splits > 0:
+    if n_splits > 1 and combine:
         count_launches(1)
+
+
+def attention_combine(out, partial_o, partial_ml, positions, nh: int, hd: int, window, split_keys: int) -> None:
+    """Merge the key splits of decode tokens: out [T, nh * hd] bf16."""
+    rc = _attention(hd).alofa_attention_combine(
+        _dev(out, "out", torch.bfloat16), _dev(partial_o, "partial_o", torch.float32), _dev(partial_ml, "partial_ml", torch.float32),
+        _dev(positions, "positions", torch.int32), out.shape[0], nh, int(window or 0), split_keys, _stream(),
+    )
+    _done(rc, "attention_combine")
 
 
 def norm_fused(out, h, weight, eps: float, rows=None, partial=None, splits: int = 0, bias=None) -> bool:

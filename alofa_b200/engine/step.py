@@ -13,7 +13,9 @@ reference's counterpart is ``BatchExecutor.plan`` + ``forward``
 
 Steps that hold one token per request and want every row (plain decoding) are
 replayed as CUDA graphs, one graph per batch size: the metadata buffer has the
-same layout and address every time, so a replay only needs the new metadata."""
+same layout and address every time, so a replay only needs the new metadata.
+Steps with prompt portions are recorded too, once a shape (tokens, requests,
+wanted rows) comes a third time; a few such graphs are kept."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -49,8 +51,8 @@ class StepEntry:
 @dataclass
 class DecodeGraph:
     graph: "torch.cuda.CUDAGraph"
-    logits: torch.Tensor
-    tokens: torch.Tensor
+    logits: Optional[torch.Tensor]
+    tokens: Optional[torch.Tensor]
     kernels: int
     program: Optional[DecodeProgram] = None  # the step as one resident kernel, when the model and the sizes allow
 
@@ -87,7 +89,10 @@ class StepRunner:
         self.feeds_tokens = bool(getattr(model.embedding, "reads_fed_tokens", False))
         self._layouts = {}
         self.cuda_graphs = cuda_graphs and on_gpu and model.graph_safe()
-        self._graphs = {}
+        self._graphs = {}  # decode steps by batch size; steps with prompt portions by (tokens, requests, wanted rows)
+        self.prompt_graphs = self.cuda_graphs and os.environ.get("ALOFA_PROMPT_GRAPHS", "1") != "0"
+        self.max_prompt_graphs = 4
+        self._seen_shapes = {}
         # Small decode steps as one resident kernel: ALOFA_DECODE_PROGRAM=1.  Off unless asked for:
         # measured at the benchmark's sizes, a layer takes longer in the resident kernel (barriers over
         # the grid and operand loads that cannot start before them) than as ten dependent launches.
@@ -197,19 +202,40 @@ class StepRunner:
 
     def _run(self, ctx: StepContext, sample: bool):
         """(logits or None, tokens or None) for a prepared step."""
-        graphable = self.cuda_graphs and ctx.decode_only and ctx.n_out == ctx.n_seqs
-        if graphable:
+        if self.cuda_graphs and ctx.decode_only and ctx.n_out == ctx.n_seqs:
             g = self._graphs.get(ctx.n_seqs)
             if g is None:
-                g = self._capture(ctx)
+                g = self._capture(ctx, ctx.n_seqs)
+            g.graph.replay()
+            ops.count_launches(g.kernels)
+            return g.logits, g.tokens
+        if self.prompt_graphs and not ctx.decode_only:
+            # A step with prompt portions is some two hundred launches, about as long to issue from
+            # Python as to run: a shape (tokens, requests, wanted rows) met a third time is recorded
+            # (which costs two more runs of it) and replayed from then on.  A few shapes are kept, the least recently used one goes.
+            key = (ctx.n_tokens, ctx.n_seqs, ctx.n_out)
+            g = self._graphs.pop(key, None)
+            if g is None:
+                seen = self._seen_shapes.get(key, 0)
+                if len(self._seen_shapes) > 4096:
+                    self._seen_shapes.clear()
+                self._seen_shapes[key] = seen + 1
+                if seen >= 2:
+                    kept = [k for k in self._graphs if isinstance(k, tuple)]
+                    if len(kept) >= self.max_prompt_graphs:
+                        del self._graphs[kept[0]]
+                    g = self._capture(ctx, key)
+                    self._graphs.pop(key)
             if g is not None:
+                self._graphs[key] = g  # most recently used last
                 g.graph.replay()
                 ops.count_launches(g.kernels)
-                return g.logits, g.tokens
-        logits = self.model.forward(ctx, self.storage.caches)
-        tokens = None
-        if sample and logits is not None:
-            tokens = self._sample(ctx, logits, ctx.any_hot)
+                return (g.logits if ctx.n_out else None), (g.tokens if ctx.n_out else None)
+        with ops.bound_stream():
+            logits = self.model.forward(ctx, self.storage.caches)
+            tokens = None
+            if sample and logits is not None:
+                tokens = self._sample(ctx, logits, ctx.any_hot)
         return logits, tokens
 
     def _sample(self, ctx: StepContext, logits: torch.Tensor, any_hot: bool) -> torch.Tensor:
@@ -220,12 +246,16 @@ class StepRunner:
         ops.sample(tokens, logits, ctx.temperature, ctx.uniform, scratch, any_hot)
         return tokens
 
-    def _capture(self, ctx: StepContext) -> Optional[DecodeGraph]:
-        """Record the decode step of this batch size as a CUDA graph.  The step
-        is first run once outright (its cache writes are the same ones the
-        replay repeats), which also loads every kernel before recording."""
+    def _capture(self, ctx: StepContext, key) -> DecodeGraph:
+        """Record the step of this shape as a CUDA graph.  The step is first run
+        once outright (its cache writes are the same ones the replay repeats),
+        which also loads every kernel before recording.  Launch shapes inside
+        must depend on the shape alone: attention is sized for the longest
+        context and for one request holding all tokens but one each of the others."""
         ctx.capturing = True
-        program = self._program(ctx)
+        if not ctx.decode_only:
+            ctx.max_q_len = ctx.n_tokens - ctx.n_seqs + 1
+        program = self._program(ctx) if ctx.decode_only else None
         if program is not None:
             program.run()
         else:
@@ -233,15 +263,15 @@ class StepRunner:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph), ops.bound_stream():
             if program is not None:
                 program.run()
                 logits = program.logits
             else:
                 logits = self.model.forward(ctx, self.storage.caches)
-            tokens = self._sample(ctx, logits, True)  # a replay may meet rows of any temperature
+            tokens = self._sample(ctx, logits, True) if logits is not None else None  # a replay may meet rows of any temperature
         entry = DecodeGraph(graph, logits, tokens, ops.launch_count() - before, program)
-        self._graphs[ctx.n_seqs] = entry
+        self._graphs[key] = entry
         return entry
 
     def _program(self, ctx: StepContext) -> Optional[DecodeProgram]:

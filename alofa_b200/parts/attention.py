@@ -20,7 +20,7 @@ import torch
 from ..csrc import ops
 from ..errors import AlofaError
 from .base import Ineligible, PagedKV, Part, TensorSpec, as_float32_vector, build_part, register_part
-from .linear import RESIDUAL, STORE, Linear
+from .linear import RESIDUAL, STORE, Linear, MergedSplits
 
 
 class GQAttention(Part):
@@ -107,8 +107,7 @@ class GQAttention(Part):
                 k_view = qkv[:, self.q_dim : self.q_dim + nkv_in * self.hd].view(n, nkv_in, self.hd)
                 custom(ctx, q_view, k_view)
             ops.rope_store(q, cache.k, cache.v, qkv, table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, rot, writes)
-        attn = ctx.buf((n, self.q_dim), dt)
-        self.attend(ctx, attn, q, cache, group)
+        attn = self.attend(ctx, q, cache, group)
         owed = self.out(h, attn, defer=True)
         if owed is not None:
             ctx.set_pending(h, owed)
@@ -132,9 +131,17 @@ class GQAttention(Part):
     # long tiles' tail saves (4.9 ms against 4.5 ms for the step), so it is off.
     PROMPT_SPLIT_KEYS = 0
 
-    def attend(self, ctx, out, q, cache, group):
-        """Attention of the step's rows over the cache: the tensor-core kernel
-        for bfloat16 and head sizes it is built for, else the generic one."""
+    # Decode tokens in at most this many key splits are handed to the output product unmerged: it
+    # merges them while it loads its operand, which saves a kernel; with more splits every CTA of
+    # the product would re-read too many partial outputs.
+    MERGE_IN_PRODUCT_SPLITS = 16
+
+    def attend(self, ctx, q, cache, group):
+        """Attention of the step's rows over the cache: the tensor-core kernels
+        for bfloat16 and head sizes they are built for, else the generic one.
+        Returns the output rows, or a :class:`MergedSplits` for the product
+        that follows to merge."""
+        out = ctx.buf((q.shape[0], self.q_dim), q.dtype)
         if q.dtype == torch.bfloat16 and ops.attention_bf16_supported(self.hd):
             splits, po, pml = 0, None, None
             longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
@@ -148,15 +155,19 @@ class GQAttention(Part):
             if splits:
                 po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
                 pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
+            unmerged = ctx.decode_only and 1 < splits <= self.MERGE_IN_PRODUCT_SPLITS and self.nh // self.nkv <= 16 and ctx.n_tokens <= 16
             ops.attention_bf16(
                 out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, ctx.positions, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
-                self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest, ctx.status,
+                self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest, ctx.status, combine=not unmerged,
             )
-            return
+            if unmerged:
+                return MergedSplits(po, pml, ctx.positions, ctx.n_tokens, self.nh, self.hd, self.window, per_split)
+            return out
         ops.paged_attention_generic(
             out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
             self.nh, self.nkv, self.hd, self.window, self.scale,
         )
+        return out
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from ..errors import AlofaError
 
 SMS = 148
 K_SLICE = 64
@@ -67,20 +68,29 @@ def plan(linear):
     gated = linear.epi == ops.EPI_GATED
     n_acc = 2 if gated else 1
 
-    def run(out, x: torch.Tensor, defer: bool = False):
+    def run(out, x, defer: bool = False):
         tokens = x.shape[0]
         if tokens == 0:
             return True
-        if x.data_ptr() % 16 or not x.is_contiguous():
-            return False
         bn = _tile(tokens, linear.out_features, gated)
+        computed = None
+        if not isinstance(x, torch.Tensor):
+            # rows still to be made: the weights-on-M kernel makes them as it loads; else they are made first
+            if bn == 16 and linear.epi == ops.EPI_RESIDUAL and depth % 8 == 0 and x.fits_kernel():  # tiles of 16 tokens: a 16-byte chunk per epilogue thread
+                computed, x = x.computed(), None
+            else:
+                x = x.rows()
+        if x is not None and (x.data_ptr() % 16 or not x.is_contiguous()):
+            return False
         splits = ops.gemm_tc_splits(depth, _splits(_ctas(tokens, linear.out_features, bn, gated), depth, defer and n_acc == 1))
         partial = None
         if splits > 1:
-            partial = torch.empty((splits * n_acc, tokens, linear.out_features), dtype=torch.float32, device=x.device)
+            partial = torch.empty((splits * n_acc, tokens, linear.out_features), dtype=torch.float32, device=w.device)
         deferred = defer and splits > 1 and n_acc == 1
         dst = partial[0] if deferred else out  # a deferred product writes partial sums only
-        if not ops.gemm_tc(dst, x, w, linear.bias, linear.epi, bn, splits, partial, reduce=not deferred):
+        if not ops.gemm_tc(dst, x, w, linear.bias, linear.epi, bn, splits, partial, reduce=not deferred, computed=computed):
+            if computed is not None:
+                raise AlofaError("state", "the tensor-core product refused an operand it had accepted")
             return False
         return Partial(partial, splits, linear.bias) if deferred else True
 

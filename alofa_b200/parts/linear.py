@@ -34,6 +34,32 @@ class Partial:
     bias: Optional[torch.Tensor]
 
 
+class MergedSplits:
+    """Rows a product may read that are not in memory yet: the attention
+    output of decode tokens, still split by keys (``partial_o [splits, T *
+    heads, head_dim]``, ``partial_ml [splits, T * heads, 2]``).  A product that
+    can merges them while it loads its operand; any other consumer calls
+    :meth:`rows`."""
+
+    dtype = torch.bfloat16
+
+    def __init__(self, partial_o, partial_ml, positions, tokens: int, heads: int, head_dim: int, window, split_keys: int):
+        self.partial_o, self.partial_ml, self.positions = partial_o, partial_ml, positions
+        self.heads, self.head_dim, self.window, self.split_keys = heads, head_dim, window, split_keys
+        self.shape = (tokens, heads * head_dim)
+
+    def fits_kernel(self) -> bool:
+        return self.partial_o.shape[0] <= 16
+
+    def computed(self):
+        return (ops.B_MERGED_SPLITS, self.partial_o, self.partial_ml, self.positions, self.heads, self.head_dim, self.window, self.split_keys)
+
+    def rows(self) -> torch.Tensor:
+        out = torch.empty(self.shape, dtype=torch.bfloat16, device=self.partial_o.device)
+        ops.attention_combine(out, self.partial_o, self.partial_ml, self.positions, self.heads, self.head_dim, self.window, self.split_keys)
+        return out
+
+
 class Linear:
     """``epi`` STORE: out = x W^T + b.  RESIDUAL: out (fp32) += x W^T + b.
     GATED: W = [gate; up]: out = silu(x Wg^T) * (x Wu^T)."""
@@ -52,12 +78,16 @@ class Linear:
 
             self._fast = fast_linear.plan(self)
 
-    def __call__(self, out: Optional[torch.Tensor], x: torch.Tensor, defer: bool = False) -> Optional[Partial]:
-        """Run the product.  With ``defer`` the result may come back as a
-        :class:`Partial` (``out`` is then untouched); else None."""
+    def __call__(self, out: Optional[torch.Tensor], x, defer: bool = False) -> Optional[Partial]:
+        """Run the product.  ``x`` is a tensor of rows, or rows still to be
+        made (:class:`MergedSplits`).  With ``defer`` the
+        result may come back as a :class:`Partial` (``out`` is then
+        untouched); else None."""
         if self._fast is not None and x.dtype == torch.bfloat16:
             done = self._fast(out, x, defer)
             if done is not False:
                 return done if isinstance(done, Partial) else None
+        if not isinstance(x, torch.Tensor):
+            x = x.rows()
         ops.gemm_generic(out, x, self.weight, self.bias, self.epi)
         return None

@@ -95,3 +95,38 @@ def test_program_is_refused_for_shapes_it_does_not_take(model_folders):
     runner.forward([StepEntry(slot, [4], [0])])
     runner.check_status()
     assert runner._graphs[1].program is None
+
+
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_prompt_steps_of_a_repeated_shape_are_replayed_as_graphs(folders, name):
+    """Steps with prompt portions whose shape (tokens, requests, wanted rows)
+    repeats are recorded as CUDA graphs at the third occurrence and replayed
+    after it: the same shape with the tokens divided differently among the
+    requests, with a decode token beside a prompt, and with earlier context,
+    against the plain implementation."""
+    from alofa_b200.engine.step import StepEntry
+
+    wts, cfg = plain.load(folders[name])
+    vocab = configs()[name][0].vocab_size
+    rng = np.random.default_rng(9)
+    runner = runner_for(folders[name], False, pages=60)
+    assert runner.prompt_graphs
+    key = (200, 2, 2)
+    # (tokens of the first request, of the second) per step: always 200 tokens, two requests, two wanted rows
+    for step, (a, b) in enumerate([(120, 80), (10, 190), (199, 1), (150, 50), (64, 136), (1, 199)]):
+        seqs = [[int(t) for t in rng.integers(0, vocab, n + 3)] for n in (a + 70, b + 70)]
+        want = [plain.forward(s, wts, cfg) for s in seqs]
+        slots = [runner.admit(10 * step + i) for i in range(2)]
+        # 70 earlier tokens each (a step of another shape), then the step of the repeated shape, then a decoded token
+        runner.forward([StepEntry(slots[0], seqs[0][:70], []), StepEntry(slots[1], seqs[1][:70], [])])
+        got = runner.forward([StepEntry(slots[0], seqs[0][70 : 70 + a], [a - 1]), StepEntry(slots[1], seqs[1][70 : 70 + b], [b - 1])]).float().cpu().numpy()
+        assert (key in runner._graphs) == (step >= 2), f"step {step}: graphs {list(runner._graphs)}"
+        nxt = runner.forward([StepEntry(slots[0], [seqs[0][70 + a]], [0]), StepEntry(slots[1], [seqs[1][70 + b]], [0])]).float().cpu().numpy()
+        for i, n in enumerate((a, b)):
+            for row, ref in ((got[i], want[i][70 + n - 1]), (nxt[i], want[i][70 + n])):
+                bound = 2e-2 * max(1.0, float(np.abs(ref).max()))
+                assert np.abs(row - ref).max() <= bound, f"{name} step {step} request {i}: {np.abs(row - ref).max():.3e} > {bound:.3e}"
+        for s in slots:
+            runner.release(s)
+    runner.check_status()
+    assert runner.manager.defects() == 0
