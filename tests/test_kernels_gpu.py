@@ -301,6 +301,51 @@ def test_attention_window_edge(ops, dtype, window):
         assert_close(got, want, TOL[dtype], f"window {window} offset {offset}")
 
 
+@pytest.mark.parametrize("hd, nh, nkv, window", [(64, 14, 2, None), (32, 3, 1, 300), (128, 4, 4, None), (48, 5, 5, 700)])
+def test_output_product_merges_the_key_splits(ops, hd, nh, nkv, window):
+    """Decode tokens whose key splits are left unmerged, and the residual
+    product that merges them while it loads its operand, against the merge
+    kernel followed by the plain product, and against fp64: one to sixteen
+    tokens, lengths on both sides of the split edges, products with one and
+    with several k-slices per CTA."""
+    rng = np.random.default_rng(hd)
+    for lens in ([600], [1, 255, 256, 257, 900, 3000, 512, 64, 4000, 33, 1023, 1024, 1025, 2047, 2048, 2049]):
+        n = len(lens)
+        ks = [rounded(rng.normal(size=(m, nkv * hd)), BF16) for m in lens]
+        vs = [rounded(rng.normal(size=(m, nkv * hd)), BF16) for m in lens]
+        qs = [rounded(rng.normal(size=(m, nh * hd)), BF16) for m in lens]
+        k_cache, v_cache, table = paged_from_sequences(ks, vs, 64, nkv, hd, BF16, rng)
+        q = dev(np.stack([qs[i][-1] for i in range(n)]), BF16)
+        positions = dev(np.array([m - 1 for m in lens], dtype=np.int32))
+        kv_len = dev(np.array(lens, dtype=np.int32))
+        q_start = dev(np.arange(n + 1, dtype=np.int32))
+        splits = -(-max(lens) // 256)
+        po = torch.zeros(splits, n * nh, hd, device="cuda")
+        pml = torch.zeros(splits, n * nh, 2, device="cuda")
+        unused = torch.full((n, nh * hd), 7.0, dtype=BF16, device="cuda")
+        ops.attention_bf16(unused, q, k_cache, v_cache, q_start, kv_len, positions, table, 64, n, 1, nh, nkv, hd, window, hd ** -0.5, splits, 256, po, pml, combine=False)
+        assert float(unused.float().min()) == 7.0, "the attention kernel was told not to merge"
+        merged = torch.empty(n, nh * hd, dtype=BF16, device="cuda")
+        ops.attention_combine(merged, po, pml, positions, nh, hd, window, 256)
+        want_attn = np.stack([plain.attention(qs[i], ks[i], vs[i], nh, nkv, hd, window)[-1] for i in range(n)])
+        assert_close(merged.float().cpu(), want_attn, TOL[BF16], "merged splits")
+        feats = 200
+        w = rounded(rng.normal(size=(feats, nh * hd)) / np.sqrt(nh * hd), BF16)
+        res = rng.normal(size=(n, feats)).astype(np.float32)
+        for k_splits in (1, 4, ops.gemm_tc_splits(nh * hd, 64)):
+            real = ops.gemm_tc_splits(nh * hd, k_splits)
+            if splits > 16:
+                continue  # more key splits than the product merges: the caller merges first
+            part = torch.empty(real, n, feats, device="cuda") if real > 1 else None
+            fused, plain_way = dev(res), dev(res)
+            computed = (ops.B_MERGED_SPLITS, po, pml, positions, nh, hd, window, 256)
+            assert ops.gemm_tc(fused, None, dev(w, BF16), None, ops.EPI_RESIDUAL, 16, k_splits, part, computed=computed)
+            part2 = torch.empty(real, n, feats, device="cuda") if real > 1 else None
+            assert ops.gemm_tc(plain_way, merged, dev(w, BF16), None, ops.EPI_RESIDUAL, 16, k_splits, part2)
+            assert torch.equal(fused, plain_way), f"merging in the product changes bits (k splits {real})"
+            assert_close(fused.cpu(), res + plain.linear(rounded(want_attn, BF16), w), 2e-2, f"product of merged splits (k splits {real})")
+
+
 @pytest.mark.parametrize("hd, nh, nkv", [(16, 4, 2), (32, 3, 1), (48, 5, 5), (64, 14, 2), (80, 6, 3), (128, 8, 1)])
 @pytest.mark.parametrize("page", [16, 48, 64])
 def test_attention_bf16_sizes_portions_and_windows(ops, hd, nh, nkv, page):
