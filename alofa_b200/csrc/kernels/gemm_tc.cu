@@ -49,6 +49,7 @@ struct GemmArgs {
   const float* b_ml;        // merged splits: (maximum, sum) [splits, T * heads, 2]
   const int* b_positions;   // merged splits: position of each token
   int b_heads, b_head_dim, b_window, b_split_keys;
+  int cluster;              // the splits of a tile are a thread-block cluster and add their sums up themselves (MODE_CLUSTER)
 #ifdef ALOFA_GEMM_TIMING
   long long* stamps;  // [8] clock64 of CTA (0,0,0): start, after setup, first data, accumulator done, epilogue done, end
 #endif
@@ -122,11 +123,31 @@ __device__ __forceinline__ uint4 merged_splits8(const GemmArgs& a, int t, int k0
   return pack8(v);
 }
 
-// COMPUTED: the token operand is made by the epilogue warps (GemmArgs::b_kind); a variant of
-// its own, so that the plain kernel keeps its small register count and the next kernel's
-// CTAs can become resident beside it under programmatic dependent launch.
-template <int BN, int EPI, bool COMPUTED = false>
-__global__ void __launch_bounds__(NUM_THREADS, COMPUTED ? 2 : 1)
+// Variants (kernels of their own, so that the plain one keeps its small register count and the
+// next kernel's CTAs can become resident beside it under programmatic dependent launch):
+// MODE_COMPUTED: the token operand is made by the epilogue warps (GemmArgs::b_kind).
+// MODE_CLUSTER: the CTAs that split the depth of a tile form a thread-block cluster along z; the
+// others push their accumulators into the shared memory of the first, which adds them in split
+// order and runs the epilogue - no partial sums in global memory, no second kernel.
+enum { MODE_PLAIN = 0, MODE_COMPUTED = 1, MODE_CLUSTER = 2 };
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {  // every thread of every CTA of the cluster, exactly once
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void store_remote_f32(uint32_t local_smem_addr, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+template <int BN, int EPI, int MODE = MODE_PLAIN>
+__global__ void __launch_bounds__(NUM_THREADS, MODE == MODE_COMPUTED ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args, const int stages) {
   constexpr int N_ACC = (EPI == EPI_GATED) ? 2 : 1;
   constexpr uint32_t A_BYTES = BM * BK * 2;
@@ -154,7 +175,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int slice_end = min(total_slices, slice_begin + args.k_slices_per_split);
   const int n_slices = slice_end - slice_begin;
 
+  constexpr bool COMPUTED = MODE == MODE_COMPUTED, CLUSTER = MODE == MODE_CLUSTER;
   constexpr bool computed_b = COMPUTED;
+  const uint32_t rank = CLUSTER ? cluster_rank() : 0;  // this CTA's split of the depth, within its cluster
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
@@ -180,6 +203,104 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #ifdef ALOFA_GEMM_TIMING
   if (probe && threadIdx.x == 0) args.stamps[1] = clock64();
 #endif
+
+  // The epilogue of the four epilogue warps: warp q reads lanes [32q, 32q + 32) of the accumulator.
+  // with_remote (first CTA of a cluster): the other CTAs' accumulators, pushed into `pushed`
+  // [rank - 1][accumulator][token][feature], are added in rank order first.
+  bool epilogue_ok = false;
+  float* pushed = reinterpret_cast<float*>(tiles + (size_t)stages * STAGE_BYTES);
+  auto epilogue = [&](bool with_remote) {
+    const int q = warp & 3;
+    const int f = f0 + q * 32 + lane;
+    const bool f_ok = f < args.N;
+    const bool split = gridDim.z > 1 && !CLUSTER;
+    const bool push = CLUSTER && rank != 0;
+    float bias0 = 0.f, bias1 = 0.f;
+    if (!split && !push && args.bias && f_ok) {
+      bias0 = args.bias[f];
+      if (N_ACC == 2) bias1 = args.bias[args.N + f];
+    }
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      if (t0 + c0 >= args.T) break;
+      uint32_t r0[16], r1[16];
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+      if (n_slices > 0) {
+        tmem_ld16(taddr, r0);
+        if (N_ACC == 2) tmem_ld16(taddr + CHAINS * BN, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 1; c < CHAINS; ++c) {
+          uint32_t x0[16], x1[16];
+          tmem_ld16(taddr + c * BN, x0);
+          if (N_ACC == 2) tmem_ld16(taddr + (CHAINS + c) * BN, x1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __uint_as_float(x0[j]));
+            if (N_ACC == 2) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __uint_as_float(x1[j]));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r0[j] = r1[j] = 0u;
+      }
+      if constexpr (CLUSTER) {
+        const int row = q * 32 + lane;
+        if (push) {  // this CTA's sums into the first CTA's shared memory; nothing goes to global memory
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            store_remote_f32(smem_u32(pushed + (((rank - 1) * N_ACC + 0) * BN + c0 + j) * 128 + row), 0, __uint_as_float(r0[j]));
+            if (N_ACC == 2) store_remote_f32(smem_u32(pushed + (((rank - 1) * N_ACC + 1) * BN + c0 + j) * 128 + row), 0, __uint_as_float(r1[j]));
+          }
+          continue;
+        }
+        if (with_remote) {
+          for (uint32_t z = 1; z < gridDim.z; ++z) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + pushed[(((z - 1) * N_ACC + 0) * BN + c0 + j) * 128 + row]);
+              if (N_ACC == 2) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + pushed[(((z - 1) * N_ACC + 1) * BN + c0 + j) * 128 + row]);
+            }
+          }
+        }
+      }
+      if (!f_ok) continue;
+      const int t_base = t0 + c0;
+      if (!split && EPI == EPI_RESIDUAL) {
+        // read the 16 residual values first, then write: the loads overlap
+        float* o = (float*)args.out + (size_t)t_base * args.N + f;
+        float prev[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) prev[j] = (t_base + j < args.T) ? o[(size_t)j * args.N] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (t_base + j < args.T) o[(size_t)j * args.N] = prev[j] + (__uint_as_float(r0[j]) + bias0);
+        continue;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int t = t_base + j;
+        if (t >= args.T) break;
+        const float a0 = __uint_as_float(r0[j]);
+        if (split) {
+          const size_t plane = (size_t)args.T * args.N;
+          float* p = args.partial + (size_t)blockIdx.z * N_ACC * plane + (size_t)t * args.N + f;
+          p[0] = a0;
+          if (N_ACC == 2) p[plane] = __uint_as_float(r1[j]);
+        } else if (EPI == EPI_GATED) {
+          const float g = a0 + bias0, u = __uint_as_float(r1[j]) + bias1;
+          const float y = g / (1.0f + __expf(-g)) * u;
+          if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
+          else ((float*)args.out)[(size_t)t * args.N + f] = y;
+        } else {
+          const float y = a0 + bias0;
+          if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
+          else ((float*)args.out)[(size_t)t * args.N + f] = y;
+        }
+      }
+    }
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -222,10 +343,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       umma_commit(&acc_bar);  // the accumulator is complete once all MMAs are done
     }
   } else {
-    // ---- epilogue: 4 warps, warp q reads lanes [32q, 32q + 32) ------------------
-    const int q = warp & 3;
-    const int f = f0 + q * 32 + lane;
-    const bool f_ok = f < args.N;
+    // ---- the four epilogue warps ------------------------------------------------
     if constexpr (COMPUTED) {
       // First the token operand, slice by slice: rows of 128 bytes, 16-byte chunk c of row r at
       // c ^ (r & 7).  The host allows this for tiles of 16 tokens only: one chunk per thread.
@@ -248,74 +366,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #ifdef ALOFA_GEMM_TIMING
     if (probe && warp == 2 && lane == 0) args.stamps[3] = clock64();
 #endif
-    if (ok) {
-      const bool split = gridDim.z > 1;
-      float bias0 = 0.f, bias1 = 0.f;
-      if (!split && args.bias && f_ok) {
-        bias0 = args.bias[f];
-        if (N_ACC == 2) bias1 = args.bias[args.N + f];
-      }
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (t0 + c0 >= args.T) break;
-        uint32_t r0[16], r1[16];
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
-        if (n_slices > 0) {
-          tmem_ld16(taddr, r0);
-          if (N_ACC == 2) tmem_ld16(taddr + CHAINS * BN, r1);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 1; c < CHAINS; ++c) {
-            uint32_t x0[16], x1[16];
-            tmem_ld16(taddr + c * BN, x0);
-            if (N_ACC == 2) tmem_ld16(taddr + (CHAINS + c) * BN, x1);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __uint_as_float(x0[j]));
-              if (N_ACC == 2) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __uint_as_float(x1[j]));
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) r0[j] = r1[j] = 0u;
-        }
-        if (!f_ok) continue;
-        const int t_base = t0 + c0;
-        if (!split && EPI == EPI_RESIDUAL) {
-          // read the 16 residual values first, then write: the loads overlap
-          float* o = (float*)args.out + (size_t)t_base * args.N + f;
-          float prev[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) prev[j] = (t_base + j < args.T) ? o[(size_t)j * args.N] : 0.f;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (t_base + j < args.T) o[(size_t)j * args.N] = prev[j] + (__uint_as_float(r0[j]) + bias0);
-          continue;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int t = t_base + j;
-          if (t >= args.T) break;
-          const float a0 = __uint_as_float(r0[j]);
-          if (split) {
-            const size_t plane = (size_t)args.T * args.N;
-            float* p = args.partial + (size_t)blockIdx.z * N_ACC * plane + (size_t)t * args.N + f;
-            p[0] = a0;
-            if (N_ACC == 2) p[plane] = __uint_as_float(r1[j]);
-          } else if (EPI == EPI_GATED) {
-            const float g = a0 + bias0, u = __uint_as_float(r1[j]) + bias1;
-            const float y = g / (1.0f + __expf(-g)) * u;
-            if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
-            else ((float*)args.out)[(size_t)t * args.N + f] = y;
-          } else {
-            const float y = a0 + bias0;
-            if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
-            else ((float*)args.out)[(size_t)t * args.N + f] = y;
-          }
-        }
-      }
-    }
+    epilogue_ok = ok;
+    if (ok && !(CLUSTER && rank == 0)) epilogue(false);  // in a cluster the first CTA waits for the others' sums
+  }
+  if constexpr (CLUSTER) {
+    cluster_sync_all();  // the pushed accumulators are in the first CTA's shared memory
+    if (warp >= 2 && rank == 0 && epilogue_ok) epilogue(true);
   }
 #ifdef ALOFA_GEMM_TIMING
   if (probe && warp == 2 && lane == 0) args.stamps[4] = clock64();
@@ -833,15 +889,49 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
     if constexpr (BN == 16 && EPI == EPI_RESIDUAL) {
       static bool configured_c = false;
       if (!configured_c) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, MODE_COMPUTED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
           return ALOFA_ERR_LAUNCH;
-        prefer_max_shared(gemm_tc_kernel<BN, EPI, true>);
+        prefer_max_shared(gemm_tc_kernel<BN, EPI, MODE_COMPUTED>);
         configured_c = true;
       }
-      launch_dep(gemm_tc_kernel<BN, EPI, true>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
+      launch_dep(gemm_tc_kernel<BN, EPI, MODE_COMPUTED>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
       return launch_status();
     } else {
       return ALOFA_ERR_ARGUMENT;  // a computed operand feeds residual products of up to 16 tokens
+    }
+  }
+  if (args.cluster) {
+    if constexpr (BN == 16 && EPI == EPI_GATED) {
+      // room behind the ring for the accumulators the other CTAs of a cluster push
+      const size_t pushed = (size_t)(splits - 1) * N_ACC * BN * 128 * sizeof(float);
+      int cstages = (int)((200 * 1024 - pushed) / STAGE);
+      if (cstages > 12) cstages = 12;
+      if (cstages < 2) return ALOFA_ERR_ARGUMENT;
+      static bool configured_k = false;
+      if (!configured_k) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, MODE_CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
+          return ALOFA_ERR_LAUNCH;
+        prefer_max_shared(gemm_tc_kernel<BN, EPI, MODE_CLUSTER>);
+        configured_k = true;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(NUM_THREADS);
+      cfg.dynamicSmemBytes = STAGE * cstages + pushed + 1024;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+      attr[1].id = cudaLaunchAttributeClusterDimension;
+      attr[1].val.clusterDim.x = 1;
+      attr[1].val.clusterDim.y = 1;
+      attr[1].val.clusterDim.z = (unsigned)splits;
+      cfg.attrs = attr;
+      cfg.numAttrs = 2;
+      cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, MODE_CLUSTER>, mw, mx, args, cstages);
+      return launch_status();
+    } else {
+      return ALOFA_ERR_ARGUMENT;
     }
   }
   launch_dep(gemm_tc_kernel<BN, EPI>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
@@ -927,6 +1017,18 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 // reduce kernel after (else the caller's next kernel adds the partials up).
 // Returns ALOFA_ERR_ARGUMENT for sizes this kernel does not take (K % 8 != 0,
 // pointers not 16-byte aligned).
+// Whether a product with these settings adds its split sums up inside a thread-block cluster
+// (no partial sums in global memory, no second kernel): gated products of up to 16 tokens
+// split two to eight ways.
+ALOFA_API int alofa_gemm_tc_reduces_in_cluster(int epi, int bn, int splits) {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* env = getenv("ALOFA_GEMM_CLUSTER");
+    enabled = (env && env[0] == '0') ? 0 : 1;
+  }
+  return enabled && epi == EPI_GATED && bn == 16 && splits >= 2 && splits <= 8;
+}
+
 // b_kind = B_MERGED_SPLITS (residual products of up to 16 tokens only): x is ignored and the
 // token operand is computed in the kernel from the attention output of decode tokens still in
 // key splits (b_src partial outputs, b_ml maxima and sums, b_positions; heads * head_dim == K).
@@ -977,6 +1079,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   args.b_head_dim = b_head_dim;
   args.b_window = b_window;
   args.b_split_keys = b_split_keys;
+  args.cluster = alofa_gemm_tc_reduces_in_cluster(epi, bn, splits) && do_reduce && b_kind == B_ROWS;
 #ifdef ALOFA_GEMM_TIMING
   args.stamps = (long long*)status;  // the timing build reuses the status pointer for its stamps
   args.status = nullptr;
@@ -991,7 +1094,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   else if (epi == EPI_RESIDUAL) rc = dispatch_bn<EPI_RESIDUAL>(bn, mw, mx, args, splits, stream);
   else if (epi == EPI_GATED) rc = dispatch_bn<EPI_GATED>(bn, mw, mx, args, splits, stream);
   else return ALOFA_ERR_ARGUMENT;
-  if (rc != ALOFA_OK || splits == 1 || !do_reduce) return rc;
+  if (rc != ALOFA_OK || splits == 1 || !do_reduce || args.cluster) return rc;
   const size_t plane = (size_t)T * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)((plane + threads - 1) / threads);

@@ -74,6 +74,8 @@ def _gemm_tc():
         lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P]
         lib.alofa_splitk_reduce.restype = _I
         lib.alofa_splitk_reduce.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _P]
+        lib.alofa_gemm_tc_reduces_in_cluster.restype = _I
+        lib.alofa_gemm_tc_reduces_in_cluster.argtypes = [_I, _I, _I]
         lib.alofa_gemm_tc_splits.restype = _I
         lib.alofa_gemm_tc_splits.argtypes = [_I, _I]
         _libs["gemm_tc"] = lib
@@ -373,8 +375,8 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
     if rc == 1:
         return False
     _done(rc, "gemm_tc", f"M={m} N={n} K={k} epi={epi} bn={bn} splits={splits}")
-    if splits > 1 and reduce:
-        count_launches(1)
+    if splits > 1 and reduce and not _gemm_tc().alofa_gemm_tc_reduces_in_cluster(epi, bn, splits):
+        count_launches(1)  # the kernel that adds the split sums up
     return True
 
 
