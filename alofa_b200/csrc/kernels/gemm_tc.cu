@@ -901,7 +901,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
     }
   }
   if (args.cluster) {
-    if constexpr (BN == 16 && EPI == EPI_GATED) {
+    if constexpr ((BN == 16 || BN == 32) && EPI == EPI_GATED) {
       // room behind the ring for the accumulators the other CTAs of a cluster push
       const size_t pushed = (size_t)(splits - 1) * N_ACC * BN * 128 * sizeof(float);
       int cstages = (int)((200 * 1024 - pushed) / STAGE);
@@ -1019,14 +1019,15 @@ static int dispatch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, con
 // pointers not 16-byte aligned).
 // Whether a product with these settings adds its split sums up inside a thread-block cluster
 // (no partial sums in global memory, no second kernel): gated products of up to 16 tokens
-// split two to eight ways.
+// split two to eight ways, of up to 32 tokens split two to four ways (the pushed sums must fit
+// in shared memory beside the ring).
 ALOFA_API int alofa_gemm_tc_reduces_in_cluster(int epi, int bn, int splits) {
   static int enabled = -1;
   if (enabled < 0) {
     const char* env = getenv("ALOFA_GEMM_CLUSTER");
     enabled = (env && env[0] == '0') ? 0 : 1;
   }
-  return enabled && epi == EPI_GATED && bn == 16 && splits >= 2 && splits <= 8;
+  return enabled && epi == EPI_GATED && (bn == 16 || (bn == 32 && splits <= 4)) && splits >= 2 && splits <= 8;
 }
 
 // b_kind = B_MERGED_SPLITS (residual products of up to 16 tokens only): x is ignored and the

@@ -180,7 +180,7 @@ def test_rope_store_fused_from_tensor_and_from_partial_sums(ops, hd):
 
 
 @pytest.mark.parametrize("shape", [(5, 128, 64, 16, 1), (33, 379, 96, 64, 1), (300, 1152, 896, 128, 3), (8, 896, 4864, 16, 19), (513, 640, 320, 256, 2),
-                                   (8, 512, 896, 16, 3), (13, 200, 320, 16, 5), (16, 131, 512, 16, 8),  # gated: the splits add up inside a cluster
+                                   (8, 512, 896, 16, 3), (13, 200, 320, 16, 5), (16, 131, 512, 16, 8), (29, 640, 896, 32, 3),  # gated: the splits add up inside a cluster
                                    (5, 128, 64, -64, 1), (130, 379, 96, -128, 1), (300, 1152, 896, -256, 3), (513, 650, 320, -256, 2), (257, 200, 240, -128, 1)])
 def test_gemm_tc_epilogues_and_split_depth(ops, shape):
     """The tcgen05 product against fp64: every epilogue, ragged sizes, split
