@@ -21,10 +21,12 @@
 // Every wait on an mbarrier is bounded: after the limit the CTA raises the
 // status word, skips its remaining work, frees its tensor memory and returns.
 #include "common.cuh"
+#include <string.h>
+
 #include "tcgen05.cuh"
 #include "tma.cuh"
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED = 2 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED = 2, EPI_ROPE = 3 };  // EPI_ROPE: weights-on-M tiles of 16 tokens only
 enum { B_ROWS = 0, B_MERGED_SPLITS = 1 };
 
 constexpr int BM = 128;        // features per CTA (UMMA M)
@@ -50,6 +52,15 @@ struct GemmArgs {
   const int* b_positions;   // merged splits: position of each token
   int b_heads, b_head_dim, b_window, b_split_keys;
   int cluster;              // the splits of a tile are a thread-block cluster and add their sums up themselves (MODE_CLUSTER)
+  // EPI_ROPE: the weight is [q heads | k heads | v heads] stacked; the epilogue adds the bias, rotates q and k
+  // (NeoX halves, cos/sin from a table by position) and writes q to its buffer, k and v to their cache slots
+  bf16* rope_q;             // [T, heads * head_dim]
+  bf16* rope_k;             // cache [slots, kv_heads, head_dim]
+  bf16* rope_v;
+  const int* rope_slots;    // [T] cache slot of each token, negative: not written
+  const int* rope_positions;
+  const float* rope_table;  // [positions, head_dim / 2, 2]
+  int rope_heads, rope_kv_heads, rope_head_dim;
 #ifdef ALOFA_GEMM_TIMING
   long long* stamps;  // [8] clock64 of CTA (0,0,0): start, after setup, first data, accumulator done, epilogue done, end
 #endif
@@ -199,6 +210,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int t = t0 + ((threadIdx.x - 64) >> 3);
     if (t < args.T) token_pos = args.b_positions[t];
   }
+  // Rotate-and-store: each epilogue thread's cosines and sines (one feature, 16 tokens) and the
+  // tokens' cache slots.  Positions and slots came with the step's metadata and the table is a
+  // constant of the model, so they too may be read ahead of the wait.
+  float2 rope_cs[EPI == EPI_ROPE ? 16 : 1];
+  int rope_slot[EPI == EPI_ROPE ? 16 : 1];
+  if constexpr (EPI == EPI_ROPE) {
+    if (warp >= 2 && rank == 0) {
+      const int row = ((warp & 3) << 5) + lane, hd = args.rope_head_dim, half = hd >> 1;
+      const int d = row % hd, i = d < half ? d : d - half;
+      const bool rotated = (f0 + row) / hd < args.rope_heads + args.rope_kv_heads;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int t = t0 + j;
+        rope_cs[j] = make_float2(1.f, 0.f);
+        rope_slot[j] = -1;
+        if (t < args.T) {
+          if (rotated) rope_cs[j] = *reinterpret_cast<const float2*>(args.rope_table + ((size_t)args.rope_positions[t] * half + i) * 2);
+          if (args.rope_slots) rope_slot[j] = args.rope_slots[t];
+        }
+      }
+    }
+  }
   pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
 #ifdef ALOFA_GEMM_TIMING
   if (probe && threadIdx.x == 0) args.stamps[1] = clock64();
@@ -209,6 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // [rank - 1][accumulator][token][feature], are added in rank order first.
   bool epilogue_ok = false;
   float* pushed = reinterpret_cast<float*>(tiles + (size_t)stages * STAGE_BYTES);
+  float* rope_xchg = pushed + (CLUSTER ? (size_t)(gridDim.z - 1) * N_ACC * BN * 128 : 0);  // EPI_ROPE: [16 tokens][128 features]
   auto epilogue = [&](bool with_remote) {
     const int q = warp & 3;
     const int f = f0 + q * 32 + lane;
@@ -264,6 +298,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
           }
         }
+      }
+      if constexpr (EPI == EPI_ROPE) {
+        // Rotate-and-store.  A thread holds one feature of 16 tokens; its rotation partner, half a
+        // head away, is another thread of this CTA (a tile of 128 features holds whole heads): the
+        // values change hands through shared memory, [token][feature] so that no bank is hit twice.
+        const int row = q * 32 + lane, hd = args.rope_head_dim, half = hd >> 1;
+        float v[16], pv[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          v[j] = __uint_as_float(r0[j]) + bias0;
+          rope_xchg[j * 128 + row] = v[j];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        const int d = row % hd;  // tiles start at multiples of 128, which head_dim divides
+        const int partner = d < half ? row + half : row - half;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pv[j] = rope_xchg[j * 128 + partner];
+        if (!f_ok) continue;
+        const int head = f / hd;
+        const bool is_q = head < args.rope_heads, is_k = !is_q && head < args.rope_heads + args.rope_kv_heads;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + c0 + j;
+          if (t >= args.T) break;
+          const float2 cs = rope_cs[j];  // (1, 0) for the value heads
+          const float y = d < half ? v[j] * cs.x - pv[j] * cs.y : v[j] * cs.x + pv[j] * cs.y;
+          if (is_q) {
+            args.rope_q[(size_t)t * args.rope_heads * hd + f] = __float2bfloat16_rn(y);
+          } else {
+            const int slot = rope_slot[j];
+            if (slot < 0) continue;
+            if (is_k) args.rope_k[((size_t)slot * args.rope_kv_heads + (head - args.rope_heads)) * hd + d] = __float2bfloat16_rn(y);
+            else args.rope_v[((size_t)slot * args.rope_kv_heads + (head - args.rope_heads - args.rope_kv_heads)) * hd + d] = __float2bfloat16_rn(y);
+          }
+        }
+        continue;
       }
       if (!f_ok) continue;
       const int t_base = t0 + c0;
@@ -872,10 +942,11 @@ template <int BN, int EPI>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& args, int splits, cudaStream_t stream) {
   constexpr int N_ACC = (EPI == EPI_GATED) ? 2 : 1;
   constexpr size_t STAGE = (size_t)N_ACC * BM * BK * 2 + (size_t)BN * BK * 2;
-  int stages = (int)((200 * 1024) / STAGE);
+  constexpr size_t XCHG = (EPI == EPI_ROPE) ? 16 * 128 * sizeof(float) : 0;  // where rotation partners swap values
+  int stages = (int)((200 * 1024 - XCHG) / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) return ALOFA_ERR_ARGUMENT;
-  const size_t smem = STAGE * stages + 1024;
+  const size_t smem = STAGE * stages + XCHG + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
@@ -901,9 +972,9 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
     }
   }
   if (args.cluster) {
-    if constexpr ((BN == 16 || BN == 32) && EPI == EPI_GATED) {
+    if constexpr (((BN == 16 || BN == 32) && EPI == EPI_GATED) || (BN == 16 && EPI == EPI_ROPE)) {
       // room behind the ring for the accumulators the other CTAs of a cluster push
-      const size_t pushed = (size_t)(splits - 1) * N_ACC * BN * 128 * sizeof(float);
+      const size_t pushed = (size_t)(splits - 1) * N_ACC * BN * 128 * sizeof(float) + XCHG;
       int cstages = (int)((200 * 1024 - pushed) / STAGE);
       if (cstages > 12) cstages = 12;
       if (cstages < 2) return ALOFA_ERR_ARGUMENT;
@@ -1119,6 +1190,48 @@ ALOFA_API int alofa_splitk_reduce(void* out, const float* partial, const float* 
   else if (epi == EPI_GATED) launch_dep(splitk_reduce_kernel<EPI_GATED>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
   else return ALOFA_ERR_ARGUMENT;
   return launch_status();
+}
+
+// q/k/v of up to 16 tokens in one kernel: x [T, K] bf16 times the stacked weight w
+// [(heads + 2 kv_heads) * head_dim, K] (heads * head_dim rows when the layer reads another
+// layer's cache: kv_heads = 0), bias, NeoX rotation of q and k by `table`
+// [positions, head_dim / 2, 2] at `positions`, q to q_out [T, heads * head_dim], k and v to
+// their cache slots.  The depth is split over a cluster of up to 8 CTAs that add their sums up
+// themselves.  head_dim must divide 128 (a tile of 128 weight rows then holds whole heads).
+ALOFA_API int alofa_gemm_tc_rope(const void* x, const void* w, const float* bias, int T, int K, void* q_out, void* k_cache, void* v_cache,
+                                 const int* slots, const int* positions, const float* table, int heads, int kv_heads, int head_dim,
+                                 int splits, int* status, cudaStream_t stream) {
+  if (T <= 0) return ALOFA_OK;
+  const int N = (heads + 2 * kv_heads) * head_dim;
+  if (T > 16 || K <= 0 || (K % 8) != 0 || head_dim <= 0 || 128 % head_dim || head_dim % 2 || heads <= 0) return ALOFA_ERR_ARGUMENT;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || !q_out || !positions || !table || (kv_heads > 0 && (!k_cache || !v_cache || !slots))) return ALOFA_ERR_ARGUMENT;
+  const int total_slices = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > 8) splits = 8;
+  if (splits > total_slices) splits = total_slices;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, w, N, K, BM) || !make_map(&mx, x, T, K, 16)) return ALOFA_ERR_ARGUMENT;
+  GemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.bias = bias;
+  args.T = T;
+  args.N = N;
+  args.K = K;
+  args.k_slices_per_split = (total_slices + splits - 1) / splits;
+  splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;
+  args.status = status;
+  args.b_kind = B_ROWS;
+  args.cluster = splits > 1;
+  args.rope_q = (bf16*)q_out;
+  args.rope_k = (bf16*)k_cache;
+  args.rope_v = (bf16*)v_cache;
+  args.rope_slots = slots;
+  args.rope_positions = positions;
+  args.rope_table = table;
+  args.rope_heads = heads;
+  args.rope_kv_heads = kv_heads;
+  args.rope_head_dim = head_dim;
+  return launch_tc<16, EPI_ROPE>(mw, mx, args, splits, stream);
 }
 
 // How many splits alofa_gemm_tc will really use (it never leaves one empty).

@@ -76,6 +76,8 @@ def _gemm_tc():
         lib.alofa_splitk_reduce.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _P]
         lib.alofa_gemm_tc_reduces_in_cluster.restype = _I
         lib.alofa_gemm_tc_reduces_in_cluster.argtypes = [_I, _I, _I]
+        lib.alofa_gemm_tc_rope.restype = _I
+        lib.alofa_gemm_tc_rope.argtypes = [_P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]
         lib.alofa_gemm_tc_splits.restype = _I
         lib.alofa_gemm_tc_splits.argtypes = [_I, _I]
         _libs["gemm_tc"] = lib
@@ -377,6 +379,27 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
     _done(rc, "gemm_tc", f"M={m} N={n} K={k} epi={epi} bn={bn} splits={splits}")
     if splits > 1 and reduce and not _gemm_tc().alofa_gemm_tc_reduces_in_cluster(epi, bn, splits):
         count_launches(1)  # the kernel that adds the split sums up
+    return True
+
+
+def gemm_tc_rope(x, w, bias, q_out, k_cache, v_cache, slot_map, positions, cos_sin, nh: int, nkv: int, hd: int, splits: int, status=None) -> bool:
+    """q/k/v of up to 16 tokens in one kernel: ``x @ w.T + bias`` for the
+    stacked weight [q; k; v] (``nkv`` = 0: q only), q and k rotated, q to
+    ``q_out``, k and v to their cache slots.  False, having launched nothing,
+    when the kernel does not take these sizes."""
+    bf, f32 = torch.bfloat16, torch.float32
+    t, k = x.shape
+    if t > 16 or 128 % hd or w.shape != ((nh + 2 * nkv) * hd, k):
+        return False
+    rc = _gemm_tc().alofa_gemm_tc_rope(
+        _dev(x, "x", bf), _dev(w, "w", bf), _dev(bias, "bias", f32) if bias is not None else None, t, k, _dev(q_out, "q_out", bf),
+        _dev(k_cache, "k_cache", bf) if nkv else None, _dev(v_cache, "v_cache", bf) if nkv else None,
+        _dev(slot_map, "slot_map", torch.int32) if nkv else None, _dev(positions, "positions", torch.int32), _dev(cos_sin, "cos_sin", f32),
+        nh, nkv, hd, splits, _dev(status, "status", torch.int32) if status is not None else None, _stream(),
+    )
+    if rc == 1:
+        return False
+    _done(rc, "gemm_tc_rope", f"T={t} K={k} heads={nh}+2x{nkv} hd={hd}")
     return True
 
 

@@ -93,8 +93,23 @@ class GQAttention(Part):
         custom = getattr(self.position, "apply", None)
         # the vectorised rotate-and-store: bf16, the whole head rotated, head size a multiple of 16
         vectorised = dt == torch.bfloat16 and custom is None and rot == self.hd and self.hd % 16 == 0
-        owed = (self.qkv if writes else self.q_only)(qkv, x, defer=vectorised)
+        lin = self.qkv if writes else self.q_only
         q = ctx.buf((n, self.q_dim), dt)
+        # a handful of tokens: product, bias, rotation and the cache write in one kernel
+        if vectorised and n <= 16 and lin.weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and ops.gemm_tc_rope(
+            x, lin.weight, lin.bias, q, cache.k, cache.v, group.slot_map, ctx.positions, table, self.nh, nkv_in, self.hd, 8, ctx.status
+        ):
+            owed = None
+        else:
+            owed = lin(qkv, x, defer=vectorised)
+            self._rotate_and_store(ctx, q, qkv, owed, cache, group, table, rot, custom, vectorised, nkv_in, writes)
+        attn = self.attend(ctx, q, cache, group)
+        owed = self.out(h, attn, defer=True)
+        if owed is not None:
+            ctx.set_pending(h, owed)
+
+    def _rotate_and_store(self, ctx, q, qkv, owed, cache, group, table, rot, custom, vectorised, nkv_in, writes):
+        n = q.shape[0]
         if vectorised:
             ops.rope_store_fused(
                 q, cache.k, cache.v, None if owed is not None else qkv, owed.sums if owed is not None else None,
@@ -107,10 +122,6 @@ class GQAttention(Part):
                 k_view = qkv[:, self.q_dim : self.q_dim + nkv_in * self.hd].view(n, nkv_in, self.hd)
                 custom(ctx, q_view, k_view)
             ops.rope_store(q, cache.k, cache.v, qkv, table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, rot, writes)
-        attn = self.attend(ctx, q, cache, group)
-        owed = self.out(h, attn, defer=True)
-        if owed is not None:
-            ctx.set_pending(h, owed)
 
     def emit(self, prog, ctx, x, h, cache, writes=True):
         group = ctx.groups[cache.group]

@@ -179,6 +179,46 @@ def test_rope_store_fused_from_tensor_and_from_partial_sums(ops, hd):
         assert_close(v_cache.float().cpu().reshape(40, -1), want_v, TOL[BF16], f"v {source}")
 
 
+@pytest.mark.parametrize("hd, nh, nkv, k", [(64, 14, 2, 896), (32, 3, 1, 96), (128, 4, 2, 512), (64, 3, 0, 192), (16, 5, 5, 64)])
+def test_qkv_product_rotates_and_stores(ops, hd, nh, nkv, k):
+    """q/k/v of a few tokens in one kernel (product, bias, rotation, cache
+    write; the depth split over a cluster) against fp64, and bit for bit
+    against the product followed by the rotate-and-store kernel."""
+    from alofa_b200.config.spec import PartSpec
+    from alofa_b200.parts.base import Runtime
+    from alofa_b200.parts.position import RotaryNeox
+
+    rng = np.random.default_rng(hd + k)
+    table = RotaryNeox(PartSpec("rotary_neox", {"head_dim": hd, "theta": 1e4, "max_position": 900}), Runtime(torch.device("cuda"), BF16)).build_table(900)
+    C = (nh + 2 * nkv) * hd
+    w = rounded(rng.normal(size=(C, k)) / np.sqrt(k), BF16)
+    bias = rng.normal(size=C).astype(np.float32)
+    for n in (1, 7, 16):
+        x = rounded(rng.normal(size=(n, k)), BF16)
+        positions = rng.integers(0, 900, n).astype(np.int32)
+        slots = rng.permutation(40)[:n].astype(np.int32)
+        if n > 3:
+            slots[3] = -1
+        for splits in (1, 8):
+            kc = torch.full((40, max(nkv, 1), hd), 3.0, dtype=BF16, device="cuda")
+            vc = torch.full((40, max(nkv, 1), hd), 3.0, dtype=BF16, device="cuda")
+            q_out = torch.empty(n, nh * hd, dtype=BF16, device="cuda")
+            assert ops.gemm_tc_rope(dev(x, BF16), dev(w, BF16), dev(bias), q_out, kc, vc, dev(slots), dev(positions), table, nh, nkv, hd, splits)
+            qkv = plain.linear(x, w, bias)
+            q, kk, vv = qkv[:, : nh * hd], qkv[:, nh * hd : (nh + nkv) * hd], qkv[:, (nh + nkv) * hd :]
+            assert_close(q_out.float().cpu(), plain.rope(q, positions, nh, hd, 1e4), TOL[BF16], f"q n={n} splits={splits}")
+            if nkv:
+                want_k, want_v = np.full((40, nkv * hd), 3.0), np.full((40, nkv * hd), 3.0)
+                rk = plain.rope(kk, positions, nkv, hd, 1e4)
+                for t, s_ in enumerate(slots):
+                    if s_ >= 0:
+                        want_k[s_], want_v[s_] = rk[t], vv[t]
+                assert_close(kc.float().cpu().reshape(40, -1), want_k, TOL[BF16], f"k n={n} splits={splits}")
+                assert_close(vc.float().cpu().reshape(40, -1), want_v, TOL[BF16], f"v n={n} splits={splits}")
+    assert not ops.gemm_tc_rope(torch.zeros(17, k, dtype=BF16, device="cuda"), dev(w, BF16), None, torch.empty(17, nh * hd, dtype=BF16, device="cuda"),
+                                kc, vc, dev(np.zeros(17, dtype=np.int32)), dev(np.zeros(17, dtype=np.int32)), table, nh, nkv, hd, 4), "more than 16 tokens"
+
+
 @pytest.mark.parametrize("shape", [(5, 128, 64, 16, 1), (33, 379, 96, 64, 1), (300, 1152, 896, 128, 3), (8, 896, 4864, 16, 19), (513, 640, 320, 256, 2),
                                    (8, 512, 896, 16, 3), (13, 200, 320, 16, 5), (16, 131, 512, 16, 8), (29, 640, 896, 32, 3),  # gated: the splits add up inside a cluster
                                    (5, 128, 64, -64, 1), (130, 379, 96, -128, 1), (300, 1152, 896, -256, 3), (513, 650, 320, -256, 2), (257, 200, 240, -128, 1)])
