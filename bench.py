@@ -213,7 +213,9 @@ def run(args) -> dict:
     achieved = main["bytes"] / (main["ms"] * 1e-3) / 1e9
 
     # -- end to end: Engine.generate, host tokens in and out --------------------
-    e2e_new = max(8, min(64, args.steps))
+    # as many new tokens as timed steps: the requests start and end a tick apart each, so a short
+    # run is mostly steps with fewer rows than the batch
+    e2e_new = max(8, min(256, args.steps))
     prompts = [prompt(PROMPT_LEN) for _ in range(args.batch)]
     engine.generate(prompts, max_new_tokens=e2e_new)  # the same run once untimed: records the CUDA graphs it uses
     engine.marks.clear()
