@@ -130,3 +130,45 @@ def test_prompt_steps_of_a_repeated_shape_are_replayed_as_graphs(folders, name):
             runner.release(s)
     runner.check_status()
     assert runner.manager.defects() == 0
+
+
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_engine_variants_generate_the_same_tokens(folders, name):
+    """Random workloads (prompt lengths, new-token counts, a stop token, greedy
+    and temperature rows, more requests than slots, a pool small enough to
+    preempt) through engines that differ only in how steps are issued -
+    overlapped or one after the other, CUDA graphs or plain launches: the
+    kernels and their order are the same, so every token must be."""
+    from alofa_b200.engine.engine import Engine
+    from alofa_b200.sampling.params import SamplingParams
+
+    vocab = configs()[name][0].vocab_size
+    rng = np.random.default_rng(21)
+    rounds = []
+    for _ in range(3):
+        reqs = []
+        for i in range(int(rng.integers(3, 9))):
+            prompt = [int(t) for t in rng.integers(0, vocab, int(rng.integers(1, 400)))]
+            temp = float(rng.choice([0.0, 0.0, 0.7]))
+            reqs.append((prompt, SamplingParams(temperature=temp, seed=int(rng.integers(1, 1 << 30)), max_new_tokens=int(rng.integers(1, 40)),
+                                                stop_token_ids=(int(rng.integers(0, vocab)), int(rng.integers(0, vocab))))))
+        rounds.append(reqs)
+    outputs = {}
+    for overlap in (True, False):
+        for graphs in (True, False):
+            eng = Engine(str(folders[name]), dtype="bfloat16", block_size=64, max_batch=4, token_budget=160, max_chunk=128, max_tokens=512,
+                         capacity_blocks=14, admission="optimistic", overlap_steps=overlap, cuda_graphs=graphs)
+            got = []
+            for reqs in rounds:  # the same engine serves round after round: graphs and pages are reused
+                ids = [eng.add_request(p, params) for p, params in reqs]
+                eng.run()
+                done = dict(eng.pop_finished())
+                got.append([done[i] for i in ids])
+                stats = eng.stats()
+                assert stats["defects"] == 0 and stats["live"] == 0 and all(u == 0 for u in stats["used_pages"])
+            eng.runner.check_status()
+            outputs[(overlap, graphs)] = got
+    first = outputs[(False, False)]
+    for key, got in outputs.items():
+        assert got == first, f"overlap={key[0]} graphs={key[1]} differs from plain stepping"
+    assert any(len(out) > 5 for round_out in first for out in round_out)
