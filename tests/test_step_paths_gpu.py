@@ -1,5 +1,7 @@
-"""The decode step as one resident kernel (a program of phases) against the
-plain implementation and against the same steps launched kernel by kernel:
+"""The ways a step can be issued, against the plain implementation and against
+each other: kernel by kernel, as CUDA graphs (decode steps; prompt steps of a
+repeated shape), overlapped with the step before, and the decode step as one
+resident kernel (a program of phases).  The program against the launches:
 two small configurations that the program kernel takes (head sizes 64 and 128,
 widths that are multiples of 32, a vocabulary that is no multiple of 8, a
 window), one to five requests of different lengths per step, pages used in a
