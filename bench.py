@@ -52,7 +52,8 @@ def peaks() -> tuple:
     if path.exists():
         try:
             raw = json.loads(path.read_text())
-            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw.get("bf16_tflops_sustained") or raw["bf16_tflops"])}, "measured"
+            # the prefill is timed over a few milliseconds: the burst figure is its denominator
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw.get("bf16_tflops") or raw["bf16_tflops_sustained"])}, "measured"
         except (ValueError, KeyError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
