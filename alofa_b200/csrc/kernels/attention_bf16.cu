@@ -356,11 +356,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
     mbar_init(&tile_bar[threadIdx.x >> 5], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  pdl_begin();
-
+  // Lengths and block tables came with the step's metadata, before any kernel of the step ran,
+  // so the split's key range is known ahead of the wait on the kernel before this one.
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int g = p.nh / p.nkv;
-  const int token = p.q_start[seq];
   const int pos = p.kv_len[seq] - 1;  // the one query position of this request
   int k_lo = 0;
   if (p.window > 0) k_lo = max(0, pos - p.window + 1);
@@ -368,7 +367,28 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   const int k_hi = min(pos, (split + 1) * DECODE_SPLIT_KEYS - 1);
   if (k_lo > k_hi) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // this warp's block of keys
+  const int j0 = (split * WARPS + warp) * BLOCK_N;
+  const bool has_keys = j0 <= k_hi && j0 + BLOCK_N - 1 >= k_lo;
+  bf16* kt = k_tiles + warp * TILE_ELEMS;
+  bf16* vt = v_tiles + warp * TILE_ELEMS;
+  auto fetch_block = [&]() {  // one lane: the block lies inside one page, its 64 rows are consecutive cache slots
+    const int e = j0 / p.page_size;
+    const int row0 = p.block_table[(size_t)seq * p.max_blocks + e] * p.page_size + (j0 - e * p.page_size);
+    mbar_expect_tx(&tile_bar[warp], 2 * TILE_BYTES_TMA);
+#pragma unroll
+    for (int sub = 0; sub < HD / 64; ++sub) {
+      tma_load_2d(reinterpret_cast<uint8_t*>(kt) + sub * BLOCK_N * 128, &map_k, &tile_bar[warp], kvh * HD + sub * 64, row0);
+      tma_load_2d(reinterpret_cast<uint8_t*>(vt) + sub * BLOCK_N * 128, &map_v, &tile_bar[warp], kvh * HD + sub * 64, row0);
+    }
+  };
+  // A block that ends before the query's own position holds only keys of earlier steps: its copy
+  // need not wait for the kernel that writes this step's key and may start at once.
+  const bool early = TMA && has_keys && j0 + BLOCK_N - 1 < pos;
+  if (early && lane == 0) fetch_block();
+  pdl_begin();
 
+  const int token = p.q_start[seq];
   // the query rows: head kvh * g + r for r < g, zero rows above
   for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += THREADS) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;
@@ -376,25 +396,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
     const bf16* src = ok ? p.q + ((size_t)token * p.nh + kvh * g + r) * HD + c * 8 : p.q;
     cp_async16((uint32_t)__cvta_generic_to_shared(q_tile + r * ROW + c * 8), src, ok);
   }
-  // this warp's block of keys
-  const int j0 = (split * WARPS + warp) * BLOCK_N;
-  const bool has_keys = j0 <= k_hi && j0 + BLOCK_N - 1 >= k_lo;
-  bf16* kt = k_tiles + warp * TILE_ELEMS;
-  bf16* vt = v_tiles + warp * TILE_ELEMS;
   if (TMA) {
-    if (lane == 0) {
-      if (has_keys) {
-        // the block lies inside one page: its 64 rows are consecutive cache slots
-        const int e = j0 / p.page_size;
-        const int row0 = p.block_table[(size_t)seq * p.max_blocks + e] * p.page_size + (j0 - e * p.page_size);
-        mbar_expect_tx(&tile_bar[warp], 2 * TILE_BYTES_TMA);
-#pragma unroll
-        for (int sub = 0; sub < HD / 64; ++sub) {
-          tma_load_2d(reinterpret_cast<uint8_t*>(kt) + sub * BLOCK_N * 128, &map_k, &tile_bar[warp], kvh * HD + sub * 64, row0);
-          tma_load_2d(reinterpret_cast<uint8_t*>(vt) + sub * BLOCK_N * 128, &map_v, &tile_bar[warp], kvh * HD + sub * 64, row0);
-        }
-      }
-    }
+    if (lane == 0 && has_keys && !early) fetch_block();
   } else if (has_keys) {
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
     for (int idx = lane; idx < BLOCK_N * CHUNKS; idx += 32) {
