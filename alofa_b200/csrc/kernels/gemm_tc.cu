@@ -232,7 +232,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   }
-  pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
+  // The weights depend on no earlier kernel: the producer asks for the first ring of weight tiles
+  // before it waits for the kernel before this one; only the token operand comes after the wait.
+  int early_slices = 0;
+  if (threadIdx.x == 0) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    early_slices = min(stages, n_slices);
+    for (int i = 0; i < early_slices; ++i) {
+      uint8_t* stage = tiles + (size_t)i * STAGE_BYTES;
+      mbar_expect_tx(&full_bar[i], computed_b ? N_ACC * A_BYTES : STAGE_BYTES);
+      const int k = (slice_begin + i) * BK;
+      tma_load_2d(stage, &map_w, &full_bar[i], k, f0);
+      if (N_ACC == 2) tma_load_2d(stage + A_BYTES, &map_w, &full_bar[i], k, args.N + f0);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  } else {
+    pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
+  }
 #ifdef ALOFA_GEMM_TIMING
   if (probe && threadIdx.x == 0) args.stamps[1] = clock64();
 #endif
@@ -379,10 +395,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int s = i % stages;
         if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1, &abort_flag)) break;
         uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], computed_b ? N_ACC * A_BYTES : STAGE_BYTES);
         const int k = (slice_begin + i) * BK;
-        tma_load_2d(stage, &map_w, &full_bar[s], k, f0);
-        if (N_ACC == 2) tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, args.N + f0);
+        if (i >= early_slices) {  // the first ring's weights were asked for ahead of the wait
+          mbar_expect_tx(&full_bar[s], computed_b ? N_ACC * A_BYTES : STAGE_BYTES);
+          tma_load_2d(stage, &map_w, &full_bar[s], k, f0);
+          if (N_ACC == 2) tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, args.N + f0);
+        }
         if (!computed_b) tma_load_2d(stage + N_ACC * A_BYTES, &map_x, &full_bar[s], k, t0);
       }
     }
@@ -946,6 +964,9 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
   int stages = (int)((200 * 1024 - XCHG) / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) return ALOFA_ERR_ARGUMENT;
+  // (The ring is not cut down to the k-slices a CTA has: with a small footprint the next kernel's
+  // CTAs become resident beside this kernel's and their weight fetches take bandwidth from it;
+  // measured 1.03 ms against 0.95 ms per decode step at batch 8.)
   const size_t smem = STAGE * stages + XCHG + 1024;
   static bool configured = false;
   if (!configured) {
