@@ -618,23 +618,36 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
-  pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
+  auto load_weights = [&](int i) {  // the weight tile of slice i into its stage
+    const int s = i % stages;
+    uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+    const int k = (slice_begin + i) * BK;
+    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+    if (GATED) {
+      tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
+      tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], k, args.N + f0);
+    } else {
+      tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
+    }
+  };
+  // the weights depend on no earlier kernel: the first ring of them is asked for ahead of the wait
+  int early_slices = 0;
+  if (threadIdx.x == 0) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    early_slices = min(stages, n_slices);
+    for (int i = 0; i < early_slices; ++i) load_weights(i);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  } else {
+    pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
+  }
 
   if (warp == 0) {
     if (lane == 0) {
       for (int i = 0; i < n_slices; ++i) {
         const int s = i % stages;
         if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1, &abort_flag)) break;
-        uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        const int k = (slice_begin + i) * BK;
-        tma_load_2d(stage, &map_x, &full_bar[s], k, t0);
-        if (GATED) {
-          tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
-          tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], k, args.N + f0);
-        } else {
-          tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
-        }
+        if (i >= early_slices) load_weights(i);
+        tma_load_2d(tiles + (size_t)s * STAGE_BYTES, &map_x, &full_bar[s], (slice_begin + i) * BK, t0);
       }
     }
   } else if (warp == 1) {
@@ -831,7 +844,29 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
-  pdl_begin();
+  auto load_weights = [&](int it, int i, int f0) {  // the weight tile of slice i of a tile into the stage of ring position it
+    const int s = it % PERSISTENT_STAGES;
+    uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
+    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+    if (GATED) {
+      tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], i * BK, f0);
+      tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], i * BK, args.N + f0);
+    } else {
+      tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], i * BK, f0);
+    }
+  };
+  // the weights depend on no earlier kernel: those of the first tile's first ring go ahead of the wait
+  int early_slices = 0;
+  if (threadIdx.x == 0) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    if ((int)blockIdx.x < n_tiles) {
+      early_slices = min(PERSISTENT_STAGES, n_slices);
+      for (int i = 0; i < early_slices; ++i) load_weights(i, i, ((int)blockIdx.x % n_ftiles) * FEATS);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  } else {
+    pdl_begin();
+  }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -841,15 +876,8 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
         for (int i = 0; i < n_slices; ++i, ++it) {
           const int s = it % PERSISTENT_STAGES;
           if (it >= PERSISTENT_STAGES && !mbar_wait(&empty_bar[s], ((it / PERSISTENT_STAGES) - 1) & 1, &abort_flag)) break;
-          uint8_t* stage = tiles + (size_t)s * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          tma_load_2d(stage, &map_x, &full_bar[s], i * BK, t0);
-          if (GATED) {
-            tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], i * BK, f0);
-            tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], i * BK, args.N + f0);
-          } else {
-            tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], i * BK, f0);
-          }
+          if (it >= early_slices) load_weights(it, i, f0);
+          tma_load_2d(tiles + (size_t)s * STAGE_BYTES, &map_x, &full_bar[s], i * BK, t0);
         }
         if (abort_flag) break;
       }
