@@ -886,14 +886,29 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     if (lane == 0) {
       int it = 0, j = 0;  // slices consumed; tiles of this CTA so far
       bool ok = true;
+#ifdef ALOFA_GEMM_TIMING
+      long long t_start = clock64(), wait_full = 0, wait_acc = 0;
+#endif
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
         const int buf = j & 1;
+#ifdef ALOFA_GEMM_TIMING
+        long long ta = clock64();
+#endif
         if (j >= 2) ok = mbar_wait(&acc_free[buf], ((j >> 1) - 1) & 1, &abort_flag);
+#ifdef ALOFA_GEMM_TIMING
+        wait_acc += clock64() - ta;
+#endif
         if (!ok) break;
         tc_fence_after();
         for (int i = 0; i < n_slices; ++i, ++it) {
           const int s = it % PERSISTENT_STAGES;
+#ifdef ALOFA_GEMM_TIMING
+          long long tf = clock64();
+#endif
           ok = mbar_wait(&full_bar[s], (it / PERSISTENT_STAGES) & 1, &abort_flag);
+#ifdef ALOFA_GEMM_TIMING
+          wait_full += clock64() - tf;
+#endif
           if (!ok) break;
           tc_fence_after();
           const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
@@ -905,6 +920,14 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
         }
         if (ok) umma_commit(&acc_full[buf]);
       }
+#ifdef ALOFA_GEMM_TIMING
+      if (blockIdx.x == 0 && args.stamps) {
+        args.stamps[0] = clock64() - t_start;  // the MMA thread's life
+        args.stamps[1] = wait_full;            // of it: waiting for operand tiles
+        args.stamps[2] = wait_acc;             // waiting for the epilogue to free an accumulator
+        args.stamps[3] = j;                    // tiles
+      }
+#endif
     }
   } else {
     const int q = warp & 3;
