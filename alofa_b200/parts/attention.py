@@ -19,6 +19,7 @@ import torch
 
 from ..csrc import ops
 from ..errors import AlofaError
+from . import fast_linear
 from .base import Ineligible, PagedKV, Part, TensorSpec, as_float32_vector, build_part, register_part
 from .linear import RESIDUAL, STORE, Linear, MergedSplits
 
@@ -96,8 +97,12 @@ class GQAttention(Part):
         lin = self.qkv if writes else self.q_only
         q = ctx.buf((n, self.q_dim), dt)
         # a handful of tokens: product, bias, rotation and the cache write in one kernel
-        if vectorised and n <= 16 and lin.weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and ops.gemm_tc_rope(
-            x, lin.weight, lin.bias, q, cache.k, cache.v, group.slot_map, ctx.positions, table, self.nh, nkv_in, self.hd, 8, ctx.status
+        # (its depth split over a cluster of up to eight CTAs, as many as keep all tiles in one wave of the GPU)
+        # and only while a CTA then has a few k-slices: on deep products (3,584 wide) the cluster measured slower
+        depth_splits = max(1, min(8, fast_linear.SMS // -(-lin.weight.shape[0] // 128)))
+        shallow = -(-(-(-self.hidden // fast_linear.K_SLICE)) // depth_splits) <= 4
+        if vectorised and shallow and n <= 16 and lin.weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and ops.gemm_tc_rope(
+            x, lin.weight, lin.bias, q, cache.k, cache.v, group.slot_map, ctx.positions, table, self.nh, nkv_in, self.hd, depth_splits, ctx.status
         ):
             owed = None
         else:

@@ -73,16 +73,21 @@ def plan(linear):
         if tokens == 0:
             return True
         bn = _tile(tokens, linear.out_features, gated)
+        lazy = None if isinstance(x, torch.Tensor) else x
+        if lazy is not None:
+            x = None
+        splits = ops.gemm_tc_splits(depth, _splits(_ctas(tokens, linear.out_features, bn, gated), depth, defer and n_acc == 1))
         computed = None
-        if not isinstance(x, torch.Tensor):
-            # rows still to be made: the weights-on-M kernel makes them as it loads; else they are made first
-            if bn == 16 and linear.epi == ops.EPI_RESIDUAL and depth % 8 == 0 and x.fits_kernel():  # tiles of 16 tokens: a 16-byte chunk per epilogue thread
-                computed, x = x.computed(), None
+        if lazy is not None:
+            # Rows still to be made.  The weights-on-M kernel makes them as it loads, a k-slice at a
+            # time and each a trip to L2: worth it while a CTA has a slice or two, else they are made first.
+            per_cta = -(-(-(-depth // K_SLICE)) // splits)
+            if bn == 16 and linear.epi == ops.EPI_RESIDUAL and depth % 8 == 0 and per_cta <= 2 and lazy.fits_kernel():
+                computed = lazy.computed()
             else:
-                x = x.rows()
+                x = lazy.rows()
         if x is not None and (x.data_ptr() % 16 or not x.is_contiguous()):
             return False
-        splits = ops.gemm_tc_splits(depth, _splits(_ctas(tokens, linear.out_features, bn, gated), depth, defer and n_acc == 1))
         partial = None
         if splits > 1:
             partial = torch.empty((splits * n_acc, tokens, linear.out_features), dtype=torch.float32, device=w.device)
