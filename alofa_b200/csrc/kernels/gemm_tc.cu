@@ -1103,7 +1103,7 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
     configured = true;
   }
   dim3 grid((args.N + FEATS - 1) / FEATS, (args.T + 127) / 128, splits);
-  if (BNF == 256 && splits == 1 && (args.N & 3) == 0 && args.T > 128 && args.K <= 2048) {
+  if (BNF == 256 && splits == 1 && (args.N & 3) == 0 && args.K <= 2048) {
     // More tiles than SMs and a shallow depth, where a tile's epilogue is a large share of its
     // time: one resident CTA per SM works through the tiles, epilogues beside MMAs.  (Deep
     // products measured faster as two CTAs per SM, which keep four stages in flight per SM.)
