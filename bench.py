@@ -67,10 +67,13 @@ class ClockSampler:
     def __init__(self):
         self.samples = []
         self.proc = None
+        self.begin = 0.0
 
     def start(self):
+        """Start sampling; nvidia-smi takes a moment to give its first line, so
+        this goes before the warm-up and :meth:`mark` before the timed steps."""
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -81,7 +84,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
-                self.samples.append(parts)
+                self.samples.append((time.perf_counter(), parts))
+
+    def mark(self):
+        """The timed region starts now: only samples from here on count."""
+        self.begin = time.perf_counter()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -93,7 +100,9 @@ class ClockSampler:
             self.proc.kill()
         clocks, reasons, max_mhz = [], set(), None
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        for at, s in self.samples:
+            if at < self.begin:
+                continue
             try:
                 clocks.append(int(s[0]))
                 max_mhz = int(s[1])
@@ -191,11 +200,15 @@ def run(args) -> dict:
             state["i"] += 1
             runner.forward_sampled([StepEntry(s, (int(t),), (0,)) for s, t in zip(slots, toks)])
 
-        for _ in range(warmup):
-            one_step()
-        launches0 = ops.launch_count()
         if clocks:
             clocks.start()
+        for _ in range(warmup):
+            one_step()
+        if clocks:
+            torch.cuda.synchronize()
+            time.sleep(0.3)  # the sampler's first lines
+            clocks.mark()
+        launches0 = ops.launch_count()
         ms = timed(one_step, steps)
         clock_report = clocks.stop() if clocks else None
         launches = ops.launch_count() - launches0
