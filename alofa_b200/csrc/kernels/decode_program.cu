@@ -274,8 +274,7 @@ __device__ __forceinline__ void epilogue_fetch(const Phase& ph, int item, int t,
     if (has_a) f.x0 = __ldcg(out + row_a + n);
     if (has_b) f.x1 = __ldcg(out + row_b + n);
   } else if (ph.epi == E_ROPE_STORE) {
-    const int per_head = HD / 16;
-    const int head = item / per_head, j = item - head * per_head;
+    const int head = item / (HD / 16);
     if (head >= ph.nh) f.slot = ph.slot_map[t];
     f.pos = ph.positions[t];
   }
