@@ -78,9 +78,10 @@ __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, f
 }
 
 // The same with one warp per row (eight rows per block): for the many rows of a
-// prompt portion, where a block per row leaves most of a block idle.  The row
-// is read twice (the second read hits L1/L2); sums stay within the warp.
-template <typename TO>
+// prompt portion, where a block per row leaves most of a block idle.  A lane keeps
+// its CHUNKS groups of four values in registers (all their loads in flight at
+// once, the row read once); sums stay within the warp.  hidden <= CHUNKS * 128.
+template <typename TO, int CHUNKS>
 __global__ void __launch_bounds__(256) norm_rows_kernel(TO* __restrict__ out, float* __restrict__ h, const float* __restrict__ w,
                                                         const float* __restrict__ partial, const float* __restrict__ bias,
                                                         const int* __restrict__ rows, int n_rows, int n_tokens, int hidden, int splits,
@@ -92,38 +93,52 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(TO* __restrict__ out, fl
   float4* hr = reinterpret_cast<float4*>(h + (size_t)src * hidden);
   const int n4 = hidden >> 2;
   const size_t plane4 = ((size_t)n_tokens * hidden) >> 2;
-  float ss = 0.f;
-  for (int c = lane; c < n4; c += 32) {
-    float4 v = hr[c];
-    if (partial) {
-      const float4* p = reinterpret_cast<const float4*>(partial) + (size_t)src * n4 + c;
-      for (int z = 0; z < splits; ++z) {
-        const float4 a = p[(size_t)z * plane4];
-        v.x += a.x;
-        v.y += a.y;
-        v.z += a.z;
-        v.w += a.w;
+  float4 v[CHUNKS];
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = lane + i * 32;
+    v[i] = c < n4 ? hr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (partial) {
+    const float4* p = reinterpret_cast<const float4*>(partial) + (size_t)src * n4;
+    for (int z = 0; z < splits; ++z) {  // added in split order
+#pragma unroll
+      for (int i = 0; i < CHUNKS; ++i) {
+        const int c = lane + i * 32;
+        if (c < n4) {
+          const float4 a = p[(size_t)z * plane4 + c];
+          v[i].x += a.x, v[i].y += a.y, v[i].z += a.z, v[i].w += a.w;
+        }
       }
-      if (bias) {
-        const float4 b = reinterpret_cast<const float4*>(bias)[c];
-        v.x += b.x;
-        v.y += b.y;
-        v.z += b.z;
-        v.w += b.w;
-      }
-      hr[c] = v;
     }
-    ss = fmaf(v.x, v.x, ss);
-    ss = fmaf(v.y, v.y, ss);
-    ss = fmaf(v.z, v.z, ss);
-    ss = fmaf(v.w, v.w, ss);
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+      const int c = lane + i * 32;
+      if (c < n4) {
+        if (bias) {
+          const float4 b = reinterpret_cast<const float4*>(bias)[c];
+          v[i].x += b.x, v[i].y += b.y, v[i].z += b.z, v[i].w += b.w;
+        }
+        hr[c] = v[i];
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    ss = fmaf(v[i].x, v[i].x, ss);
+    ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss);
+    ss = fmaf(v[i].w, v[i].w, ss);
   }
   ss = warp_sum(ss);
   const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
-  for (int c = lane; c < n4; c += 32) {
-    const float4 v = hr[c];  // this lane wrote it above, or nobody did
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = lane + i * 32;
+    if (c >= n4) break;
     const float4 g = reinterpret_cast<const float4*>(w)[c];
-    const float y0 = v.x * scale * g.x, y1 = v.y * scale * g.y, y2 = v.z * scale * g.z, y3 = v.w * scale * g.w;
+    const float y0 = v[i].x * scale * g.x, y1 = v[i].y * scale * g.y, y2 = v[i].z * scale * g.z, y3 = v[i].w * scale * g.w;
     if (sizeof(TO) == 2) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
       reinterpret_cast<uint2*>(out + (size_t)r * hidden)[c] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
@@ -133,18 +148,33 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(TO* __restrict__ out, fl
   }
 }
 
+template <typename TO, int CHUNKS>
+static void launch_norm_rows(TO* out, float* h, const float* w, const float* partial, const float* bias, const int* rows, int n_rows,
+                             int n_tokens, int hidden, int splits, float eps, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    prefer_max_shared(norm_rows_kernel<TO, CHUNKS>);
+    configured = true;
+  }
+  launch_dep(norm_rows_kernel<TO, CHUNKS>, (unsigned)((n_rows + 7) / 8), 256, 0, stream, out, h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps);
+}
+template <typename TO>
+static void dispatch_norm_rows(TO* out, float* h, const float* w, const float* partial, const float* bias, const int* rows, int n_rows,
+                               int n_tokens, int hidden, int splits, float eps, cudaStream_t stream) {
+  if (hidden <= 1024) launch_norm_rows<TO, 8>(out, h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps, stream);
+  else if (hidden <= 2048) launch_norm_rows<TO, 16>(out, h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps, stream);
+  else launch_norm_rows<TO, 32>(out, h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps, stream);
+}
+
 ALOFA_API int alofa_norm_fused(void* out, void* h, const float* w, const float* partial, const float* bias, const int* rows, int n_rows,
                                int n_tokens, int hidden, int splits, float eps, int out_bf16, cudaStream_t stream) {
   if (n_rows <= 0) return ALOFA_OK;
   if (hidden % 4 != 0 || hidden > 12288) return ALOFA_ERR_ARGUMENT;
-  if (n_rows >= 256) {  // many rows: a warp each
-    ALOFA_PREFER_MAX_SHARED(norm_rows_kernel<bf16>);
-    ALOFA_PREFER_MAX_SHARED(norm_rows_kernel<float>);
-    const unsigned blocks = (unsigned)((n_rows + 7) / 8);
+  if (n_rows >= 256 && hidden <= 4096) {  // many rows: a warp each, the row in registers
     if (out_bf16)
-      launch_dep(norm_rows_kernel<bf16>, blocks, 256, 0, stream, (bf16*)out, (float*)h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps);
+      dispatch_norm_rows<bf16>((bf16*)out, (float*)h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps, stream);
     else
-      launch_dep(norm_rows_kernel<float>, blocks, 256, 0, stream, (float*)out, (float*)h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps);
+      dispatch_norm_rows<float>((float*)out, (float*)h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps, stream);
     return launch_status();
   }
   const size_t smem = (size_t)hidden * sizeof(float);

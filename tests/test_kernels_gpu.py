@@ -127,19 +127,29 @@ def test_norm_fused_adds_owed_partial_sums(ops, out_dtype):
     assert ops.norm_fused(out, dev(h), dev(w), 1e-6, dev(rows), dev(partial), splits, None)
     assert_close(out.float().cpu(), plain.rmsnorm((h.astype(np.float64) + partial.astype(np.float64).sum(axis=0))[rows], w, 1e-6), TOL[out_dtype], "gathered rows")
     assert not ops.norm_fused(torch.empty(2, 6, dtype=out_dtype, device="cuda"), dev(h[:, :6].copy()), dev(w[:6].copy()), 1e-6)  # width not a multiple of 4
-    # many rows take the warp-per-row form
-    many = rng.normal(size=(300, 200)).astype(np.float32)
-    part = rng.normal(size=(2, 300, 200)).astype(np.float32)
-    wm = (1 + 0.1 * rng.normal(size=200)).astype(np.float32)
-    hm = dev(many)
-    out = torch.empty(300, 200, dtype=out_dtype, device="cuda")
-    assert ops.norm_fused(out, hm, dev(wm), 1e-5, None, dev(part), 2, None)
-    total = many.astype(np.float64) + part.astype(np.float64).sum(axis=0)
-    assert_close(hm.cpu(), total, 1e-6, "stream after the sums (many rows)")
-    assert_close(out.float().cpu(), plain.rmsnorm(total, wm, 1e-5), TOL[out_dtype], "norm (many rows)")
-    out = torch.empty(300, 200, dtype=out_dtype, device="cuda")
-    assert ops.norm_fused(out, dev(many), dev(wm), 1e-5)
-    assert_close(out.float().cpu(), plain.rmsnorm(many, wm, 1e-5), TOL[out_dtype], "plain norm (many rows)")
+    # many rows take the warp-per-row form (a row in 8, 16 or 32 register groups per lane; wider rows a block each)
+    for width in (200, 1000, 1536, 3588, 5120):
+        many = rng.normal(size=(259, width)).astype(np.float32)
+        part = rng.normal(size=(2, 259, width)).astype(np.float32)
+        bm = rng.normal(size=width).astype(np.float32)
+        wm = (1 + 0.1 * rng.normal(size=width)).astype(np.float32)
+        hm = dev(many)
+        out = torch.empty(259, width, dtype=out_dtype, device="cuda")
+        assert ops.norm_fused(out, hm, dev(wm), 1e-5, None, dev(part), 2, dev(bm))
+        total = many.astype(np.float64) + part.astype(np.float64).sum(axis=0) + bm
+        assert_close(hm.cpu(), total, 1e-6, f"stream after the sums (many rows of {width})")
+        assert_close(out.float().cpu(), plain.rmsnorm(total, wm, 1e-5), TOL[out_dtype], f"norm (many rows of {width})")
+        out = torch.empty(259, width, dtype=out_dtype, device="cuda")
+        assert ops.norm_fused(out, dev(many), dev(wm), 1e-5)
+        assert_close(out.float().cpu(), plain.rmsnorm(many, wm, 1e-5), TOL[out_dtype], f"plain norm (many rows of {width})")
+    picked = np.array([258, 0, 77] * 90, dtype=np.int32)  # gathered rows, many of them
+    out = torch.empty(270, 5120, dtype=out_dtype, device="cuda")
+    assert ops.norm_fused(out, dev(many), dev(wm), 1e-5, dev(picked))
+    assert_close(out.float().cpu(), plain.rmsnorm(many[picked], wm, 1e-5), TOL[out_dtype], "gathered rows (many)")
+    many = many[:, :1000].copy()
+    out = torch.empty(270, 1000, dtype=out_dtype, device="cuda")
+    assert ops.norm_fused(out, dev(many), dev(wm[:1000].copy()), 1e-5, dev(picked))
+    assert_close(out.float().cpu(), plain.rmsnorm(many[picked], wm[:1000], 1e-5), TOL[out_dtype], "gathered rows (many, a warp each)")
 
 
 @pytest.mark.parametrize("hd", [16, 48, 64, 128])
