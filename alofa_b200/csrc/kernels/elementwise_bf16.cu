@@ -16,35 +16,47 @@
 // RMSNorm with optional split-K reduction into the residual stream.
 // One block per output row; hidden % 4 == 0.
 // ---------------------------------------------------------------------------
+// B partial sums of one group of four values: their loads in flight together, added in split order.
+template <int B>
+__device__ __forceinline__ void add_splits(float4& v, const float4* p, int z0, int splits, size_t plane4) {
+  float4 a[B];
+#pragma unroll
+  for (int i = 0; i < B; ++i) a[i] = (z0 + i < splits) ? p[(size_t)(z0 + i) * plane4] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < B; ++i) {
+    v.x += a[i].x;
+    v.y += a[i].y;
+    v.z += a[i].z;
+    v.w += a[i].w;
+  }
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, float* __restrict__ h, const float* __restrict__ w,
                                                          const float* __restrict__ partial, const float* __restrict__ bias,
                                                          const int* __restrict__ rows, int n_tokens, int hidden, int splits, float eps) {
   extern __shared__ float row_buf[];  // hidden floats
   __shared__ float scratch[32];
+  const int n4 = hidden >> 2;
+  // the norm's weight is a constant of the model: this thread's first group of it is read ahead of the wait
+  float4 g_first = make_float4(0.f, 0.f, 0.f, 0.f);
+  if ((int)threadIdx.x < n4) g_first = reinterpret_cast<const float4*>(w)[threadIdx.x];
   pdl_begin();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float4* hr = reinterpret_cast<float4*>(h + (size_t)src * hidden);
-  const int n4 = hidden >> 2;
   const size_t plane4 = ((size_t)n_tokens * hidden) >> 2;
   float ss = 0.f;
   for (int c = threadIdx.x; c < n4; c += blockDim.x) {
     float4 v = hr[c];
     if (partial) {
-      // the splits are read eight at a time (the loads overlap) and added in split order
+      // up to 24 splits in one round of loads (a round is a trip to L2), more in rounds of 8
       const float4* p = reinterpret_cast<const float4*>(partial) + (size_t)src * n4 + c;
-      for (int z0 = 0; z0 < splits; z0 += 8) {
-        float4 a[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) a[i] = (z0 + i < splits) ? p[(size_t)(z0 + i) * plane4] : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v.x += a[i].x;
-          v.y += a[i].y;
-          v.z += a[i].z;
-          v.w += a[i].w;
-        }
+      if (splits <= 8) {
+        add_splits<8>(v, p, 0, splits, plane4);
+      } else {
+        add_splits<24>(v, p, 0, splits, plane4);
+        for (int z0 = 24; z0 < splits; z0 += 8) add_splits<8>(v, p, z0, splits, plane4);
       }
       if (bias) {
         const float4 b = reinterpret_cast<const float4*>(bias)[c];
@@ -65,7 +77,7 @@ __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, f
   const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
   for (int c = threadIdx.x; c < n4; c += blockDim.x) {
     const float4 v = reinterpret_cast<float4*>(row_buf)[c];
-    const float4 g = reinterpret_cast<const float4*>(w)[c];
+    const float4 g = c == (int)threadIdx.x ? g_first : reinterpret_cast<const float4*>(w)[c];
     const float y0 = v.x * scale * g.x, y1 = v.y * scale * g.y, y2 = v.z * scale * g.z, y3 = v.w * scale * g.w;
     if (sizeof(TO) == 2) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
