@@ -372,9 +372,14 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   const bool has_keys = j0 <= k_hi && j0 + BLOCK_N - 1 >= k_lo;
   bf16* kt = k_tiles + warp * TILE_ELEMS;
   bf16* vt = v_tiles + warp * TILE_ELEMS;
-  auto fetch_block = [&]() {  // one lane: the block lies inside one page, its 64 rows are consecutive cache slots
+  // the block lies inside one page, its 64 rows are consecutive cache slots
+  int row0 = 0;
+  if (TMA && has_keys && lane == 0) {
     const int e = j0 / p.page_size;
-    const int row0 = p.block_table[(size_t)seq * p.max_blocks + e] * p.page_size + (j0 - e * p.page_size);
+    row0 = p.block_table[(size_t)seq * p.max_blocks + e] * p.page_size + (j0 - e * p.page_size);
+  }
+  const int token = p.q_start[seq];
+  auto fetch_block = [&]() {  // one lane
     mbar_expect_tx(&tile_bar[warp], 2 * TILE_BYTES_TMA);
 #pragma unroll
     for (int sub = 0; sub < HD / 64; ++sub) {
@@ -388,7 +393,6 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   if (early && lane == 0) fetch_block();
   pdl_begin();
 
-  const int token = p.q_start[seq];
   // the query rows: head kvh * g + r for r < g, zero rows above
   for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += THREADS) {
     const int r = idx / CHUNKS, c = idx % CHUNKS;

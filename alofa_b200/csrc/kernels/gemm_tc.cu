@@ -215,9 +215,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // constant of the model, so they too may be read ahead of the wait.
   float2 rope_cs[EPI == EPI_ROPE ? 16 : 1];
   int rope_slot[EPI == EPI_ROPE ? 16 : 1];
+  float rope_bias = 0.f;  // the bias of this thread's feature: a constant of the model as well
   if constexpr (EPI == EPI_ROPE) {
     if (warp >= 2 && rank == 0) {
       const int row = ((warp & 3) << 5) + lane, hd = args.rope_head_dim, half = hd >> 1;
+      if (args.bias && f0 + row < args.N) rope_bias = args.bias[f0 + row];
       const int d = row % hd, i = d < half ? d : d - half;
       const bool rotated = (f0 + row) / hd < args.rope_heads + args.rope_kv_heads;
 #pragma unroll
@@ -266,7 +268,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const bool split = gridDim.z > 1 && !CLUSTER;
     const bool push = CLUSTER && rank != 0;
     float bias0 = 0.f, bias1 = 0.f;
-    if (!split && !push && args.bias && f_ok) {
+    if (EPI == EPI_ROPE) {
+      bias0 = rope_bias;
+    } else if (!split && !push && args.bias && f_ok) {
       bias0 = args.bias[f];
       if (N_ACC == 2) bias1 = args.bias[args.N + f];
     }
