@@ -127,6 +127,18 @@ def test_norm_fused_adds_owed_partial_sums(ops, out_dtype):
     assert ops.norm_fused(out, dev(h), dev(w), 1e-6, dev(rows), dev(partial), splits, None)
     assert_close(out.float().cpu(), plain.rmsnorm((h.astype(np.float64) + partial.astype(np.float64).sum(axis=0))[rows], w, 1e-6), TOL[out_dtype], "gathered rows")
     assert not ops.norm_fused(torch.empty(2, 6, dtype=out_dtype, device="cuda"), dev(h[:, :6].copy()), dev(w[:6].copy()), 1e-6)  # width not a multiple of 4
+    # a handful of rows that owe many split sums (one round of loads for up to 24, then rounds of 8)
+    for width, n_splits, n in ((896, 19, 8), (100, 30, 1), (3584, 9, 16)):
+        hh = rng.normal(size=(n, width)).astype(np.float32)
+        pp = rng.normal(size=(n_splits, n, width)).astype(np.float32)
+        bb = rng.normal(size=width).astype(np.float32)
+        ww = (1 + 0.1 * rng.normal(size=width)).astype(np.float32)
+        hdev = dev(hh)
+        out = torch.empty(n, width, dtype=out_dtype, device="cuda")
+        assert ops.norm_fused(out, hdev, dev(ww), 1e-6, None, dev(pp), n_splits, dev(bb))
+        total = hh.astype(np.float64) + pp.astype(np.float64).sum(axis=0) + bb
+        assert_close(hdev.cpu(), total, 2e-6, f"stream after {n_splits} sums")
+        assert_close(out.float().cpu(), plain.rmsnorm(total, ww, 1e-6), TOL[out_dtype], f"norm after {n_splits} sums of {width}")
     # many rows take the warp-per-row form (a row in 8, 16 or 32 register groups per lane; wider rows a block each)
     for width in (200, 1000, 1536, 3588, 5120):
         many = rng.normal(size=(259, width)).astype(np.float32)
