@@ -391,7 +391,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   // need not wait for the kernel that writes this step's key and may start at once.
   const bool early = TMA && has_keys && j0 + BLOCK_N - 1 < pos;
   if (early && lane == 0) fetch_block();
-  pdl_begin();
+  pdl_wait();
 
   // the query rows: head kvh * g + r for r < g, zero rows above
   for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += THREADS) {
@@ -418,6 +418,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
       cp_async16((uint32_t)__cvta_generic_to_shared(vt + r * ROW + c * 8), p.v_cache + offset, ok);
     }
   }
+  pdl_launch();
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();  // the query tile was copied by all threads (and the barriers are initialised)

@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, f
   // the norm's weight is a constant of the model: this thread's first group of it is read ahead of the wait
   float4 g_first = make_float4(0.f, 0.f, 0.f, 0.f);
   if ((int)threadIdx.x < n4) g_first = reinterpret_cast<const float4*>(w)[threadIdx.x];
-  pdl_begin();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float4* hr = reinterpret_cast<float4*>(h + (size_t)src * hidden);
@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, f
     ss = fmaf(v.z, v.z, ss);
     ss = fmaf(v.w, v.w, ss);
   }
+  pdl_launch();
   ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
   for (int c = threadIdx.x; c < n4; c += blockDim.x) {
@@ -252,7 +253,6 @@ __global__ void rope_store_fused_kernel(bf16* __restrict__ q_out, bf16* __restri
                                         const float* __restrict__ cos_sin, const int* __restrict__ positions,
                                         const int* __restrict__ slot_map, int n_tokens, int nh, int nkv, int hd, int splits, int write_cache) {
   const int chunks = hd >> 4;  // pairs of 8-element chunks per head
-  pdl_begin();
   const int heads = nh + 2 * nkv;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (size_t)n_tokens * heads * chunks) return;
@@ -262,15 +262,9 @@ __global__ void rope_store_fused_kernel(bf16* __restrict__ q_out, bf16* __restri
   const int half = hd >> 1;
   const int C = heads * hd;
   const int col = head * hd + c * 8;
-  Vec8 a, b;
-  if (partial) {
-    const size_t plane = (size_t)n_tokens * C;
-    a = load8_partial(partial, bias, (size_t)t * C + col, col, plane, splits);
-    b = load8_partial(partial, bias, (size_t)t * C + col + half, col + half, plane, splits);
-  } else {
-    a = load8(qkv + (size_t)t * C + col);
-    b = load8(qkv + (size_t)t * C + col + half);
-  }
+  // Where the values go and what they are rotated by: slots and positions came with the step's
+  // metadata, before any kernel of the step ran, and the table is a constant of the model, so all
+  // of it is read ahead of the wait for the kernel that makes the values.
   bf16* dst;
   bool rotate = true;
   if (head < nh) {
@@ -286,14 +280,30 @@ __global__ void rope_store_fused_kernel(bf16* __restrict__ q_out, bf16* __restri
       rotate = false;
     }
   }
+  float4 cs[4];  // (cos, sin) of eight elements
   if (rotate) {
-    const float* cs = cos_sin + ((size_t)positions[t] * half + c * 8) * 2;
+    const float4* src = reinterpret_cast<const float4*>(cos_sin + ((size_t)positions[t] * half + c * 8) * 2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) cs[i] = src[i];
+  }
+  pdl_begin();
+  Vec8 a, b;
+  if (partial) {
+    const size_t plane = (size_t)n_tokens * C;
+    a = load8_partial(partial, bias, (size_t)t * C + col, col, plane, splits);
+    b = load8_partial(partial, bias, (size_t)t * C + col + half, col + half, plane, splits);
+  } else {
+    a = load8(qkv + (size_t)t * C + col);
+    b = load8(qkv + (size_t)t * C + col + half);
+  }
+  if (rotate) {
     Vec8 ya, yb;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float co = cs[2 * i], si = cs[2 * i + 1];
-      ya.v[i] = a.v[i] * co - b.v[i] * si;
-      yb.v[i] = b.v[i] * co + a.v[i] * si;
+    for (int i = 0; i < 4; ++i) {
+      ya.v[2 * i] = a.v[2 * i] * cs[i].x - b.v[2 * i] * cs[i].y;
+      yb.v[2 * i] = b.v[2 * i] * cs[i].x + a.v[2 * i] * cs[i].y;
+      ya.v[2 * i + 1] = a.v[2 * i + 1] * cs[i].z - b.v[2 * i + 1] * cs[i].w;
+      yb.v[2 * i + 1] = b.v[2 * i + 1] * cs[i].z + a.v[2 * i + 1] * cs[i].w;
     }
     a = ya;
     b = yb;

@@ -236,9 +236,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
   // The weights depend on no earlier kernel: the producer asks for the first ring of weight tiles
   // before it waits for the kernel before this one; only the token operand comes after the wait.
+  // The kernel after this one is let in after the wait (see pdl_launch).
   int early_slices = 0;
   if (threadIdx.x == 0) {
-    asm volatile("griddepcontrol.launch_dependents;");
     early_slices = min(stages, n_slices);
     for (int i = 0; i < early_slices; ++i) {
       uint8_t* stage = tiles + (size_t)i * STAGE_BYTES;
@@ -248,8 +248,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (N_ACC == 2) tma_load_2d(stage + A_BYTES, &map_w, &full_bar[i], k, args.N + f0);
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
   } else {
-    pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
+    pdl_wait();
+    pdl_launch();
   }
 #ifdef ALOFA_GEMM_TIMING
   if (probe && threadIdx.x == 0) args.stamps[1] = clock64();
