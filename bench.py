@@ -47,15 +47,42 @@ PROMPT_LEN = 2048
 CONTEXT = 4096
 
 
+def _find_number(raw, key):
+    """The number under ``key`` anywhere in a nested JSON value (a figure may be
+    a bare number or an object with a ``value``); None when absent."""
+    if isinstance(raw, dict):
+        if key in raw:
+            v = raw[key]
+            if isinstance(v, dict):
+                v = v.get("value")
+            try:
+                return float(v)
+            except (TypeError, ValueError):
+                return None
+        for v in raw.values():
+            found = _find_number(v, key)
+            if found is not None:
+                return found
+    elif isinstance(raw, list):
+        for v in raw:
+            found = _find_number(v, key)
+            if found is not None:
+                return found
+    return None
+
+
 def peaks() -> tuple:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         try:
             raw = json.loads(path.read_text())
-            # the prefill is timed over a few milliseconds: the burst figure is its denominator
-            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw.get("bf16_tflops") or raw["bf16_tflops_sustained"])}, "measured"
-        except (ValueError, KeyError):
-            pass
+        except ValueError:
+            raw = None
+        hbm = _find_number(raw, "hbm_gbs")
+        # the prefill is timed over a few milliseconds: the burst figure is its denominator
+        flops = _find_number(raw, "bf16_tflops") or _find_number(raw, "bf16_tflops_sustained")
+        if hbm and flops:
+            return {"hbm_gbs": hbm, "bf16_tflops": flops}, "measured"
     return dict(FALLBACK_PEAKS), "fallback"
 
 
