@@ -14,6 +14,11 @@
 //   EPI_RESIDUAL out[t, f] += acc + bias[f]               (fp32 residual stream)
 //   EPI_GATED    W = [gate; up]: out[t, f] = silu(g) * u  (two accumulators)
 //   EPI_PARTIAL  ws[z, t, f] = acc                        (split-K; see reduce)
+//   EPI_ROPE     W = [q; k; v]: bias, NeoX rotation of q and k, q to its buffer,
+//                k and v to their cache slots
+// Formulas: the product with its bias src/alofa/kernels/cpu/scalar.mojo:132-205,
+// silu(gate) * up scalar.mojo:208-231, the rotation scalar.mojo:283-344, the
+// cache write through the block table src/alofa/kernels/cpu/paged.mojo:208-246.
 // Split-K (grid.z > 1) spreads the k-slices of one tile over several CTAs so
 // that a small token count still pulls weights through every SM; the partial
 // sums are added in a fixed order by alofa_splitk_reduce.

@@ -1,4 +1,9 @@
-"""From a model folder (or a configuration and a seed) to a loaded model."""
+"""From a model folder (or a configuration and a seed) to a loaded model.
+
+The reference does the same in ``QwenModel`` construction: config.json read
+into ``QwenConfig`` (src/alofa/model/arch/qwen.mojo:929-982), tensors bound by
+their Hugging Face names with the required-name list checked at once
+(qwen.mojo:1168-1189)."""
 from __future__ import annotations
 
 import torch
