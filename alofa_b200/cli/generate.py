@@ -56,6 +56,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--frequency-penalty", type=float, default=0.0)
     ap.add_argument("--presence-penalty", type=float, default=0.0)
     ap.add_argument("--min-tokens-to-keep", type=int, default=1)
+    ap.add_argument("--logit-bias", action="append", default=[], metavar="ID:VALUE[,ID:VALUE...]",
+                    help="added to the logit of token ID before anything else; repeatable")
     ap.add_argument("--seed", type=int, default=_env_int("ALOFA_SEED", SEED, 0, 2_147_483_647), help="sampling seed [ALOFA_SEED]")
     ap.add_argument("--eos-token-id", type=int, default=None)
     # engine: the reference's SchedConfig (src/alofa/engine/scheduler.mojo:139-192)
@@ -72,6 +74,26 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--trace-out", help="write the scheduler's decisions, one line per tick")
     ap.add_argument("--json", action="store_true", help="print one JSON object instead of text")
     return ap
+
+
+def parse_logit_bias(items) -> dict:
+    """``["5:1.5,7:-2", "9:0.25"]`` -> ``{5: 1.5, 7: -2.0, 9: 0.25}`` (the
+    reference's ``LogitBias(index, value)`` list, sampler.mojo:93-118); a token
+    named twice has its values added, as a list of additive entries would."""
+    bias: dict = {}
+    for item in items:
+        for pair in item.split(","):
+            if not pair.strip():
+                continue
+            index, sep, value = pair.partition(":")
+            try:
+                if not sep:
+                    raise ValueError
+                token, offset = int(index), float(value)
+            except ValueError:
+                raise SystemExit(f"generate: --logit-bias wants ID:VALUE, got {pair.strip()!r}") from None
+            bias[token] = bias.get(token, 0.0) + offset
+    return bias
 
 
 def main(argv=None) -> int:
@@ -102,7 +124,7 @@ def main(argv=None) -> int:
     sampling = SamplingParams(
         temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p, repetition_penalty=args.repetition_penalty,
         frequency_penalty=args.frequency_penalty, presence_penalty=args.presence_penalty, min_tokens_to_keep=args.min_tokens_to_keep,
-        seed=args.seed, max_new_tokens=args.max_new_tokens, stop_token_ids=(args.eos_token_id,) if args.eos_token_id is not None else (),
+        logit_bias=parse_logit_bias(args.logit_bias), seed=args.seed, max_new_tokens=args.max_new_tokens, stop_token_ids=(args.eos_token_id,) if args.eos_token_id is not None else (),
     )
     t0 = time.perf_counter()
     outputs = engine.generate(prompts, sampling=sampling)
