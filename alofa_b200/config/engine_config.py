@@ -39,6 +39,6 @@ class EngineConfig:
         need(self.max_batch > 0, "max_batch must be positive", f"max_batch={self.max_batch}")
         need(self.max_tokens > 0, "max_tokens must be positive", f"max_tokens={self.max_tokens}")
         need(self.max_chunk > 0, "max_chunk must be positive", f"max_chunk={self.max_chunk}")
-        need(self.token_budget >= 0, "token_budget must not be negative", f"token_budget={self.token_budget}")
+        need(self.token_budget >= 1, "token_budget must be at least one token a step", f"token_budget={self.token_budget}")
         need(0 <= self.watermark_permille <= 1000, "watermark_permille out of range", f"watermark_permille={self.watermark_permille}")
         need(self.max_wait_ticks >= 0, "max_wait_ticks must not be negative", f"max_wait_ticks={self.max_wait_ticks}")

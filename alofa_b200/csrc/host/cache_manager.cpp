@@ -14,6 +14,7 @@
 // of per-request state of fixed size.
 //
 // Plain C++17, no CUDA: the tables are copied to the device by the caller.
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
 #include <vector>
@@ -273,9 +274,13 @@ int cm_block_table(void* h, int s, int g, int32_t* out, int max) {
 //                         then per group slot_map, block_table
 //   max_blocks            row length of the block tables in meta
 //   info out              max tokens of an entry, max keys of an entry, total tokens
-// Token ids are copied by the caller.  Returns 0, or ERR_CAPACITY when a
-// reservation does not fit (earlier entries keep their reservation), or
-// ERR_ARGUMENT for a bad slot or place.
+// Token ids are copied by the caller.  All or nothing: every entry is checked
+// (slot live and named once, places inside its tokens) and the pages that all
+// entries need together are counted against each group's free pages before
+// anything is reserved or written, so a step that is refused (ERR_CAPACITY when
+// the pages do not suffice, ERR_ARGUMENT for a bad slot or place) leaves the
+// manager and `meta` as they were.  A reservation left by a step that was
+// planned but never committed is given back first.
 int cm_plan_step(void* h, int n, const int* slots, const int* counts, const int* want_counts, const int* wants, int32_t* meta,
                  const int* off, int max_blocks, int* info) {
   auto* m = static_cast<Manager*>(h);
@@ -288,13 +293,55 @@ int cm_plan_step(void* h, int n, const int* slots, const int* counts, const int*
   int32_t* state_slots = meta + off[4];
   int32_t* logit_rows = meta + off[5];
   int row = 0, out = 0, want_at = 0, max_q = 0, max_kv = 0;
+  // first pass: nothing is changed until every entry is known to fit
+  {
+    std::vector<int> need(G, 0);
+    std::vector<char> named(m->requests.size(), 0);
+    int at = 0;
+    for (int i = 0; i < n; ++i) {
+      const int s = slots[i], cnt = counts[i];
+      if (s < 0 || s >= (int)m->requests.size() || !m->requests[s].live || cnt <= 0 || named[s]) return ERR_ARGUMENT;
+      named[s] = 1;
+      if (want_counts[i] < 0) return ERR_ARGUMENT;
+      for (int w = 0; w < want_counts[i]; ++w) {
+        const int place = wants[at++];
+        if (place < 0 || place >= cnt) return ERR_ARGUMENT;
+      }
+      const Request& r = m->requests[s];
+      for (int g = 0; g < G; ++g) {
+        const int want = ceil_div(r.computed_len + cnt, m->groups[g].page_size);
+        if (want > m->max_blocks || want > max_blocks) return ERR_CAPACITY;
+        // pages held beyond the computed length come from a step that was planned and not committed
+        const int have = std::min((int)r.table[g].size(), ceil_div(r.computed_len, m->groups[g].page_size));
+        need[g] += want > have ? want - have : 0;
+      }
+    }
+    for (int g = 0; g < G; ++g) {
+      int stale = 0;  // pages that the second pass gives back before it reserves
+      for (int i = 0; i < n; ++i) {
+        const Request& r = m->requests[slots[i]];
+        const int keep = ceil_div(r.computed_len, m->groups[g].page_size);
+        if ((int)r.table[g].size() > keep) stale += (int)r.table[g].size() - keep;
+      }
+      if (need[g] > (int)m->groups[g].free_stack.size() + stale) return ERR_CAPACITY;
+    }
+  }
   for (int i = 0; i < n; ++i) {
     const int s = slots[i], cnt = counts[i];
-    if (s < 0 || s >= (int)m->requests.size() || !m->requests[s].live || cnt <= 0) return ERR_ARGUMENT;
     Request& r = m->requests[s];
     const int start = r.computed_len;
+    if (r.reserved_len > start) {  // an uncommitted reservation: back to what is written
+      for (int g = 0; g < G; ++g) {
+        const int keep = ceil_div(start, m->groups[g].page_size);
+        while ((int)r.table[g].size() > keep) {
+          if (r.table[g].back() >= 0 && release_page(m->groups[g], r.table[g].back()) < 0) return ERR_STATE;
+          r.table[g].pop_back();
+        }
+      }
+      r.reserved_len = start;
+    }
     int rc = cm_reserve(h, s, start + cnt);
-    if (rc != 0) return rc;
+    if (rc != 0) return rc;  // cannot happen after the first pass
     q_start[i] = row;
     kv_len[i] = start + cnt;
     state_slots[i] = s;

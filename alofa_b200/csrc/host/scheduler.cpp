@@ -261,7 +261,7 @@ int sched_step(void* h, const int64_t* arr_id, const int* arr_prompt, const int*
     int at = find(s, finished[i]);
     if (at >= 0) clear(s.slots[at]);
   }
-  // 3. one more tick waited; before arrivals, so that a new request starts at 0
+  // 3. the waiting counters of requests already queued go up by one; this tick's arrivals are queued after this, with a count of 0
   for (Slot& sl : s.slots)
     if (sl.state == ST_WAITING) sl.wait_ticks++;
 
@@ -330,7 +330,7 @@ int sched_step(void* h, const int64_t* arr_id, const int* arr_prompt, const int*
     }
 
   int budget = s.token_budget;
-  // 6. decode: running requests first, one token each, in slot order
+  // 6. the token budget is spent on decoding first: every running request gets one token, walked in slot order
   for (size_t i = 0; i < s.slots.size() && budget > 0; ++i) {
     Slot& sl = s.slots[i];
     if (sl.state != ST_RUNNING || sl.progressed) continue;

@@ -112,12 +112,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-#ifdef ALOFA_ATTN_TIMING
-  long long* stamps = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && p.partial_o) ? reinterpret_cast<long long*>(p.partial_o) : nullptr;
-#define TSTAMP(i, k) do { if (stamps && (i) < 32) stamps[(i) * 8 + (k)] = clock64(); } while (0)
-#else
-#define TSTAMP(i, k)
-#endif
   const uint32_t tmem = tmem_base_smem;
   const uint32_t tmem_o = tmem + 256;  // S buffers at columns 0 and 128, O behind them
   pdl_begin();
@@ -166,7 +160,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
           umma_bf16(tmem + (i & 1) * TC_BN, smem_desc_sw128(q_addr + off), smem_desc_sw128(k_addr + off), IDESC_QK, k > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[i & 1]);
-        TSTAMP(i, 0);  // S of block i issued
         return true;
       };
       bool ok = mbar_wait(&q_ready, 0, &abort_flag);
@@ -177,7 +170,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
       for (int i = 0; i < nblk && ok; ++i) {
         if (i + 1 < nblk) ok = issue_qk(i + 1);
         if (!ok || !mbar_wait(&p_full, i & 1, &abort_flag)) break;
-        TSTAMP(i, 1);  // P of block i seen
         tc_fence_after();
         const uint32_t v_addr = smem_u32(kv_ring + (size_t)(i % TC_STAGES) * 2 * TC_KV_BYTES + TC_KV_BYTES);
 #pragma unroll
@@ -187,7 +179,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
         }
         umma_commit(&kv_free[i % TC_STAGES]);  // both products of block i have read its stage
         umma_commit(&pv_done);
-        TSTAMP(i, 2);  // O += P V of block i issued
       }
     }
   } else {
@@ -231,7 +222,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
       ok = mbar_wait(&s_full[i & 1], (i >> 1) & 1, &abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (warp == 2 && lane == 0) TSTAMP(i, 3);  // S of block i complete
       tc_fence_after();
       float s[COLS];
 #pragma unroll
@@ -242,7 +232,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
         for (int j = 0; j < 16; ++j) s[c0 + j] = __uint_as_float(v[j]);
       }
       tmem_ld_wait();
-      if (warp == 2 && lane == 0) TSTAMP(i, 4);  // S read out
       const int j0 = (jb0 + i) * TC_BN + half * COLS;
       const bool all_visible = row_ok && j0 + COLS - 1 <= my_pos && j0 >= my_lo;
       if (!all_visible) {
@@ -289,7 +278,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
         packed[(j >> 1) + 1] = pack_bf16(p2, p3);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      if (warp == 2 && lane == 0) TSTAMP(i, 5);  // exponentials done
       // O belongs to the MMA until the product of the block before is complete.  Every block
       // waits for it, although only a raised maximum needs O: a wait by parity must see every
       // phase of its barrier, or it takes an older phase for the one it wants.
@@ -310,7 +298,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
           }
         }
       }
-      if (warp == 2 && lane == 0) TSTAMP(i, 6);  // O rescaled where needed
       // P over the S it came from: bfloat16 pairs, two keys to a column, this thread's 64 keys in 32 columns
       // (its partner has read the S columns they replace: the two met after reading)
 #pragma unroll
@@ -323,7 +310,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full);
-      if (warp == 2 && lane == 0) TSTAMP(i, 7);  // P written
     }
     if (ok) {
       ok = mbar_wait(&pv_done, (nblk - 1) & 1, &abort_flag);

@@ -66,9 +66,6 @@ struct GemmArgs {
   const int* rope_positions;
   const float* rope_table;  // [positions, head_dim / 2, 2]
   int rope_heads, rope_kv_heads, rope_head_dim;
-#ifdef ALOFA_GEMM_TIMING
-  long long* stamps;  // [8] clock64 of CTA (0,0,0): start, after setup, first data, accumulator done, epilogue done, end
-#endif
 };
 
 // ---------------------------------------------------------------------------
@@ -182,10 +179,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * BM, t0 = blockIdx.y * BN;
-#ifdef ALOFA_GEMM_TIMING
-  const bool probe = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && args.stamps;
-  if (probe && threadIdx.x == 0) args.stamps[0] = clock64();
-#endif
   const int total_slices = (args.K + BK - 1) / BK;
   const int slice_begin = blockIdx.z * args.k_slices_per_split;
   const int slice_end = min(total_slices, slice_begin + args.k_slices_per_split);
@@ -258,9 +251,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     pdl_wait();
     pdl_launch();
   }
-#ifdef ALOFA_GEMM_TIMING
-  if (probe && threadIdx.x == 0) args.stamps[1] = clock64();
-#endif
 
   // The epilogue of the four epilogue warps: warp q reads lanes [32q, 32q + 32) of the accumulator.
   // with_remote (first CTA of a cluster): the other CTAs' accumulators, pushed into `pushed`
@@ -423,9 +413,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int s = i % stages;
         ok = mbar_wait(&full_bar[s], (i / stages) & 1, &abort_flag);
         if (!ok) break;
-#ifdef ALOFA_GEMM_TIMING
-        if (probe && i == 0) args.stamps[2] = clock64();
-#endif
         tc_fence_after();
         const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
         const uint64_t desc_b = smem_desc_sw128(stage + N_ACC * A_BYTES);
@@ -462,9 +449,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     bool ok = n_slices > 0 ? mbar_wait(&acc_bar, 0, &abort_flag) : true;
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
-#ifdef ALOFA_GEMM_TIMING
-    if (probe && warp == 2 && lane == 0) args.stamps[3] = clock64();
-#endif
     epilogue_ok = ok;
     if (ok && !(CLUSTER && rank == 0)) epilogue(false);  // in a cluster the first CTA waits for the others' sums
   }
@@ -472,18 +456,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     cluster_sync_all();  // the pushed accumulators are in the first CTA's shared memory
     if (warp >= 2 && rank == 0 && epilogue_ok) epilogue(true);
   }
-#ifdef ALOFA_GEMM_TIMING
-  if (probe && warp == 2 && lane == 0) args.stamps[4] = clock64();
-#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-#ifdef ALOFA_GEMM_TIMING
-  if (probe && warp == 2 && lane == 0) args.stamps[5] = clock64();
-#endif
   if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
 }
 
@@ -607,10 +585,6 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.x * FEATS, t0 = blockIdx.y * 128;
-#ifdef ALOFA_GEMM_TIMING
-  const bool probe = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && args.stamps;
-  if (probe && threadIdx.x == 0) args.stamps[0] = clock64();
-#endif
   const int total_slices = (args.K + BK - 1) / BK;
   const int slice_begin = blockIdx.z * args.k_slices_per_split;
   const int n_slices = min(total_slices, slice_begin + args.k_slices_per_split) - slice_begin;
@@ -666,9 +640,6 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       for (int i = 0; i < n_slices; ++i) {
         const int s = i % stages;
         if (!mbar_wait(&full_bar[s], (i / stages) & 1, &abort_flag)) break;
-#ifdef ALOFA_GEMM_TIMING
-        if (probe && i == 0) args.stamps[2] = clock64();
-#endif
         tc_fence_after();
         const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
         const uint64_t desc_a = smem_desc_sw128(stage), desc_b = smem_desc_sw128(stage + A_BYTES);
@@ -685,9 +656,6 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
-#ifdef ALOFA_GEMM_TIMING
-    if (probe && warp == 2 && lane == 0) args.stamps[3] = clock64();
-#endif
     const bool staged = (args.N & 3) == 0 && !(GATED && gridDim.z > 1);
     if (ok && staged && t0 + q * 32 < args.T) {
       tokens_epilogue_staged<BNF, EPI>(args, tmem_base, reinterpret_cast<float*>(tiles), q, lane, f0, t0, (int)gridDim.z, (int)blockIdx.z, nullptr);
@@ -788,18 +756,12 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       }
     }
   }
-#ifdef ALOFA_GEMM_TIMING
-  if (probe && warp == 2 && lane == 0) args.stamps[4] = clock64();
-#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-#ifdef ALOFA_GEMM_TIMING
-  if (probe && warp == 2 && lane == 0) args.stamps[5] = clock64();
-#endif
   if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
 }
 
@@ -897,29 +859,14 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     if (lane == 0) {
       int it = 0, j = 0;  // slices consumed; tiles of this CTA so far
       bool ok = true;
-#ifdef ALOFA_GEMM_TIMING
-      long long t_start = clock64(), wait_full = 0, wait_acc = 0;
-#endif
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
         const int buf = j & 1;
-#ifdef ALOFA_GEMM_TIMING
-        long long ta = clock64();
-#endif
         if (j >= 2) ok = mbar_wait(&acc_free[buf], ((j >> 1) - 1) & 1, &abort_flag);
-#ifdef ALOFA_GEMM_TIMING
-        wait_acc += clock64() - ta;
-#endif
         if (!ok) break;
         tc_fence_after();
         for (int i = 0; i < n_slices; ++i, ++it) {
           const int s = it % PERSISTENT_STAGES;
-#ifdef ALOFA_GEMM_TIMING
-          long long tf = clock64();
-#endif
           ok = mbar_wait(&full_bar[s], (it / PERSISTENT_STAGES) & 1, &abort_flag);
-#ifdef ALOFA_GEMM_TIMING
-          wait_full += clock64() - tf;
-#endif
           if (!ok) break;
           tc_fence_after();
           const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
@@ -931,14 +878,6 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
         }
         if (ok) umma_commit(&acc_full[buf]);
       }
-#ifdef ALOFA_GEMM_TIMING
-      if (blockIdx.x == 0 && args.stamps) {
-        args.stamps[0] = clock64() - t_start;  // the MMA thread's life
-        args.stamps[1] = wait_full;            // of it: waiting for operand tiles
-        args.stamps[2] = wait_acc;             // waiting for the epilogue to free an accumulator
-        args.stamps[3] = j;                    // tiles
-      }
-#endif
     }
   } else {
     const int q = warp & 3;
@@ -1235,10 +1174,6 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   args.b_window = b_window;
   args.b_split_keys = b_split_keys;
   args.cluster = alofa_gemm_tc_reduces_in_cluster(epi, bn, splits) && do_reduce && b_kind == B_ROWS;
-#ifdef ALOFA_GEMM_TIMING
-  args.stamps = (long long*)status;  // the timing build reuses the status pointer for its stamps
-  args.status = nullptr;
-#endif
   int rc;
   if (tokens_on_m) {
     if (epi == EPI_STORE) rc = dispatch_tokens<EPI_STORE>(bnf, mw, mx, args, splits, stream);

@@ -21,16 +21,21 @@
  *   logits       [n_rows, vocab] float32, device
  *   temperature  [n_rows] float32, device, or NULL (all rows greedy)
  *   uniform      [n_rows] float32 in [0, 1), device, or NULL
- *   any_hot      0 promises that no temperature is positive
+ *   any_hot      0 promises that no temperature is positive (a row that breaks
+ *                the promise gets its largest logit)
  *
  * Returns 0 on success, ALOFA_NOALLOC_TOO_MANY_ROWS when n_rows exceeds
- * ALOFA_NOALLOC_MAX_ROWS (nothing is launched), 1 for other bad arguments,
- * 2 when the CUDA runtime refuses (symbol lookup or launch).
+ * ALOFA_NOALLOC_MAX_ROWS (nothing is launched), 1 for other bad arguments -
+ * among them any_hot set and temperature given without uniform: a row that
+ * draws needs its uniform number, and is refused rather than left unwritten -
+ * and 2 when the CUDA runtime refuses (symbol lookup or launch).
  *
  * The first call on a device looks up the array's device address (with that
  * device current) and remembers it; make that first call before any stream
- * capture begins.  All calls on a device share the one array: it still holds
- * the previous call's values when the next call starts (every entry a call
+ * capture begins.  Host threads may make that first call at the same time:
+ * each then looks the same address up and stores the same value.  All calls
+ * on a device share the one array: it still holds the previous call's values
+ * when the next call starts (every entry a call
  * reads is written by that call first, so nothing needs clearing), and two
  * calls that overlap on the GPU - different streams, no ordering between them
  * - race on it.  Keep calls on one stream, or order them yourself.

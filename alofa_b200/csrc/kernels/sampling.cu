@@ -162,7 +162,8 @@ __global__ void argmax_final_kernel(int* __restrict__ tokens, const float* __res
                                     const float* __restrict__ temperature) {
   const int r = blockIdx.x, lane = threadIdx.x;  // one warp per row
   pdl_begin();
-  if (temperature && temperature[r] > 0.f) return;
+  // every row gets its largest logit; rows with a positive temperature are overwritten by
+  // sample_hot_kernel when it runs, and keep the largest logit when the caller promised no such row
   ArgMax best{part_val[r * ARGMAX_PARTS + lane], part_idx[r * ARGMAX_PARTS + lane]};
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -205,6 +206,7 @@ ALOFA_API int alofa_sample(int* tokens, const float* logits, const float* temper
     launch_dep(sample_kernel, n_rows, SAMPLE_THREADS, 0, stream, tokens, logits, temperature, uniform, vocab);
     return launch_status();
   }
+  if (any_hot && temperature && !uniform) return ALOFA_ERR_ARGUMENT;  // a draw needs its uniform number
   float* part_val = (float*)scratch;
   int* part_idx = (int*)(part_val + (size_t)n_rows * ARGMAX_PARTS);
   ALOFA_PREFER_MAX_SHARED(argmax_parts_kernel);
@@ -224,7 +226,9 @@ static __device__ __align__(256) float g_noalloc_scratch[2 * ALOFA_NOALLOC_MAX_R
 
 // Device address of g_noalloc_scratch on the current device, looked up once per
 // device.  In host code the array's name is only a handle for this lookup; it
-// is not an address a kernel could use.
+// is not an address a kernel could use.  Two host threads that make their first
+// call on a device at the same moment both look the address up and both store
+// the same value: harmless, and not guarded.
 static float* noalloc_scratch_address() {
   static float* address[64] = {nullptr};
   int device = 0;
@@ -247,6 +251,7 @@ ALOFA_API int alofa_sample_noalloc(int* tokens, const float* logits, const float
   if (n_rows <= 0) return ALOFA_OK;
   if (n_rows > ALOFA_NOALLOC_MAX_ROWS) return ALOFA_NOALLOC_TOO_MANY_ROWS;
   if (!tokens || !logits || vocab <= 0) return ALOFA_ERR_ARGUMENT;
+  if (any_hot && temperature && !uniform) return ALOFA_ERR_ARGUMENT;  // a draw needs its uniform number
   float* scratch = noalloc_scratch_address();
   if (!scratch) return ALOFA_ERR_LAUNCH;
   float* part_val = scratch;

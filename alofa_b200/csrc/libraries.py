@@ -12,5 +12,4 @@ def all_libraries() -> list:
         {"name": "alofa_gemm_tc", "sources": ["kernels/gemm_tc.cu"]},
         {"name": "alofa_elementwise_bf16", "sources": ["kernels/elementwise_bf16.cu"]},
         *[{"name": f"alofa_attention_hd{hd}", "sources": ["kernels/attention_bf16.cu"], "defines": {"HEAD_DIM": hd}} for hd in (16, 32, 48, 64, 128)],
-        *[{"name": f"alofa_program_hd{hd}", "sources": ["kernels/decode_program.cu"], "defines": {"HEAD_DIM": hd}} for hd in (64, 128)],
     ]

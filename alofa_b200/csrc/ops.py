@@ -97,53 +97,6 @@ def _attention(head_dim: int):
     return lib
 
 
-PROGRAM_MAX_TOKENS = 16          # tokens a decode program takes (rows of one mma tile)
-PROGRAM_MAX_SMEM = 220 * 1024    # shared memory the program kernel may ask for
-
-
-def program_supported(head_dim: int) -> bool:
-    """Head sizes the decode-program kernel is built for."""
-    return head_dim in (64, 128)
-
-
-def program_library(head_dim: int):
-    key = f"program_hd{head_dim}"
-    lib = _libs.get(key)
-    if lib is None:
-        lib = load_library(f"alofa_program_hd{head_dim}", ["kernels/decode_program.cu"], defines={"HEAD_DIM": head_dim})
-        LL = ctypes.c_longlong
-        lib.alofa_program_phase_bytes.restype = _I
-        lib.alofa_program_smem_bytes.restype = LL
-        lib.alofa_program_smem_bytes.argtypes = [_P, _I]
-        lib.alofa_program_grid.restype = _I
-        lib.alofa_program_splits.restype = _I
-        lib.alofa_program_splits.argtypes = [_I]
-        lib.alofa_program_embed.restype = _I
-        lib.alofa_program_embed.argtypes = [_P, _P, _P, _P, _P, _P, _I, _I, _I]
-        lib.alofa_program_linear.restype = _I
-        lib.alofa_program_linear.argtypes = [_P, _I, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I]
-        lib.alofa_program_attention.restype = _I
-        lib.alofa_program_attention.argtypes = [_P, _P, _P, _P, _P, LL, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P]
-        lib.alofa_program_run.restype = _I
-        lib.alofa_program_run.argtypes = [_P, _I, _P, _P, LL, _P]
-        _libs[key] = lib
-    return lib
-
-
-def program_grid() -> int:
-    """CTAs of the decode-program kernel (one per SM)."""
-    grid = program_library(64).alofa_program_grid()
-    if grid <= 0:
-        raise AlofaError("state", "no CUDA device to run a decode program on")
-    return grid
-
-
-def program_run(lib, phases, n_phases: int, sync, status, smem: int) -> None:
-    """Run a decode program (descriptors in device memory) on the current stream."""
-    rc = lib.alofa_program_run(_dev(phases, "phases", torch.uint8), n_phases, _dev(sync, "sync", torch.int32), _dev(status, "status", torch.int32), smem, _stream())
-    _done(rc, "decode_program", f"phases={n_phases} smem={smem}")
-
-
 def attention_bf16_supported(head_dim: int) -> bool:
     """Head sizes the bfloat16 attention kernel is built for."""
     return head_dim % 16 == 0 and 16 <= head_dim <= 128

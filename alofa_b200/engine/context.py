@@ -67,8 +67,9 @@ class Layout:
 class StepContext:
     """Per-step batch description plus scratch allocation."""
 
-    def __init__(self, rt, layout: Layout, dev_meta: torch.Tensor, host_meta: np.ndarray, groups: list, status: torch.Tensor):
+    def __init__(self, rt, layout: Layout, dev_meta: torch.Tensor, host_meta: np.ndarray, groups: list, status: torch.Tensor, arena):
         self.rt = rt
+        self.arena = arena
         self.layout = layout
         self.n_tokens, self.n_seqs, self.n_out = layout.n_tokens, layout.n_seqs, layout.n_out
         self.host = host_meta
@@ -133,5 +134,14 @@ class StepContext:
         return self.host[at : at + count]
 
     def buf(self, shape, dtype) -> torch.Tensor:
-        """Scratch for this step (uninitialised)."""
-        return torch.empty(shape, dtype=dtype, device=self.rt.device)
+        """Scratch for this step (uninitialised): a slice of the step runner's
+        arena, nothing is allocated.  Inside a layer it is valid until the
+        layer after the next begins, outside until the step ends."""
+        return self.arena.buf(shape, dtype)
+
+    def begin_layer(self) -> None:
+        """The model calls this before each entry of its run list."""
+        self.arena.begin_layer()
+
+    def end_layers(self) -> None:
+        self.arena.end_layers()

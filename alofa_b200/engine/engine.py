@@ -50,6 +50,7 @@ class InFlight:
     epochs: list        # their preemption counts at launch: a request preempted since is skipped
     row_of: dict        # request id -> row
     host: "torch.Tensor"  # pinned; the tokens arrive here
+    status: "torch.Tensor"  # pinned [1]; the kernels' status word arrives here with the tokens
     event: "torch.cuda.Event"
     finishing: list     # requests the scheduler ended with this step
     kind: str
@@ -103,7 +104,12 @@ class Engine:
         if self._trace:
             self._trace.write(format_config(self.sched_config) + "\n")
         self._inflight: Optional[InFlight] = None
-        self._pinned = [torch.zeros(max(step_tokens, 1), dtype=torch.int32).pin_memory() for _ in range(2)]
+        on_gpu = self.runner.rt.device.type == "cuda"
+        pin = (lambda t: t.pin_memory()) if on_gpu else (lambda t: t)
+        self._pinned = [pin(torch.zeros(max(step_tokens, 1), dtype=torch.int32)) for _ in range(2)]
+        # the status word the kernels raise (a wait that ran out, a token id outside the vocabulary)
+        # comes to the host with every step's tokens, behind the same event
+        self._pinned_status = [pin(torch.zeros(1, dtype=torch.int32)) for _ in range(2)]
         self._pin_flip = 0
         self.overlap = bool(cfg.overlap_steps) and self.runner.feeds_tokens
         self.marks = []  # (time a step's tokens reached the host, kind, rows)
@@ -244,14 +250,15 @@ class Engine:
         t0 = time.perf_counter()
         rows = sum(len(e.tokens) for e in entries)
         ctx, logits, tokens = self.runner.forward_sampled(entries)
-        host = self._pinned[self._pin_flip]
+        host, status = self._pinned[self._pin_flip], self._pinned_status[self._pin_flip]
         self._pin_flip ^= 1
         n = len(owners)
         if n:
             host[:n].copy_(tokens[:n], non_blocking=True)
+        self.runner.copy_status(status)
         event = torch.cuda.Event()
         event.record()
-        return InFlight(owners, [r.preemptions for r in owners], {r.id: i for i, r in enumerate(owners)}, host, event, finishing, kind, rows, t0)
+        return InFlight(owners, [r.preemptions for r in owners], {r.id: i for i, r in enumerate(owners)}, host, status, event, finishing, kind, rows, t0)
 
     def _settle(self) -> None:
         """Read the tokens of the step in flight, if any, and act on them."""
@@ -260,6 +267,7 @@ class Engine:
             return
         self._inflight = None
         fl.event.synchronize()
+        self.runner.raise_status(int(fl.status[0]))  # tokens of a step whose kernels gave up are not handed out
         picked = fl.host[: len(fl.owners)].tolist()
         self._account(fl.kind, fl.rows, fl.t0)
         for req, epoch, tok in zip(fl.owners, fl.epochs, picked):
@@ -276,10 +284,15 @@ class Engine:
         rows = sum(len(e.tokens) for e in entries)
         ctx, logits, tokens = self.runner.forward_sampled(entries)
         picked = []
+        status = self._pinned_status[self._pin_flip]
         if logits is not None:
             if not all(req.params.plain() for req in owners):
                 tokens = sample_rows(ctx, logits, owners)
-            picked = tokens.cpu().tolist()
+            self.runner.copy_status(status)
+            picked = tokens.cpu().tolist()  # waits for the stream: the status word is on the host too
+            self.runner.raise_status(int(status[0]))
+        # (a portion of a prompt nobody samples from is not waited for: the word stays raised
+        # until it is read, so the step that yields the request's first token reports it)
         self._account(kind, rows, t0)
         for req, tok in zip(owners, picked):
             self._take(req, int(tok))

@@ -29,10 +29,10 @@ from ..cache.manager import CacheManager, GroupSpec
 from ..cache.storage import CacheStorage, group_windows
 from ..csrc import ops
 from ..errors import AlofaError
-from ..parts.base import Ineligible, PagedKV
+from ..parts.base import PagedKV
 from ..parts.model import Model
+from .arena import Arena
 from .context import GroupView, Layout, StepContext
-from .program import DecodeProgram
 
 
 @dataclass
@@ -54,7 +54,6 @@ class DecodeGraph:
     logits: Optional[torch.Tensor]
     tokens: Optional[torch.Tensor]
     kernels: int
-    program: Optional[DecodeProgram] = None  # the step as one resident kernel, when the model and the sizes allow
 
 
 class StepRunner:
@@ -87,16 +86,18 @@ class StepRunner:
         # the tokens of the last sampled step stay here, where the next step's embedding can read them
         self._fed = torch.zeros(max(max_step_tokens, 1), dtype=torch.int32, device=self.rt.device)
         self.feeds_tokens = bool(getattr(model.embedding, "reads_fed_tokens", False))
+        # Scratch of every step: sized once here for the largest step (its rows' longest-lived
+        # buffers, one row of logits per request) and handed out as slices; nothing is allocated per step.
+        step_row, layer_row = model.scratch_row_bytes()
+        vocab_bytes = 4 * model.spec.vocab_size
+        self.arena = Arena(self.rt.device, max_step_tokens * step_row + max_requests * vocab_bytes * 5 // 4 + (1 << 20),
+                           max_step_tokens * layer_row * 5 // 4 + (4 << 20))
         self._layouts = {}
         self.cuda_graphs = cuda_graphs and on_gpu and model.graph_safe()
         self._graphs = {}  # decode steps by batch size; steps with prompt portions by (tokens, requests, wanted rows)
         self.prompt_graphs = self.cuda_graphs and os.environ.get("ALOFA_PROMPT_GRAPHS", "1") != "0"
         self.max_prompt_graphs = 4
         self._seen_shapes = {}
-        # Small decode steps as one resident kernel: ALOFA_DECODE_PROGRAM=1.  Off unless asked for:
-        # measured at the benchmark's sizes, a layer takes longer in the resident kernel (barriers over
-        # the grid and operand loads that cannot start before them) than as ten dependent launches.
-        self.decode_programs = self.cuda_graphs and os.environ.get("ALOFA_DECODE_PROGRAM", "0") == "1"
 
     # -- requests -----------------------------------------------------------
     def admit(self, request_id: int) -> int:
@@ -187,7 +188,8 @@ class StepRunner:
             ev = torch.cuda.Event()
             ev.record()
             self._host_event[flip] = ev
-        ctx = StepContext(self.rt, layout, self._dev_meta, host, self._group_shapes, self._status)
+        ctx = StepContext(self.rt, layout, self._dev_meta, host, self._group_shapes, self._status, self.arena)
+        self.arena.begin_step()
         ctx.fed_tokens = self._fed if self.feeds_tokens else None
         ctx.max_q_len, ctx.max_kv_len = max_q, max_kv
         ctx.decode_only = max_q == 1
@@ -200,19 +202,31 @@ class StepRunner:
         """The step's entries are written: advance the cache manager."""
         self.manager.commit_step(ctx.slots, ctx.counts)
 
+    def _context_bucket(self, longest: int) -> int:
+        """Decode graphs are recorded per batch size and per bucket of the
+        longest context in the step (powers of two): the number of key splits
+        that attention launches inside a graph then follows the real lengths
+        instead of the longest context the engine allows."""
+        bucket = 256
+        while bucket < longest:
+            bucket *= 2
+        return min(bucket, max(self.max_tokens, 1))
+
     def _run(self, ctx: StepContext, sample: bool):
         """(logits or None, tokens or None) for a prepared step."""
         if self.cuda_graphs and ctx.decode_only and ctx.n_out == ctx.n_seqs:
-            g = self._graphs.get(ctx.n_seqs)
+            ctx.max_context = self._context_bucket(ctx.max_kv_len)
+            key = (ctx.n_seqs, ctx.max_context, "decode")
+            g = self._graphs.get(key)
             if g is None:
-                g = self._capture(ctx, ctx.n_seqs)
+                return self._capture(ctx, key, sample)
             g.graph.replay()
             ops.count_launches(g.kernels)
             return g.logits, g.tokens
         if self.prompt_graphs and not ctx.decode_only:
             # A step with prompt portions is some two hundred launches, about as long to issue from
             # Python as to run: a shape (tokens, requests, wanted rows) met a third time is recorded
-            # (which costs two more runs of it) and replayed from then on.  A few shapes are kept, the least recently used one goes.
+            # and replayed from then on.  A few shapes are kept, the least recently used one goes.
             key = (ctx.n_tokens, ctx.n_seqs, ctx.n_out)
             g = self._graphs.pop(key, None)
             if g is None:
@@ -221,11 +235,12 @@ class StepRunner:
                     self._seen_shapes.clear()
                 self._seen_shapes[key] = seen + 1
                 if seen >= 2:
-                    kept = [k for k in self._graphs if isinstance(k, tuple)]
+                    kept = [k for k in self._graphs if len(k) == 3 and k[2] != "decode"]
                     if len(kept) >= self.max_prompt_graphs:
                         del self._graphs[kept[0]]
-                    g = self._capture(ctx, key)
-                    self._graphs.pop(key)
+                    logits, tokens = self._capture(ctx, key, sample)
+                    self._graphs[key] = self._graphs.pop(key)  # most recently used last
+                    return (logits if ctx.n_out else None), (tokens if ctx.n_out else None)
             if g is not None:
                 self._graphs[key] = g  # most recently used last
                 g.graph.replay()
@@ -246,46 +261,37 @@ class StepRunner:
         ops.sample(tokens, logits, ctx.temperature, ctx.uniform, scratch, any_hot)
         return tokens
 
-    def _capture(self, ctx: StepContext, key) -> DecodeGraph:
-        """Record the step of this shape as a CUDA graph.  The step is first run
-        once outright (its cache writes are the same ones the replay repeats),
-        which also loads every kernel before recording.  Launch shapes inside
-        must depend on the shape alone: attention is sized for the longest
-        context and for one request holding all tokens but one each of the others."""
+    def _capture(self, ctx: StepContext, key, sample: bool):
+        """Run the step outright and record it as a CUDA graph for the next
+        time its shape comes; returns this run's (logits, tokens).  The step is
+        executed once only: recording launches nothing, and the recorded graph
+        is first replayed by the NEXT step of this shape, so a part that
+        updates per-request state in place advances it once per step.  The
+        outright run also loads every kernel before recording and makes the
+        arena grow, if it has to, outside the recording; both passes rewind the
+        arena first, so they get the same addresses.  Launch shapes inside must
+        depend on the shape alone: attention is sized for the bucket of the
+        longest context, and in steps with prompt portions for one request
+        holding all tokens but one each of the others."""
         ctx.capturing = True
         if not ctx.decode_only:
             ctx.max_q_len = ctx.n_tokens - ctx.n_seqs + 1
-        program = self._program(ctx) if ctx.decode_only else None
-        if program is not None:
-            program.run()
-        else:
-            self.model.forward(ctx, self.storage.caches)
+        with ops.bound_stream():
+            self.arena.begin_step()
+            first_logits = self.model.forward(ctx, self.storage.caches)
+            first_tokens = self._sample(ctx, first_logits, ctx.any_hot) if (sample and first_logits is not None) else None
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
+        grown = self.arena.grown
         with torch.cuda.graph(graph), ops.bound_stream():
-            if program is not None:
-                program.run()
-                logits = program.logits
-            else:
-                logits = self.model.forward(ctx, self.storage.caches)
+            self.arena.begin_step()
+            logits = self.model.forward(ctx, self.storage.caches)
             tokens = self._sample(ctx, logits, True) if logits is not None else None  # a replay may meet rows of any temperature
-        entry = DecodeGraph(graph, logits, tokens, ops.launch_count() - before, program)
-        self._graphs[key] = entry
-        return entry
-
-    def _program(self, ctx: StepContext) -> Optional[DecodeProgram]:
-        """The decode step of this batch size as a program for the resident
-        kernel, or None when a part or a size rules it out."""
-        if not self.decode_programs:
-            return None
-        try:
-            program = DecodeProgram(ctx)
-            program.logits = self.model.emit(program, ctx, self.storage.caches)
-            program.finish()
-        except Ineligible:
-            return None
-        return program
+        if self.arena.grown != grown or (logits is not None and logits.data_ptr() != first_logits.data_ptr()):
+            raise AlofaError("state", "recording a step asked the arena for other memory than running it did")
+        self._graphs[key] = DecodeGraph(graph, logits, tokens, ops.launch_count() - before)
+        return first_logits, first_tokens
 
     def forward(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; logits (fp32, on the device) at the wanted places in
@@ -314,9 +320,21 @@ class StepRunner:
     def check_status(self) -> None:
         """Raise if a kernel flagged bad input since the last check (reads the
         device, so it waits for the stream)."""
-        code = int(self._status.item())
-        if code != 0:
-            self._status.zero_()
-            if code == 2:
-                raise AlofaError("state", "a kernel gave up waiting on its own pipeline")
-            raise AlofaError("out_of_range", "a kernel met a token id outside the vocabulary")
+        self.raise_status(int(self._status.item()))
+
+    def copy_status(self, host: torch.Tensor) -> None:
+        """Queue a copy of the status word into ``host`` (pinned, int32 [1])
+        behind the work already on the stream; the caller reads it once an
+        event recorded after this call has passed and hands the value to
+        :meth:`raise_status`."""
+        host.copy_(self._status, non_blocking=True)
+
+    def raise_status(self, code: int) -> None:
+        """Turn a status word read from the device into the error it stands
+        for; the word is cleared so that the next step starts clean."""
+        if code == 0:
+            return
+        self._status.zero_()
+        if code == 2:
+            raise AlofaError("state", "a kernel gave up waiting on its own pipeline")
+        raise AlofaError("out_of_range", "a kernel met a token id outside the vocabulary")

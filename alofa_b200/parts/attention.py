@@ -20,7 +20,7 @@ import torch
 from ..csrc import ops
 from ..errors import AlofaError
 from . import fast_linear
-from .base import Ineligible, PagedKV, Part, TensorSpec, as_float32_vector, build_part, register_part
+from .base import PagedKV, Part, TensorSpec, as_float32_vector, build_part, register_part
 from .linear import RESIDUAL, STORE, Linear, MergedSplits
 
 
@@ -52,6 +52,10 @@ class GQAttention(Part):
 
     def cache_spec(self):
         return PagedKV(self.nkv, self.hd, self.window)
+
+    def scratch_row_bytes(self) -> int:
+        # q/k/v, q, the attention output, and the output product's split sums
+        return 4 * (self.q_dim + 2 * self.kv_dim) + 2 * 4 * self.q_dim + 2 * 4 * self.hidden
 
     def tensors(self):
         pre = self.prefix
@@ -106,10 +110,10 @@ class GQAttention(Part):
         ):
             owed = None
         else:
-            owed = lin(qkv, x, defer=vectorised)
+            owed = lin(qkv, x, defer=vectorised, buf=ctx.buf)
             self._rotate_and_store(ctx, q, qkv, owed, cache, group, table, rot, custom, vectorised, nkv_in, writes)
         attn = self.attend(ctx, q, cache, group)
-        owed = self.out(h, attn, defer=True)
+        owed = self.out(h, attn, defer=True, buf=ctx.buf)
         if owed is not None:
             ctx.set_pending(h, owed)
 
@@ -127,19 +131,6 @@ class GQAttention(Part):
                 k_view = qkv[:, self.q_dim : self.q_dim + nkv_in * self.hd].view(n, nkv_in, self.hd)
                 custom(ctx, q_view, k_view)
             ops.rope_store(q, cache.k, cache.v, qkv, table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, rot, writes)
-
-    def emit(self, prog, ctx, x, h, cache, writes=True):
-        group = ctx.groups[cache.group]
-        table, rot = self.position.rotary_table()
-        if getattr(self.position, "apply", None) is not None or rot != self.hd or group.page_size % 64:
-            raise Ineligible("the program rotates whole heads from a table and reads pages that hold whole 64-key blocks")
-        lin = self.qkv if writes else self.q_only
-        q = prog.buf((ctx.n_tokens, self.q_dim), torch.bfloat16)
-        prog.rope_store(x, lin.weight, lin.bias, q, cache.k, cache.v, group.slot_map, ctx.positions, table, self.nh, self.nkv, self.hd, writes)
-        attn = prog.buf((ctx.n_tokens, self.q_dim), torch.bfloat16)
-        prog.attention(attn, q, cache.k, cache.v, ctx.kv_len, group.block_table, group.page_size, self.nh, self.nkv, self.hd,
-                       self.window, self.scale, ctx.max_context)
-        prog.linear(prog.rows(attn), self.out.weight, self.out.bias, prog.RESIDUAL, h)
 
     SPLIT_KEYS = 256  # keys per CTA when a decode-only step splits each request's keys (four 64-key blocks, one per warp)
     # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.
@@ -177,7 +168,7 @@ class GQAttention(Part):
                 self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest, ctx.status, combine=not unmerged,
             )
             if unmerged:
-                return MergedSplits(po, pml, ctx.positions, ctx.n_tokens, self.nh, self.hd, self.window, per_split)
+                return MergedSplits(po, pml, ctx.positions, ctx.n_tokens, self.nh, self.hd, self.window, per_split, ctx.buf)
             return out
         ops.paged_attention_generic(
             out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,

@@ -71,11 +71,6 @@ class Runtime:
     dtype: torch.dtype  # torch.float32 (true 32-bit path) or torch.bfloat16
 
 
-class Ineligible(Exception):
-    """A step cannot be run as a decode program (a part without ``emit``, a
-    size the program kernel does not take); the caller launches kernels."""
-
-
 class Part:
     """Base of all parts.  Constructors only record sizes; device memory is
     touched in :meth:`load`."""
@@ -97,12 +92,6 @@ class Part:
 
     def load(self, state: dict) -> None:
         pass
-
-    def emit(self, prog, *args, **kwargs):
-        """Write this part's share of a decode step into a program (the
-        arguments of ``forward`` after the program).  Parts that can run
-        inside the resident decode kernel override it."""
-        raise Ineligible(f"part {self.spec.kind} has no emit")
 
     def param(self, key, default=None):
         if key not in self.params:

@@ -38,6 +38,9 @@ class PrenormResidual(Part):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
+    def scratch_row_bytes(self) -> int:
+        return sum(getattr(part, "scratch_row_bytes", lambda: 0)() for part in self.parts())
+
     absorbs_pending = True  # its norms add partial sums owed to h; other readers get them flushed first
 
     def _norm(self, norm, ctx, h):
@@ -50,11 +53,6 @@ class PrenormResidual(Part):
         self.mixer.forward(ctx, x, h, cache, writes)
         x = self._norm(self.feed_forward_norm, ctx, h)
         self.feed_forward.forward(ctx, x, h)
-
-
-    def emit(self, prog, ctx, h, cache, writes=True):
-        self.mixer.emit(prog, ctx, self.mixer_norm.emit(prog, ctx, h), h, cache, writes)
-        self.feed_forward.emit(prog, ctx, self.feed_forward_norm.emit(prog, ctx, h), h)
 
 
 register_part("block", "prenorm_residual", PrenormResidual)

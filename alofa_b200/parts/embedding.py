@@ -35,10 +35,6 @@ class TokenEmbedding(Part):
     def forward(self, ctx, h):
         ops.embed_gather(h, self.weight, ctx.token_ids, ctx.status, ctx.token_src if ctx.fed_tokens is not None else None, ctx.fed_tokens)
 
-    def emit(self, prog, ctx, h):
-        prog.embed(h, self.weight, ctx.token_ids, ctx.token_src if ctx.fed_tokens is not None else None, ctx.fed_tokens)
-
-
 class LinearHead(Part):
     family = "head"
     graph_safe = True
@@ -65,14 +61,8 @@ class LinearHead(Part):
 
     def forward(self, ctx, x):
         logits = ctx.buf((x.shape[0], self.vocab), torch.float32)
-        self.linear(logits, x)
+        self.linear(logits, x, buf=ctx.buf)
         return logits
-
-    def emit(self, prog, ctx, x):
-        logits = prog.buf((ctx.n_tokens, self.vocab), torch.float32)
-        prog.linear(x, self.linear.weight, None, prog.STORE_F32, logits)
-        return logits
-
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("head", "linear_head", LinearHead)

@@ -68,7 +68,7 @@ def plan(linear):
     gated = linear.epi == ops.EPI_GATED
     n_acc = 2 if gated else 1
 
-    def run(out, x, defer: bool = False):
+    def run(out, x, defer: bool = False, buf=None):
         tokens = x.shape[0]
         if tokens == 0:
             return True
@@ -90,7 +90,8 @@ def plan(linear):
             return False
         partial = None
         if splits > 1:
-            partial = torch.empty((splits * n_acc, tokens, linear.out_features), dtype=torch.float32, device=w.device)
+            shape = (splits * n_acc, tokens, linear.out_features)
+            partial = buf(shape, torch.float32) if buf is not None else torch.empty(shape, dtype=torch.float32, device=w.device)
         deferred = defer and splits > 1 and n_acc == 1
         dst = partial[0] if deferred else out  # a deferred product writes partial sums only
         if not ops.gemm_tc(dst, x, w, linear.bias, linear.epi, bn, splits, partial, reduce=not deferred, computed=computed):

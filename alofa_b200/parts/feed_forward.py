@@ -38,18 +38,15 @@ class GatedMLP(Part):
         self.gate_up = Linear(torch.cat([state[pre + "gate_proj.weight"], state[pre + "up_proj.weight"]], dim=0), None, GATED)
         self.down = Linear(state[pre + "down_proj.weight"], None, RESIDUAL)
 
+    def scratch_row_bytes(self) -> int:
+        return 4 * self.inter + 2 * 4 * self.hidden  # the activation, and the down product's depth split in two
+
     def forward(self, ctx, x, h):
         act = ctx.buf((x.shape[0], self.inter), self.rt.dtype)
-        self.gate_up(act, x)
-        owed = self.down(h, act, defer=True)
+        self.gate_up(act, x, buf=ctx.buf)
+        owed = self.down(h, act, defer=True, buf=ctx.buf)
         if owed is not None:
             ctx.set_pending(h, owed)
-
-
-    def emit(self, prog, ctx, x, h):
-        act = prog.buf((ctx.n_tokens, self.inter), torch.bfloat16)
-        prog.linear(x, self.gate_up.weight, None, prog.GATED, act)
-        prog.linear(prog.rows(act), self.down.weight, None, prog.RESIDUAL, h)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -43,8 +43,9 @@ class MergedSplits:
 
     dtype = torch.bfloat16
 
-    def __init__(self, partial_o, partial_ml, positions, tokens: int, heads: int, head_dim: int, window, split_keys: int):
+    def __init__(self, partial_o, partial_ml, positions, tokens: int, heads: int, head_dim: int, window, split_keys: int, buf):
         self.partial_o, self.partial_ml, self.positions = partial_o, partial_ml, positions
+        self.buf = buf  # the step's scratch allocator
         self.heads, self.head_dim, self.window, self.split_keys = heads, head_dim, window, split_keys
         self.shape = (tokens, heads * head_dim)
 
@@ -55,7 +56,7 @@ class MergedSplits:
         return (ops.B_MERGED_SPLITS, self.partial_o, self.partial_ml, self.positions, self.heads, self.head_dim, self.window, self.split_keys)
 
     def rows(self) -> torch.Tensor:
-        out = torch.empty(self.shape, dtype=torch.bfloat16, device=self.partial_o.device)
+        out = self.buf(self.shape, torch.bfloat16)
         ops.attention_combine(out, self.partial_o, self.partial_ml, self.positions, self.heads, self.head_dim, self.window, self.split_keys)
         return out
 
@@ -78,13 +79,15 @@ class Linear:
 
             self._fast = fast_linear.plan(self)
 
-    def __call__(self, out: Optional[torch.Tensor], x, defer: bool = False) -> Optional[Partial]:
+    def __call__(self, out: Optional[torch.Tensor], x, defer: bool = False, buf=None) -> Optional[Partial]:
         """Run the product.  ``x`` is a tensor of rows, or rows still to be
         made (:class:`MergedSplits`).  With ``defer`` the
         result may come back as a :class:`Partial` (``out`` is then
-        untouched); else None."""
+        untouched); else None.  ``buf(shape, dtype)`` is the step's scratch
+        allocator (``ctx.buf``), used for split sums; without it they are
+        allocated."""
         if self._fast is not None and x.dtype == torch.bfloat16:
-            done = self._fast(out, x, defer)
+            done = self._fast(out, x, defer, buf)
             if done is not False:
                 return done if isinstance(done, Partial) else None
         if not isinstance(x, torch.Tensor):

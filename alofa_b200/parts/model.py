@@ -41,6 +41,13 @@ class Model:
         """True when every part may be recorded in a CUDA graph."""
         return all(part.graph_safe for part in self.parts())
 
+    def scratch_row_bytes(self) -> tuple:
+        """(bytes per token that live for a whole step, bytes per token of the
+        layer that needs most): what the step runner sizes its arena from."""
+        hidden = self.spec.hidden_size
+        per_layer = max([getattr(block, "scratch_row_bytes", lambda: 0)() for block in self.layers] + [8 * hidden])
+        return 4 * hidden + 4 * hidden, per_layer
+
     def cache_plan(self) -> dict:
         """run index -> cache spec, for the entries that own a cache."""
         return {i: self.layers[layer].cache_spec() for i, (layer, cache) in enumerate(self.run) if cache == i}
@@ -54,7 +61,9 @@ class Model:
             block = self.layers[layer]
             if not getattr(block, "absorbs_pending", False):
                 ctx.flush_pending()
+            ctx.begin_layer()
             block.forward(ctx, h, caches.get(cache), writes=(cache == i))
+        ctx.end_layers()
         if ctx.n_out == 0:  # a prompt portion whose logits nobody wants
             ctx.pending = None
             return None
@@ -63,15 +72,6 @@ class Model:
         x = self.final_norm.forward(ctx, h, ctx.logit_rows)
         ctx.pending = None
         return self.head.forward(ctx, x)
-
-    def emit(self, prog, ctx, caches: dict) -> torch.Tensor:
-        """The same step written into a decode program; the logits buffer."""
-        h = prog.buf((ctx.n_tokens, self.spec.hidden_size), torch.float32)
-        self.embedding.emit(prog, ctx, h)
-        for i, (layer, cache) in enumerate(self.run):
-            self.layers[layer].emit(prog, ctx, h, caches.get(cache), writes=(cache == i))
-        return self.head.emit(prog, ctx, self.final_norm.emit(prog, ctx, h, ctx.logit_rows))
-
 
 def expected_tensors(spec: ModelSpec) -> dict:
     """name -> TensorSpec of everything the model reads from a checkpoint."""

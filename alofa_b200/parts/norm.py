@@ -27,6 +27,9 @@ class RMSNorm(Part):
 
     absorbs_pending = True  # adds split-K partial sums owed to h while reading it
 
+    def scratch_row_bytes(self) -> int:
+        return 4 * self.size
+
     def forward(self, ctx, h, rows=None):
         """Normalised rows of the fp32 stream ``h`` in the compute dtype;
         ``rows`` (int32 on the device) picks rows of ``h``."""
@@ -41,12 +44,6 @@ class RMSNorm(Part):
             return out
         ops.rmsnorm(out, h, self.weight, self.eps, rows)
         return out
-
-
-    def emit(self, prog, ctx, h, rows=None):
-        """The operand "rows of h, normalised" (every row: a program's steps
-        want the logits of all their tokens)."""
-        return prog.normed(h, self.weight, self.eps)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -143,3 +143,46 @@ def test_digest_tells_states_apart():
 
     assert play([0, 1, 0]) == play([0, 1, 0])
     assert play([0, 1, 0]) != play([1, 0, 0])
+
+
+def plan(cm, entries, words=4096):
+    """plan_step over [(slot, tokens)], every row wanted; returns the metadata words."""
+    slots = np.array([s for s, _ in entries], dtype=np.int32)
+    counts = np.array([n for _, n in entries], dtype=np.int32)
+    want_counts = np.ones(len(entries), dtype=np.int32)
+    wants = np.zeros(len(entries), dtype=np.int32)
+    meta = np.full(words, -7, dtype=np.int32)
+    n_tok, n_seq = int(counts.sum()), len(entries)
+    at, offsets = 0, []
+    for size in [n_tok, n_tok, n_seq + 1, n_seq, n_seq, n_seq] + [n_tok, n_seq * cm.max_blocks] * len(cm.groups):
+        offsets.append(at)
+        at += size
+    cm.plan_step(slots, counts, want_counts, wants, meta.ctypes.data, np.array(offsets, dtype=np.int32), cm.max_blocks)
+    return meta
+
+
+def test_a_step_that_does_not_fit_changes_nothing():
+    """Two entries, the second of which does not fit: the first keeps no
+    reservation, the metadata is untouched, and a smaller step goes through."""
+    cm = CacheManager([GroupSpec(16, 4)], max_requests=2, max_tokens=128)
+    a, b = cm.admit(1), cm.admit(2)
+    with pytest.raises(AlofaError, match="too few free pages"):
+        meta = plan(cm, [(a, 40), (b, 40)])  # 3 + 3 pages of 4
+    assert cm.free_pages() == [4] and cm.reserved_len(a) == 0 and cm.reserved_len(b) == 0
+    check_books(cm, [a, b])
+    meta = plan(cm, [(a, 20), (b, 30)])  # 2 + 2 pages
+    assert list(meta[:50]) == list(range(20)) + list(range(30))  # positions
+    cm.commit_step(np.array([a, b], dtype=np.int32), np.array([20, 30], dtype=np.int32))
+    check_books(cm, [a, b])
+    # a step that was planned and never committed is taken back by the next plan
+    plan(cm, [(a, 10)])
+    assert cm.reserved_len(a) == 30 and cm.free_pages() == [0]
+    meta = plan(cm, [(a, 4), (b, 2)])
+    assert cm.reserved_len(a) == 24 and cm.reserved_len(b) == 32
+    check_books(cm, [a, b])
+    # a slot named twice, or a wanted place outside the entry's tokens, is refused before anything is reserved
+    for bad in ([(a, 1), (a, 1)],):
+        with pytest.raises(AlofaError):
+            plan(cm, bad)
+    assert cm.reserved_len(a) == 24
+    check_books(cm, [a, b])

@@ -104,6 +104,6 @@ def test_spec_is_data(tmp_path):
 
 def test_engine_config_checks():
     EngineConfig().validate()
-    for bad in ({"dtype": "float16"}, {"block_size": 24}, {"max_batch": 0}, {"watermark_permille": 1001}, {"token_budget": -1}):
+    for bad in ({"dtype": "float16"}, {"block_size": 24}, {"max_batch": 0}, {"watermark_permille": 1001}, {"token_budget": -1}, {"token_budget": 0}):
         with pytest.raises(AlofaError):
             EngineConfig(**bad).validate()

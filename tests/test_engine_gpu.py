@@ -57,6 +57,22 @@ def test_float32_checkpoint_in_bfloat16_mode(tmp_path):
     near_plain_maximum(prompt, eng.generate([prompt], max_new_tokens=5)[0], wts, cfg)
 
 
+@pytest.mark.parametrize("overlap", [True, False])
+def test_a_raised_status_word_stops_generation(model_folders, overlap):
+    """The kernels report a wait that ran out, or a token id outside the
+    vocabulary, in a status word and skip their work; the engine reads the word
+    with every step's tokens and raises instead of handing out those tokens."""
+    from alofa_b200.errors import AlofaError
+
+    eng = engine(model_folders["A"], "bfloat16", overlap_steps=overlap)
+    prompt = tiny.tokens("A", 9)
+    assert len(eng.generate([prompt], max_new_tokens=3)[0]) == 3
+    eng.runner._status.fill_(2)  # what a kernel whose wait ran out leaves behind
+    with pytest.raises(AlofaError, match="gave up waiting"):
+        eng.generate([prompt], max_new_tokens=3)
+    assert int(eng.runner._status.item()) == 0  # cleared: the engine can be used again
+
+
 def test_pages_run_out_preempted_requests_are_recomputed(model_folders):
     wts, cfg = plain.load(model_folders["B"])
     prompts = [tiny.tokens("B", n, seed=i) for i, n in enumerate([30, 31, 29])]

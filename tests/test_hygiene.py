@@ -26,6 +26,20 @@ def test_package_imports_no_library_model_code_or_compiler():
         assert "scaled_dot_product_attention" not in text, path
 
 
+def test_package_shares_no_code_with_the_tests():
+    """The plain implementation and the other test helpers are the oracle: the
+    package, the bench, the entry points and the programs under bin/ import
+    nothing from tests/ (the smoke test alone reads the plain implementation,
+    to compare with it)."""
+    helpers = sorted(p.stem for p in (ROOT / "tests").glob("*.py") if not p.stem.startswith("test_"))
+    assert "plain_qwen2" in helpers
+    pattern = re.compile(r"^\s*(?:from|import)\s+(tests|" + "|".join(helpers) + r")\b", re.M)
+    for path in python_sources(PACKAGE) + [ROOT / "bench.py", ROOT / "bin" / "trace_run", ROOT / "bin" / "generate"]:
+        found = pattern.findall(path.read_text())
+        assert not found, f"{path.relative_to(ROOT)} imports {found} from the tests"
+        assert "plain_qwen2" not in path.read_text(), path
+
+
 def test_model_math_of_the_package_goes_through_its_own_kernels():
     """Parts call the package's kernels; torch is there for memory, streams and
     graphs.  No part multiplies matrices or takes a softmax with torch."""
@@ -51,11 +65,11 @@ def test_nothing_committed_reads_working_files():
 
 
 def test_kernel_waits_are_bounded():
-    """Every spin on an mbarrier goes through the bounded wait of tma.cuh (or the
-    program kernel's own bounded loops): no bare try_wait loop elsewhere."""
+    """Every spin on an mbarrier goes through the bounded wait of tma.cuh: no
+    bare try_wait loop elsewhere."""
     kernels = PACKAGE / "csrc" / "kernels"
     for path in list(kernels.glob("*.cu")) + list(kernels.glob("*.cuh")):
-        if path.name in ("tma.cuh", "decode_program.cu"):
+        if path.name == "tma.cuh":
             continue
         text = path.read_text()
         assert "mbarrier.try_wait" not in text and "mbarrier.test_wait" not in text, path.name

@@ -1,11 +1,10 @@
 """The ways a step can be issued, against the plain implementation and against
 each other: kernel by kernel, as CUDA graphs (decode steps; prompt steps of a
-repeated shape), overlapped with the step before, and the decode step as one
-resident kernel (a program of phases).  The program against the launches:
-two small configurations that the program kernel takes (head sizes 64 and 128,
-widths that are multiples of 32, a vocabulary that is no multiple of 8, a
-window), one to five requests of different lengths per step, pages used in a
-scattered order, and contexts that span several 256-key splits."""
+repeated shape), and overlapped with the step before.  Two small configurations
+that the tensor-core kernels take (head sizes 64 and 128, widths that are
+multiples of 32, a vocabulary that is no multiple of 8, a window), one to five
+requests of different lengths per step, pages used in a scattered order, and
+contexts that span several 256-key splits."""
 import numpy as np
 import pytest
 import torch
@@ -31,22 +30,20 @@ def folders(tmp_path_factory):
     from alofa_b200.models.qwen2 import NAME
     from alofa_b200.weights.random_init import write_random_model
 
-    base = tmp_path_factory.mktemp("program_models")
+    base = tmp_path_factory.mktemp("step_path_models")
     return {name: write_random_model(base / name, NAME, cfg, seed, torch.bfloat16) for name, (cfg, seed) in configs().items()}
 
 
-def runner_for(folder, programs: bool, pages: int):
+def runner_for(folder, graphs: bool, pages: int, dtype="bfloat16", max_requests=5, max_tokens=1024):
     from alofa_b200.engine.loading import load_model
     from alofa_b200.engine.step import StepRunner
 
-    model, _, _ = load_model(folder, "bfloat16")
-    runner = StepRunner(model, block_size=64, num_pages=pages, max_requests=5, max_tokens=1024, max_step_tokens=768)
-    runner.decode_programs = programs
-    return runner
+    model, _, _ = load_model(folder, dtype)
+    return StepRunner(model, block_size=64, num_pages=pages, max_requests=max_requests, max_tokens=max_tokens, max_step_tokens=768, cuda_graphs=graphs)
 
 
 @pytest.mark.parametrize("name", ["P", "Q"])
-def test_decode_program_against_plain_and_kernels(folders, name):
+def test_decode_graphs_against_plain_and_launches(folders, name):
     from alofa_b200.engine.step import StepEntry
 
     wts, cfg = plain.load(folders[name])
@@ -57,8 +54,8 @@ def test_decode_program_against_plain_and_kernels(folders, name):
     seqs = [[int(t) for t in rng.integers(0, vocab, n + n_new)] for n in lens]
     want = [plain.forward(s, wts, cfg) for s in seqs]
     results = {}
-    for programs in (True, False):
-        runner = runner_for(folders[name], programs, pages=40)
+    for graphs in (True, False):
+        runner = runner_for(folders[name], graphs, pages=40)
         slots = [runner.admit(i) for i in range(len(seqs))]
         # prompts in an order that scatters the pages, one of them in two portions
         for i in (3, 0, 4):
@@ -67,36 +64,21 @@ def test_decode_program_against_plain_and_kernels(folders, name):
         runner.forward([StepEntry(slots[2], seqs[2][: lens[2]], []), StepEntry(slots[1], seqs[1][130 : lens[1]], [])])
         got = [[] for _ in seqs]
         for step in range(n_new):
-            live = range(len(seqs)) if step % 2 == 0 else (1, 3)  # five requests, then two: two batch sizes, two programs
+            live = range(len(seqs)) if step % 2 == 0 else (1, 3)  # five requests, then two: two batch sizes, two graphs
             logits = runner.forward([StepEntry(slots[i], [seqs[i][lens[i] + len(got[i])]], [0]) for i in live]).float().cpu().numpy()
             for row, i in zip(logits, live):
                 got[i].append(row)
         runner.check_status()
-        used = {n for n, g in runner._graphs.items() if g.program is not None}
-        assert used == ({2, 5} if programs else set()), f"batch sizes run as programs: {used}"
-        results[programs] = got
+        used = {key[0] if isinstance(key, tuple) else key for key in runner._graphs}
+        assert used == ({2, 5} if graphs else set()), f"batch sizes replayed as graphs: {used}"
+        results[graphs] = got
     for i, rows in enumerate(results[True]):
         ref = want[i][lens[i] : lens[i] + len(rows)]
         bound = 2e-2 * max(1.0, float(np.abs(ref).max()))
         diff = np.abs(np.stack(rows).astype(np.float64) - ref)
         assert diff.max() <= bound, f"{name} request {i}: decoded token {int(np.argmax(diff.max(axis=1) > bound))} differs from plain by {diff.max():.3e} > {bound:.3e}"
         other = np.abs(np.stack(rows) - np.stack(results[False][i])).max()
-        assert other <= bound, f"{name} request {i}: program and kernels differ by {other:.3e}"
-
-
-def test_program_is_refused_for_shapes_it_does_not_take(model_folders):
-    """A head size of 16 and pages of 16 keys: the step runs kernel by kernel."""
-    from alofa_b200.engine.loading import load_model
-    from alofa_b200.engine.step import StepEntry, StepRunner
-
-    model, _, _ = load_model(model_folders["A"], "bfloat16")
-    runner = StepRunner(model, block_size=16, num_pages=8, max_requests=2, max_tokens=128, max_step_tokens=64)
-    runner.decode_programs = True
-    slot = runner.admit(0)
-    runner.forward([StepEntry(slot, [1, 2, 3], [])])
-    runner.forward([StepEntry(slot, [4], [0])])
-    runner.check_status()
-    assert runner._graphs[1].program is None
+        assert other <= bound, f"{name} request {i}: graph replay and launches differ by {other:.3e}"
 
 
 @pytest.mark.parametrize("name", ["P", "Q"])
@@ -111,7 +93,7 @@ def test_prompt_steps_of_a_repeated_shape_are_replayed_as_graphs(folders, name):
     wts, cfg = plain.load(folders[name])
     vocab = configs()[name][0].vocab_size
     rng = np.random.default_rng(9)
-    runner = runner_for(folders[name], False, pages=60)
+    runner = runner_for(folders[name], True, pages=60)
     assert runner.prompt_graphs
     key = (200, 2, 2)
     # (tokens of the first request, of the second) per step: always 200 tokens, two requests, two wanted rows

@@ -51,11 +51,17 @@ def test_no_alloc_sampling_matches_the_ordinary_entry_point_twice():
         scratch = torch.empty(2 * rows * 32, dtype=torch.float32, device="cuda")
         assert lib.alofa_sample(want.data_ptr(), logits.data_ptr(), temperature.data_ptr(), uniform.data_ptr(), rows, vocab, scratch.data_ptr(), 1, stream) == 0
         got = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
-        before = torch.cuda.memory_allocated()
+        if call == 0:  # the first call on a device may load the library's image and looks the array up
+            assert lib.alofa_sample_noalloc(got.data_ptr(), logits.data_ptr(), temperature.data_ptr(), uniform.data_ptr(), rows, vocab, 1, stream) == 0
+            torch.cuda.synchronize()
+            got.fill_(-1)
+        # free device memory as the driver counts it (not only what the tensor library's own pool
+        # holds): a cudaMalloc inside the entry point would lower it
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.alofa_sample_noalloc(got.data_ptr(), logits.data_ptr(), temperature.data_ptr(), uniform.data_ptr(), rows, vocab, 1, stream)
         torch.cuda.synchronize()
         assert rc == 0
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert got.cpu().tolist() == want.cpu().tolist(), f"call {call}"
         greedy = [int(np.argmax(r)) for r in logits.cpu().numpy()]
         for r in range(rows):
@@ -63,6 +69,24 @@ def test_no_alloc_sampling_matches_the_ordinary_entry_point_twice():
                 assert int(got[r]) == greedy[r]
         if call == 1:
             assert int(got[0]) == 11
+
+
+def test_no_alloc_sampling_refuses_a_draw_without_its_uniform_number():
+    """A row with a positive temperature needs a uniform number: without the
+    array the call is refused (1) and nothing is written; with any_hot = 0 the
+    caller promises that no row draws, and every row gets its largest logit."""
+    lib = library()
+    rows, vocab = 5, 301
+    stream = torch.cuda.current_stream().cuda_stream
+    logits = torch.from_numpy(np.random.default_rng(3).normal(0, 2, size=(rows, vocab)).astype(np.float32)).cuda()
+    temperature = torch.tensor([0.0, 0.9, 0.0, 1.1, 0.5], device="cuda")
+    tokens = torch.full((rows,), -7, dtype=torch.int32, device="cuda")
+    assert lib.alofa_sample_noalloc(tokens.data_ptr(), logits.data_ptr(), temperature.data_ptr(), None, rows, vocab, 1, stream) == 1
+    torch.cuda.synchronize()
+    assert tokens.cpu().tolist() == [-7] * rows
+    assert lib.alofa_sample_noalloc(tokens.data_ptr(), logits.data_ptr(), temperature.data_ptr(), None, rows, vocab, 0, stream) == 0
+    torch.cuda.synchronize()
+    assert tokens.cpu().tolist() == logits.argmax(dim=1).cpu().tolist()
 
 
 def test_no_alloc_sampling_refuses_too_many_rows():
