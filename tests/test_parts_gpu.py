@@ -278,14 +278,15 @@ def test_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
     a = [int(t) for t in rng.integers(0, 97, 30)]
     b = [int(t) for t in rng.integers(0, 97, 22)]
     sa, sb = runner.admit(1), runner.admit(2)
-    got_a = [runner.forward([StepEntry(sa, a[:7], list(range(7)))])]
-    mixed = runner.forward([StepEntry(sa, a[7:9], [0, 1]), StepEntry(sb, b[:20], list(range(20)))])
+    # (a step's logits live in the runner's arena until the next step: copy what is kept)
+    got_a = [runner.forward([StepEntry(sa, a[:7], list(range(7)))]).clone()]
+    mixed = runner.forward([StepEntry(sa, a[7:9], [0, 1]), StepEntry(sb, b[:20], list(range(20)))]).clone()
     got_a.append(mixed[:2])
     got_b = [mixed[2:]]
-    mixed = runner.forward([StepEntry(sb, b[20:21], [0]), StepEntry(sa, a[9:], list(range(21)))])
+    mixed = runner.forward([StepEntry(sb, b[20:21], [0]), StepEntry(sa, a[9:], list(range(21)))]).clone()
     got_b.append(mixed[:1])
     got_a.append(mixed[1:])
-    got_b.append(runner.forward([StepEntry(sb, b[21:], [0])]))
+    got_b.append(runner.forward([StepEntry(sb, b[21:], [0])]).clone())
     assert_close(torch.cat(got_a).cpu(), plain_toy(a), 2e-5, "toy request a")
     assert_close(torch.cat(got_b).cpu(), plain_toy(b), 2e-5, "toy request b")
     # a new request in a used slot starts from zeroed state
