@@ -90,11 +90,10 @@ class CacheManager:
     """Host-side owner of pages, block tables and state slots."""
 
     def __init__(self, groups: list, max_requests: int, max_tokens: int):
-        if not groups:
-            raise AlofaError("invalid_argument", "the cache manager needs at least one group")
+        # no group at all is a model whose layers keep fixed-size state only: slots, no pages
         self.groups = list(groups)
         self.max_requests = max_requests
-        self.max_blocks = max((max_tokens + g.block_size - 1) // g.block_size for g in groups)
+        self.max_blocks = max([(max_tokens + g.block_size - 1) // g.block_size for g in groups] + [1])
         n = len(groups)
         arr = lambda vals: (ctypes.c_int * n)(*vals)
         self._h = _native().cm_create(

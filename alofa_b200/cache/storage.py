@@ -37,10 +37,11 @@ class StateCache:
 
 
 def group_windows(plan: dict) -> list:
-    """The distinct windows of a cache plan, all-keys (None) first."""
+    """The distinct windows of a cache plan, all-keys (None) first; empty when
+    no layer wants pages (the model then has state slots only, and neither the
+    cache manager nor the scheduler books a page for it)."""
     windows = {spec.window for spec in plan.values() if isinstance(spec, PagedKV)}
-    ordered = ([None] if None in windows else []) + sorted(w for w in windows if w is not None)
-    return ordered or [None]
+    return ([None] if None in windows else []) + sorted(w for w in windows if w is not None)
 
 
 class CacheStorage:

@@ -1,6 +1,7 @@
 """``generate``: token ids in, token ids out, with timing.
 
     python -m alofa_b200.cli.generate --model DIR --prompt-ids 1,2,3 --max-new-tokens 16
+    python -m alofa_b200.cli.generate --random-config config.json --weights-seed 0 --prompt-len 100
 
 The reference's ``generate`` (src/alofa/cli.mojo:361-560, 1054-1119) has no
 flags (a compiled Mojo binary sees no argv; its settings are constants,
@@ -11,7 +12,14 @@ meanings as flags, with the environment variables as defaults: ALOFA_WEIGHTS
 ALOFA_MAX_PROMPT_TOKENS, ALOFA_SEED.  It prints what the reference prints:
 prompt ids, generated ids, ticks, preemptions, prefill time, decode time per
 token (mean and median) and tokens per second (cli.mojo:319-358, 530-535).
-Text goes through no tokenizer: prompts are token ids."""
+Text goes through no tokenizer: prompts are token ids.
+
+``--random-config FILE`` runs a model of seeded random weights made in memory
+from a config.json (no folder is written; ``--weights-seed`` names the seed),
+and ``--dump-logits FILE`` writes the logits every generated token was sampled
+from: little-endian float32 rows ``[tokens, vocab]`` in the order the tokens
+were produced, as ``bin/trace_run`` writes them, with ``FILE.tsv`` naming each
+row's request (its index among the prompts) and which of its tokens it is."""
 from __future__ import annotations
 
 import argparse
@@ -42,6 +50,9 @@ def _env_int(name: str, default: int, lo: int, hi: int) -> int:
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="generate", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--model", default=os.environ.get("ALOFA_WEIGHTS"), help="folder with config.json and model.safetensors [ALOFA_WEIGHTS]")
+    ap.add_argument("--random-config", metavar="FILE", help="instead of --model: a config.json; the weights are seeded random numbers, made in memory")
+    ap.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights of --random-config")
+    ap.add_argument("--dump-logits", metavar="FILE", help="write the logits each generated token was sampled from (float32 rows), and FILE.tsv")
     ap.add_argument("--prompt-ids", action="append", help="comma-separated token ids; repeat for several requests")
     ap.add_argument("--prompt-len", type=int, help="instead of --prompt-ids: this many uniform random token ids")
     ap.add_argument("--num-prompts", type=int, default=1, help="how many random prompts with --prompt-len")
@@ -58,7 +69,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--min-tokens-to-keep", type=int, default=1)
     ap.add_argument("--logit-bias", action="append", default=[], metavar="ID:VALUE[,ID:VALUE...]",
                     help="added to the logit of token ID before anything else; repeatable")
-    ap.add_argument("--seed", type=int, default=_env_int("ALOFA_SEED", SEED, 0, 2_147_483_647), help="sampling seed [ALOFA_SEED]")
+    ap.add_argument("--seed", "--sample-seed", dest="seed", type=int, default=_env_int("ALOFA_SEED", SEED, 0, 2_147_483_647), help="sampling seed [ALOFA_SEED]")
     ap.add_argument("--eos-token-id", type=int, default=None)
     # engine: the reference's SchedConfig (src/alofa/engine/scheduler.mojo:139-192)
     ap.add_argument("--max-tokens", type=int, default=_env_int("ALOFA_MAX_TOKENS", 4096, 1, 1 << 20), help="context window per request [ALOFA_MAX_TOKENS]")
@@ -98,16 +109,36 @@ def parse_logit_bias(items) -> dict:
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
-    if not args.model:
-        raise SystemExit("generate: --model (or ALOFA_WEIGHTS) is required")
+    if args.random_config and args.model and not os.environ.get("ALOFA_WEIGHTS") == args.model:
+        raise SystemExit("generate: give --model or --random-config, not both")
+    if not args.model and not args.random_config:
+        raise SystemExit("generate: --model (or ALOFA_WEIGHTS) or --random-config is required")
     from alofa_b200.engine.engine import Engine
     from alofa_b200.sampling.params import SamplingParams
 
-    engine = Engine(
-        args.model, dtype=args.dtype, max_tokens=args.max_tokens, token_budget=args.token_budget, max_chunk=args.max_chunk,
+    settings = dict(
+        dtype=args.dtype, max_tokens=args.max_tokens, token_budget=args.token_budget, max_chunk=args.max_chunk,
         block_size=args.block_size, capacity_blocks=args.capacity_blocks, watermark_permille=args.watermark_permille,
         max_wait_ticks=args.max_wait_ticks, max_batch=args.max_batch, admission=args.admission, trace_out=args.trace_out,
     )
+    if args.random_config:
+        from alofa_b200.config.registry import read_model_config_file
+
+        arch, cfg = read_model_config_file(args.random_config)
+        engine = Engine.from_random(arch.name, cfg, args.weights_seed, **settings)
+    else:
+        engine = Engine(args.model, **settings)
+    dump = None
+    if args.dump_logits:
+        dump = {"file": open(args.dump_logits, "wb"), "rows": [], "count": {}}
+
+        def sink(request_ids, rows):
+            dump["file"].write(rows.astype("<f4").tobytes())
+            for rid in request_ids:
+                dump["rows"].append((rid, dump["count"].get(rid, 0)))
+                dump["count"][rid] = dump["count"].get(rid, 0) + 1
+
+        engine.logits_sink = sink
     vocab = engine.model.spec.vocab_size
     if args.prompt_ids:
         prompts = [[int(t) for t in p.split(",") if t.strip()] for p in args.prompt_ids]
@@ -130,6 +161,12 @@ def main(argv=None) -> int:
     outputs = engine.generate(prompts, sampling=sampling)
     wall = time.perf_counter() - t0
     engine.close()
+    if dump is not None:
+        dump["file"].close()
+        first = min((rid for rid, _ in dump["rows"]), default=0)  # request ids are handed out in prompt order
+        with open(args.dump_logits + ".tsv", "w") as fh:
+            for rid, k in dump["rows"]:
+                fh.write(f"{rid - first}\t{k}\n")
     stats = engine.stats()
     prefill_ms = sum(engine.timings["prefill_ms"])
     decode = engine.timings["decode_ms"]

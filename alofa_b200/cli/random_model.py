@@ -22,23 +22,13 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     import torch
 
-    from alofa_b200.config.registry import read_model_config
+    from alofa_b200.config.registry import read_model_config_file
     from alofa_b200.weights.random_init import write_random_model
 
-    arch, cfg = read_model_config(Path(args.config).parent if Path(args.config).name == "config.json" else _as_folder(args.config))
+    arch, cfg = read_model_config_file(args.config)
     folder = write_random_model(args.out, arch.name, cfg, args.seed, torch.bfloat16 if args.dtype == "bfloat16" else torch.float32)
     print(folder)
     return 0
-
-
-def _as_folder(path: str) -> Path:
-    """A config file under another name is read through a temporary folder view."""
-    import shutil
-    import tempfile
-
-    tmp = Path(tempfile.mkdtemp())
-    shutil.copy(path, tmp / "config.json")
-    return tmp
 
 
 if __name__ == "__main__":

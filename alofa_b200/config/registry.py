@@ -48,9 +48,28 @@ def get_architecture(name: str) -> Architecture:
     return _ARCHITECTURES[name]
 
 
+_plugins_loaded = False
+
+
 def _ensure_builtin() -> None:
-    # importing the models package registers the built-in architectures
+    """Importing the models package registers the built-in architectures.
+    ``ALOFA_PLUGINS`` (comma-separated module names, importable from the
+    Python path) names modules of the user's own that register further parts
+    and architectures when imported: the command-line programs, which build
+    nothing but what config.json names, find them this way."""
+    global _plugins_loaded
     from .. import models  # noqa: F401
+
+    if not _plugins_loaded:
+        _plugins_loaded = True
+        import importlib
+        import os
+
+        for name in filter(None, (m.strip() for m in os.environ.get("ALOFA_PLUGINS", "").split(","))):
+            try:
+                importlib.import_module(name)
+            except ImportError as err:
+                raise AlofaError("invalid_argument", "a module named in ALOFA_PLUGINS cannot be imported", f"module={name}: {err}") from err
 
 
 def architecture_name_of(obj: dict, origin: str) -> str:
@@ -62,7 +81,12 @@ def architecture_name_of(obj: dict, origin: str) -> str:
 
 def read_model_config(folder):
     """(architecture, typed config) of a model folder, chosen by config.json."""
-    path = Path(folder) / "config.json"
+    return read_model_config_file(Path(folder) / "config.json")
+
+
+def read_model_config_file(path):
+    """(architecture, typed config) of a config.json under any file name."""
+    path = Path(path)
     obj = read_json_object(path)
     arch = get_architecture(architecture_name_of(obj, str(path)))
     return arch, arch.read_config(obj, str(path))

@@ -86,7 +86,7 @@ extern "C" {
 
 void* cm_create(int n_groups, const int* page_size, const int* num_pages, const int* window,
                 int max_requests, int max_blocks_per_request) {
-  if (n_groups <= 0 || max_requests <= 0 || max_blocks_per_request <= 0) return nullptr;
+  if (n_groups < 0 || max_requests <= 0 || max_blocks_per_request <= 0) return nullptr;  // no group: state slots only
   auto* m = new Manager();
   m->groups.resize(n_groups);
   for (int i = 0; i < n_groups; ++i) {

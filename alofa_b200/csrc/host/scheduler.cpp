@@ -192,7 +192,9 @@ extern "C" {
 
 // cfg: token_budget, max_chunk, max_batch, max_tokens, watermark_permille,
 //      max_wait_ticks, admission, n_groups, then per group page_size, window,
-//      capacity.
+//      capacity.  n_groups may be 0 (a model whose layers keep fixed-size state
+//      only): no page is ever booked, nothing is ever preempted, and admission is
+//      bounded by the request slots alone.
 void* sched_create(const int* cfg, int n) {
   if (n < 8) return nullptr;
   auto* s = new Sched();
@@ -206,7 +208,7 @@ void* sched_create(const int* cfg, int n) {
   int G = cfg[7];
   bool ok = s->token_budget >= 0 && s->max_chunk > 0 && s->max_batch > 0 && s->max_tokens > 0 &&
             s->watermark_permille >= 0 && s->watermark_permille <= 1000 && s->max_wait_ticks >= 0 &&
-            (s->admission == ADMIT_COMMITTED || s->admission == ADMIT_OPTIMISTIC) && G > 0 && n == 8 + 3 * G;
+            (s->admission == ADMIT_COMMITTED || s->admission == ADMIT_OPTIMISTIC) && G >= 0 && n == 8 + 3 * G;
   for (int g = 0; ok && g < G; ++g) {
     s->page_size.push_back(cfg[8 + 3 * g]);
     s->window.push_back(cfg[9 + 3 * g]);

@@ -112,6 +112,9 @@ class Engine:
         self._pinned_status = [pin(torch.zeros(1, dtype=torch.int32)) for _ in range(2)]
         self._pin_flip = 0
         self.overlap = bool(cfg.overlap_steps) and self.runner.feeds_tokens
+        # set to a callable (request ids, logits [rows, vocab] as a float32 numpy array) to see the
+        # logits every token is sampled from; steps then run one after the other
+        self.logits_sink = None
         self.marks = []  # (time a step's tokens reached the host, kind, rows)
         self.counters = {"ticks": 0, "rows_run": 0, "prefill_rows": 0, "decode_rows": 0, "preempt_total": 0, "steps_prefill": 0, "steps_decode": 0}
         self.timings = {"prefill_ms": [], "decode_ms": []}
@@ -200,7 +203,7 @@ class Engine:
                 req.slot = self.runner.admit(rid)
             plan.append((req, (start, end), end == len(req.prompt)))
         owners = [req for req, _, samples in plan if samples]
-        overlap = self.overlap and bool(plan) and all(req.params.plain() for req in owners)
+        overlap = self.overlap and self.logits_sink is None and bool(plan) and all(req.params.plain() for req in owners)
         if not overlap:
             self._settle()  # every token is on the host before this step is put together
         fl = self._inflight
@@ -290,6 +293,8 @@ class Engine:
                 tokens = sample_rows(ctx, logits, owners)
             self.runner.copy_status(status)
             picked = tokens.cpu().tolist()  # waits for the stream: the status word is on the host too
+            if self.logits_sink is not None:
+                self.logits_sink([req.id for req in owners], logits[: len(owners)].float().cpu().numpy())
             self.runner.raise_status(int(status[0]))
         # (a portion of a prompt nobody samples from is not waited for: the word stays raised
         # until it is read, so the step that yields the request's first token reports it)

@@ -186,3 +186,17 @@ def test_a_step_that_does_not_fit_changes_nothing():
             plan(cm, bad)
     assert cm.reserved_len(a) == 24
     check_books(cm, [a, b])
+
+
+def test_a_manager_without_groups_hands_out_state_slots_only():
+    cm = CacheManager([], max_requests=2, max_tokens=64)
+    a, b = cm.admit(1), cm.admit(2)
+    assert (a, b) == (0, 1) and cm.free_pages() == []
+    with pytest.raises(AlofaError):
+        cm.admit(3)
+    meta = plan(cm, [(a, 5), (b, 7)])
+    assert list(meta[:12]) == list(range(5)) + list(range(7))
+    cm.commit_step(np.array([a, b], dtype=np.int32), np.array([5, 7], dtype=np.int32))
+    assert cm.computed_len(a) == 5 and cm.computed_len(b) == 7 and cm.defects() == 0
+    cm.release(a)
+    assert cm.admit(4) == a and cm.computed_len(a) == 0

@@ -48,3 +48,8 @@ def test_several_prompts_and_scheduler_options():
     assert args.prompt_ids == ["1,2,3", "4,5"]
     assert (args.token_budget, args.max_chunk, args.block_size, args.max_batch, args.watermark_permille, args.max_wait_ticks, args.admission) == (
         32, 16, 16, 4, 900, 8, "optimistic")
+
+
+def test_random_config_and_dump_logits_flags():
+    args = build_parser().parse_args(["--random-config", "cfg.json", "--weights-seed", "4", "--prompt-len", "5", "--dump-logits", "out.f32", "--sample-seed", "11"])
+    assert (args.random_config, args.weights_seed, args.dump_logits, args.seed, args.model) == ("cfg.json", 4, "out.f32", 11, None)

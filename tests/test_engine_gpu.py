@@ -201,6 +201,35 @@ def test_generate_command_line(model_folders):
     assert report["out_ids"] == [plain.greedy(prompt, 5, wts, cfg)] and report["ticks"] >= 5 and report["preemptions"] == 0
 
 
+def test_generate_from_a_random_config_dumps_the_logits_it_sampled_from(model_folders, tmp_path):
+    """--random-config makes the weights in memory from a config.json and a
+    seed (the same numbers the folder writer draws); --dump-logits writes the
+    rows every token was picked from, which must be the plain logits."""
+    name = "B"
+    seed = tiny.CONFIGS[name][1]
+    prompts = [tiny.tokens(name, 9), tiny.tokens(name, 21, seed=1)]
+    wts, cfg = plain.load(model_folders[name])
+    dump = tmp_path / "logits.f32"
+    cmd = [sys.executable, str(ROOT / "bin" / "generate"), "--random-config", str(model_folders[name] / "config.json"), "--weights-seed", str(seed),
+           "--dtype", "float32", "--max-new-tokens", "4", "--block-size", "16", "--max-tokens", "128", "--token-budget", "32", "--max-chunk", "16",
+           "--dump-logits", str(dump), "--json"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(map(str, p))]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    report = json.loads(out.stdout.strip().splitlines()[-1])
+    assert report["out_ids"] == [plain.greedy(p, 4, wts, cfg) for p in prompts]
+    vocab = tiny.CONFIGS[name][0].vocab_size
+    rows = np.fromfile(dump, dtype="<f4").reshape(-1, vocab)
+    index = [tuple(int(x) for x in line.split("\t")) for line in Path(str(dump) + ".tsv").read_text().splitlines()]
+    assert len(rows) == len(index) == 8 and sorted(index) == [(r, k) for r in range(2) for k in range(4)]
+    for row, (r, k) in zip(rows, index):
+        seq = prompts[r] + report["out_ids"][r][:k]
+        ref = plain.forward(seq, wts, cfg)[-1]
+        assert np.abs(row - ref).max() <= 1e-5 * max(1.0, float(np.abs(ref).max()))
+        assert int(np.argmax(row)) == report["out_ids"][r][k]
+
+
 def test_no_cpu_path():
     from alofa_b200.csrc import ops
     from alofa_b200.errors import AlofaError

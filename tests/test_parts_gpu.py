@@ -174,80 +174,13 @@ def test_run_list_names_a_layer_twice_and_a_layer_reads_anothers_cache():
 
 
 def register_toy_parts():
-    """Toy parts, defined here only: a mixer that keeps a running mean of its
-    inputs per request (state of fixed size, no pages), a feed-forward that
-    routes every token to one of several small experts, and a position
-    encoding that is not rotary."""
-    from alofa_b200.parts.base import Part, SlotState, TensorSpec, register_part
+    """Toy parts, defined in the tests only (tests/toy_architecture.py): a mixer
+    that keeps a running mean of its inputs per request (state of fixed size,
+    no pages), a feed-forward that routes every token to one of several small
+    experts, and a position encoding that is not rotary."""
+    import toy_architecture
 
-    class RunningMeanMixer(Part):
-        family = "mixer"
-
-        def __init__(self, spec, rt):
-            super().__init__(spec, rt)
-            self.hidden = int(self.param("hidden_size"))
-
-        def tensors(self):
-            return {self.prefix + "mix.weight": TensorSpec((self.hidden, self.hidden))}
-
-        def load(self, state):
-            self.w = state[self.prefix + "mix.weight"].float()
-
-        def cache_spec(self):
-            return SlotState((self.hidden + 1,), torch.float32)  # sum of inputs and their count
-
-        def forward(self, ctx, x, h, cache, writes=True):
-            starts = ctx.host_field("q_start")
-            slots = ctx.host_field("state_slots")
-            xf = x.float()
-            for s in range(ctx.n_seqs):
-                lo, hi = int(starts[s]), int(starts[s + 1])
-                st = cache.state[int(slots[s])]
-                sums = st[: self.hidden] + torch.cumsum(xf[lo:hi], dim=0)
-                counts = st[self.hidden] + torch.arange(1, hi - lo + 1, device=x.device, dtype=torch.float32)
-                h[lo:hi] += (sums / counts[:, None]) @ self.w.T
-                st[: self.hidden] = sums[-1]
-                st[self.hidden] = counts[-1]
-
-    class RoutedToyMLP(Part):
-        family = "feed_forward"
-
-        def __init__(self, spec, rt):
-            super().__init__(spec, rt)
-            self.hidden, self.experts = int(self.param("hidden_size")), int(self.param("experts"))
-
-        def tensors(self):
-            t = {self.prefix + "router.weight": TensorSpec((self.experts, self.hidden))}
-            for e in range(self.experts):
-                t[self.prefix + f"experts.{e}.weight"] = TensorSpec((self.hidden, self.hidden))
-            return t
-
-        def load(self, state):
-            self.router = state[self.prefix + "router.weight"].float()
-            self.w = [state[self.prefix + f"experts.{e}.weight"].float() for e in range(self.experts)]
-
-        def forward(self, ctx, x, h):
-            xf = x.float()
-            choice = (xf @ self.router.T).argmax(dim=1)
-            for e in range(self.experts):
-                rows = (choice == e).nonzero().flatten()
-                if rows.numel():
-                    h[rows] += xf[rows] @ self.w[e].T
-
-    class AddedPosition(Part):
-        family = "position"
-
-        def rotary_table(self):
-            return None, 0
-
-        def apply(self, ctx, q, k):
-            shift = (ctx.positions.float() * 0.01)[:, None, None]
-            q += shift.to(q.dtype)
-            if k.shape[1]:
-                k += shift.to(k.dtype)
-
-    for family, kind, cls in (("mixer", "toy_running_mean", RunningMeanMixer), ("feed_forward", "toy_routed", RoutedToyMLP), ("position", "toy_added", AddedPosition)):
-        register_part(family, kind, cls, replace=True)
+    toy_architecture.register_parts()
 
 
 def test_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():

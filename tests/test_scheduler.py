@@ -180,3 +180,27 @@ def test_random_load_keeps_the_invariants(seed):
     assert done == list(range(1, rid + 1)), "every request finishes"
     assert sched.counts()["live"] == 0
     assert replay_trace(trace) == []
+
+
+def test_no_cache_group_means_admission_by_slots_alone():
+    """A model whose layers keep fixed-size state only has no page group: no
+    page is booked, nothing is preempted, and requests are admitted while a
+    slot is free, under either admission rule."""
+    for admission in ("committed", "optimistic"):
+        cfg = SchedConfig(token_budget=64, max_chunk=32, max_batch=2, max_tokens=4096, admission=admission, groups=[])
+        s = Scheduler(cfg)
+        s.can_ever_fit(4000, 96)
+        act = s.step(SchedInput([(1, 40, 3), (2, 3000, 2), (3, 5, 1)], [], [], []))
+        assert act.arrival_status == [1, 1, 0]  # two slots
+        assert [p[0] for p in act.prefill] == [1, 2] and act.preempted == []
+        seen = set()
+        for _ in range(200):
+            act = s.step(SchedInput([(3, 5, 1)] if 3 not in seen else [], [], [], []))
+            if act.arrival_status == [1]:
+                seen.add(3)
+            assert act.preempted == []
+            if not s.counts()["live"] and 3 in seen:
+                break
+        assert 3 in seen and s.counts()["live"] == 0
+        text = format_config(cfg)
+        assert text.endswith("G=-") and parse_config(text).groups == []

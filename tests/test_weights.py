@@ -113,3 +113,73 @@ def test_random_mode_is_seeded(tmp_path):
     assert "lm_head.weight" not in st.names()  # tied
     st.close()
     assert json.loads((a / "config.json").read_text())["architectures"] == [NAME]
+
+
+def shard_folder(tmp_path, state, pieces=3, name="m"):
+    """Write ``state`` as ``pieces`` shard files plus the index."""
+    folder = tmp_path / name
+    folder.mkdir()
+    names = list(state)
+    weight_map = {}
+    for i in range(pieces):
+        part = {n: state[n] for n in names[i::pieces]}
+        shard = f"model-{i + 1:05d}-of-{pieces:05d}.safetensors"
+        write_safetensors(folder / shard, part)
+        weight_map.update({n: shard for n in part})
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"metadata": {"total_size": 0}, "weight_map": weight_map}))
+    return folder, weight_map
+
+
+def test_sharded_checkpoint_loads_like_the_single_file(tmp_path):
+    cfg, seed = tiny.CONFIGS["B"]
+    expected = expected_tensors(build_spec(cfg))
+    state = random_state(expected, seed)
+    folder, _ = shard_folder(tmp_path, state)
+    got = load_state(expected, folder, torch.bfloat16, "cpu")
+    assert set(got) == set(state) and all(torch.equal(got[n], state[n]) for n in state)
+
+
+def test_sharded_checkpoint_one_error_across_shards(tmp_path):
+    cfg, seed = tiny.CONFIGS["B"]
+    expected = expected_tensors(build_spec(cfg))
+    state = random_state(expected, seed)
+    del state["model.norm.weight"]
+    state["model.layers.0.self_attn.k_proj.bias"] = torch.zeros(7)
+    state["stray.weight"] = torch.zeros(2)
+    folder, weight_map = shard_folder(tmp_path, state)
+    # one tensor twice: a copy of it in another shard than the index says; and one the index misplaces
+    twice = "model.layers.1.mlp.up_proj.weight"
+    other = next(s for s in sorted(set(weight_map.values())) if s != weight_map[twice])
+    st = SafeTensorFile(folder / other)
+    part = {n: st.tensor(n).clone() for n in st.names()}
+    st.close()
+    part[twice] = state[twice]
+    write_safetensors(folder / other, part)
+    moved = "model.layers.2.input_layernorm.weight"
+    weight_map[moved] = next(s for s in sorted(set(weight_map.values())) if s != weight_map[moved])
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": weight_map}))
+    with pytest.raises(AlofaError) as err:
+        load_state(expected, folder, torch.bfloat16, "cpu")
+    text = str(err.value)
+    assert "missing tensors" in text and "model.norm.weight" in text and moved in text
+    assert "unexpected tensors (1)" in text and "stray.weight" in text
+    assert "wrong shapes (1)" in text and "k_proj.bias got=(7,)" in text
+    assert f"{twice} is held by 2 shards" in text and f"{moved} is not in" in text
+
+
+def test_shard_index_refusals(tmp_path):
+    cfg, seed = tiny.CONFIGS["A"]
+    expected = expected_tensors(build_spec(cfg))
+    state = random_state(expected, seed)
+    folder, weight_map = shard_folder(tmp_path, state, pieces=2)
+    (folder / sorted(set(weight_map.values()))[1]).unlink()
+    with pytest.raises(AlofaError, match="shard named by the index is missing"):
+        load_state(expected, folder, torch.bfloat16, "cpu")
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "../elsewhere.safetensors"}}))
+    with pytest.raises(AlofaError, match="outside the model folder"):
+        load_state(expected, folder, torch.bfloat16, "cpu")
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}}))
+    with pytest.raises(AlofaError, match="no weight_map"):
+        load_state(expected, folder, torch.bfloat16, "cpu")
+    with pytest.raises(AlofaError, match="no model.safetensors"):
+        load_state(expected, tmp_path, torch.bfloat16, "cpu")
