@@ -211,8 +211,9 @@ def head_weight(wts, cfg):
     raise ValueError("no lm_head.weight and embeddings are not tied")
 
 
-def forward(ids, wts, cfg):
-    """Logits [n, V] (float64) at every position of one whole sequence
+def forward(ids, wts, cfg, rows=None):
+    """Logits [n, V] (float64) at every position of one whole sequence, or at
+    the positions ``rows`` only
     (src/alofa/model/arch/qwen.mojo:1362-1525; the reference projects the last
     row only, the same final norm and head are applied to every row here)."""
     n = len(ids)
@@ -221,6 +222,8 @@ def forward(ids, wts, cfg):
     for i in range(cfg["L"]):
         window = cfg["window"] if i >= cfg["first_window_layer"] else None
         h = decoder_layer(h, positions, wts, f"model.layers.{i}.", cfg, window)
+    if rows is not None:
+        h = h[np.asarray(rows, dtype=np.int64)]
     x = rmsnorm(h, wts["model.norm.weight"], cfg["eps"])
     return linear(x, head_weight(wts, cfg))
 

@@ -64,3 +64,44 @@ def test_benchmark_layer_sizes_against_plain(shaped, dtype):
         diff = np.abs(mine - want)
         assert diff.max() <= bound, f"{dtype} request {rid}: position {int(np.argmax(diff.max(axis=1) > bound))} differs by {diff.max():.3e} > {bound:.3e}"
         assert (mine.argmax(axis=1) == want.argmax(axis=1)).mean() > 0.9
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_benchmarked_prompt_step_against_plain(shaped, dtype):
+    """The benchmark's own prompt step at its real widths, two layers deep: one
+    2,048-token prompt in one step, and in portions of 512, logits wanted at
+    the first row, either side of a 128-token tile edge and the last row.
+    This is where the persistent gate/up kernel has more tiles than SMs, the
+    tensor-core attention runs several waves and the down product splits its
+    depth."""
+    from alofa_b200.engine.loading import compute_dtype
+    from alofa_b200.engine.step import StepEntry, StepRunner
+    from alofa_b200.models.qwen2 import build_spec
+    from alofa_b200.parts.base import Runtime
+    from alofa_b200.parts.model import Model
+    from alofa_b200.weights.loader import load_state
+
+    cfg, state, _, _ = shaped
+    wts = {k: v.to(torch.float64).numpy() for k, v in state.items()}
+    pcfg = {"L": 2, "H": 896, "nh": 14, "nkv": 2, "hd": 64, "I": 4864, "V": 151936, "eps": 1e-6, "theta": 1e6, "tied": True, "window": None, "first_window_layer": 2}
+    toks = [int(t) for t in np.random.default_rng(7).integers(0, 151936, 2048)]
+    rows = [0, 127, 128, 2047]
+    want = plain.forward(toks, wts, pcfg, rows=rows)
+    model = Model(build_spec(cfg), Runtime(torch.device("cuda"), compute_dtype(dtype)))
+    model.load(load_state(model.tensors(), state, model.rt.dtype, model.rt.device))
+    runner = StepRunner(model, block_size=64, num_pages=70, max_requests=2, max_tokens=4096, max_step_tokens=2112)
+    bound = TOL[dtype] * max(1.0, float(np.abs(want).max()))
+    whole = runner.admit(1)
+    got = runner.forward([StepEntry(whole, toks, rows)]).cpu().numpy().astype(np.float64)
+    assert np.abs(got - want).max() <= bound, f"{dtype} whole: {np.abs(got - want).max():.3e} > {bound:.3e}"
+    cut = runner.admit(2)
+    parts = []
+    for lo in range(0, 2048, 512):
+        local = [r - lo for r in rows if lo <= r < lo + 512]
+        out = runner.forward([StepEntry(cut, toks[lo : lo + 512], local)])
+        if local:
+            parts.append(out.cpu().numpy().astype(np.float64))
+    got = np.concatenate(parts)
+    runner.check_status()
+    assert np.abs(got - want).max() <= bound, f"{dtype} portions of 512: {np.abs(got - want).max():.3e} > {bound:.3e}"
+    assert (got.argmax(axis=1) == want.argmax(axis=1)).all()
