@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--shape 0.5b|1.5b|7b] [--no-extra]
 
 The default run has the layer sizes of the Qwen2.5-0.5B shape with random
 weights, a batch of 8 requests with 2,048-token prompts inside a 4,096-token
@@ -15,7 +15,19 @@ JSON line is printed:
 * ``prefill``: one 2,048-token prompt in one step;
 * ``roofline``: bytes a decode step has to read (every weight once, the cache
   of the live requests) over its time, against the measured copy bandwidth;
-* ``points``: decode at batch 1 and 64.
+* ``points``: decode at batch 1 and 64, and, unless ``--no-extra``, the other
+  measurements: decode at batch 8 and 64 with prompts that fill the 4,096-token
+  context; the Qwen2.5-1.5B shape serving 64 requests with prompt lengths
+  uniform in [128, 2048] and 256 new tokens each through ``Engine.generate``
+  (scheduler included); the Qwen2.5-7B shape at batch 1, 8 and 64 and its
+  2,048-token prefill.  ``points_detail`` gives each point's time per step
+  (median, min, max over the steps, each step timed by its own event pair), its
+  fraction of the roofline from the same formula, and the scheduler's counts.
+
+Method, after the reference's own benchmark (src/alofa/cli.mojo:62-82,
+819-850): warm-up first, then every repetition timed on its own and the median
+reported with the span; ``value`` itself is the contract's figure, K steps
+between one pair of events.
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from
 the fallback figures 6.65 TB/s and 1.59 PFLOP/s.  Every decode step reads more
@@ -39,10 +51,19 @@ sys.path.insert(0, str(ROOT))
 METRIC = "decode tok/s @ batch 8 (Qwen2.5-0.5B shape, 2,048-token prompts, context 4096)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
-# Qwen2.5-0.5B shape
-SHAPE = dict(num_hidden_layers=24, hidden_size=896, num_attention_heads=14, num_key_value_heads=2, head_dim=64,
-             intermediate_size=4864, vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True,
-             max_position_embeddings=32768)
+# the shapes the measurements are quoted on (their published config.json values)
+SHAPES = {
+    "0.5b": ("Qwen2.5-0.5B shape", dict(num_hidden_layers=24, hidden_size=896, num_attention_heads=14, num_key_value_heads=2, head_dim=64,
+                                        intermediate_size=4864, vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True,
+                                        max_position_embeddings=32768)),
+    "1.5b": ("Qwen2.5-1.5B shape", dict(num_hidden_layers=28, hidden_size=1536, num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+                                        intermediate_size=8960, vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True,
+                                        max_position_embeddings=32768)),
+    "7b": ("Qwen2.5-7B shape", dict(num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                                    intermediate_size=18944, vocab_size=152064, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
+                                    max_position_embeddings=32768)),
+}
+SHAPE = SHAPES["0.5b"][1]
 PROMPT_LEN = 2048
 CONTEXT = 4096
 
@@ -158,68 +179,85 @@ def prefill_flops(cfg, layers: int, tokens: int, numbers: dict) -> float:
     return gemm + attn + head
 
 
-def run(args) -> dict:
-    import numpy as np
-    import torch
+class Bench:
+    """One engine of one shape and the measurements made on it."""
 
-    from alofa_b200.csrc import ops
-    from alofa_b200.engine.engine import Engine
-    from alofa_b200.engine.step import StepEntry
-    from alofa_b200.models.qwen2 import NAME, Qwen2Config
+    def __init__(self, shape: str, layers: int, max_batch: int, context: int = CONTEXT):
+        import numpy as np
 
-    shape = dict(SHAPE)
-    full_layers = shape["num_hidden_layers"]
-    shape["num_hidden_layers"] = args.layers or full_layers
-    cfg = Qwen2Config(**shape)
-    layers = cfg.num_hidden_layers
-    max_batch = max(64, args.batch)
-    engine = Engine.from_random(NAME, cfg, seed=0, dtype="bfloat16", generate_on_device=True, block_size=64, max_batch=max_batch,
-                                max_tokens=CONTEXT, token_budget=PROMPT_LEN + max_batch, max_chunk=PROMPT_LEN)
-    runner = engine.runner
-    numbers = model_numbers(cfg, layers)
-    pk, pk_kind = peaks()
-    rng = np.random.default_rng(0)
-    vocab = cfg.vocab_size
+        from alofa_b200.engine.engine import Engine
+        from alofa_b200.models.qwen2 import NAME, Qwen2Config
 
-    def prompt(n):
-        return [int(t) for t in rng.integers(0, vocab, size=n)]
+        self.label, values = SHAPES[shape]
+        values = dict(values)
+        self.full_layers = values["num_hidden_layers"]
+        values["num_hidden_layers"] = layers or self.full_layers
+        self.cfg = Qwen2Config(**values)
+        self.layers = self.cfg.num_hidden_layers
+        self.engine = Engine.from_random(NAME, self.cfg, seed=0, dtype="bfloat16", generate_on_device=True, block_size=64, max_batch=max_batch,
+                                         max_tokens=context, token_budget=PROMPT_LEN + max_batch, max_chunk=PROMPT_LEN)
+        self.runner = self.engine.runner
+        self.numbers = model_numbers(self.cfg, self.layers)
+        self.peaks, self.peaks_kind = peaks()
+        self.rng = np.random.default_rng(0)
 
-    def timed(fn, reps):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    def prompt(self, n: int) -> list:
+        return [int(t) for t in self.rng.integers(0, self.cfg.vocab_size, size=n)]
+
+    @staticmethod
+    def timed_each(fn, reps: int) -> tuple:
+        """(mean ms over one pair of events around all repetitions, [ms of each
+        repetition by its own pair of events])."""
+        import torch
+
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
         torch.cuda.synchronize()
-        start.record()
-        for _ in range(reps):
+        marks[0].record()
+        for i in range(reps):
             fn()
-        end.record()
+            marks[i + 1].record()
         torch.cuda.synchronize()
-        return start.elapsed_time(end) / reps
+        each = [marks[i].elapsed_time(marks[i + 1]) for i in range(reps)]
+        return marks[0].elapsed_time(marks[reps]) / reps, each
 
-    # -- prefill: one 2,048-token prompt in one step --------------------------
-    def one_prefill():
-        slot = runner.admit(10_000)
-        runner.forward_logits([StepEntry(slot, prefill_tokens, (PROMPT_LEN - 1,))])
-        runner.release(slot)
+    @staticmethod
+    def spread(each: list) -> dict:
+        return {"median": round(statistics.median(each), 4), "min": round(min(each), 4), "max": round(max(each), 4), "n": len(each)}
 
-    prefill_tokens = prompt(PROMPT_LEN)
-    if args.phase == "decode":
-        prefill_ms = float("nan")
-    else:
-        for _ in range(max(1, min(args.warmup, 3))):
-            one_prefill()
-        prefill_ms = timed(one_prefill, 5)
-    if args.phase == "prefill":
-        print(json.dumps({"phase": "prefill", "ms": prefill_ms, "tok_s": PROMPT_LEN / prefill_ms * 1e3}))
-        raise SystemExit(0)
-    pf = prefill_flops(cfg, layers, PROMPT_LEN, numbers)
-    prefill = {"value": round(PROMPT_LEN / prefill_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(prefill_ms, 4),
-               "frac": round(pf / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    def prefill(self, warmup: int, reps: int = 10) -> dict:
+        """One 2,048-token prompt in one step, `reps` times; the median."""
+        from alofa_b200.engine.step import StepEntry
 
-    # -- decode ---------------------------------------------------------------
-    def decode_point(batch, steps, warmup, clocks=None):
+        tokens = self.prompt(PROMPT_LEN)
+
+        def one():
+            slot = self.runner.admit(10_000)
+            self.runner.forward_logits([StepEntry(slot, tokens, (PROMPT_LEN - 1,))])
+            self.runner.release(slot)
+
+        for _ in range(max(3, warmup)):  # a shape met a third time is recorded as a graph: time what serving replays
+            one()
+        _, each = self.timed_each(one, reps)
+        ms = statistics.median(each)
+        flops = prefill_flops(self.cfg, self.layers, PROMPT_LEN, self.numbers)
+        return {"value": round(PROMPT_LEN / ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(ms, 4),
+                "frac": round(flops / (ms * 1e-3) / (self.peaks["bf16_tflops"] * 1e12), 4), "reps": self.spread(each)}
+
+    def decode(self, batch: int, steps: int, warmup: int, prompt_len: int = PROMPT_LEN, clocks=None) -> dict:
+        """`steps` decode steps of `batch` requests whose prompts of `prompt_len`
+        tokens were run first, one request per step."""
+        import torch
+
+        from alofa_b200.csrc import ops
+        from alofa_b200.engine.step import StepEntry
+
+        runner = self.runner
         slots = [runner.admit(20_000 + i) for i in range(batch)]
-        for s in slots:  # 2,048-token prompts, one request per step
-            runner.forward_logits([StepEntry(s, prompt(PROMPT_LEN), ())])
-        feed = rng.integers(0, vocab, size=(steps + warmup, batch))
+        for s in slots:
+            toks = self.prompt(prompt_len)
+            for lo in range(0, prompt_len, PROMPT_LEN):
+                runner.forward_logits([StepEntry(s, toks[lo : lo + PROMPT_LEN], ())])
+        feed = self.rng.integers(0, self.cfg.vocab_size, size=(steps + warmup, batch))
         state = {"i": 0}
 
         def one_step():
@@ -236,28 +274,136 @@ def run(args) -> dict:
             time.sleep(0.3)  # the sampler's first lines
             clocks.mark()
         launches0 = ops.launch_count()
-        ms = timed(one_step, steps)
+        ms, each = self.timed_each(one_step, steps)
         clock_report = clocks.stop() if clocks else None
         launches = ops.launch_count() - launches0
-        mean_kv = PROMPT_LEN + warmup + steps / 2
+        mean_kv = prompt_len + warmup + steps / 2
         for s in slots:
             runner.release(s)
-        step_bytes = numbers["weight_bytes"] + numbers["kv_bytes_per_token"] * mean_kv * batch
-        return {"ms": ms, "tok_s": batch / ms * 1e3, "bytes": step_bytes, "launches": launches, "clocks": clock_report}
+        step_bytes = self.numbers["weight_bytes"] + self.numbers["kv_bytes_per_token"] * mean_kv * batch
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+        return {"ms": ms, "tok_s": batch / ms * 1e3, "bytes": step_bytes, "launches": launches, "clocks": clock_report, "step_ms": self.spread(each),
+                "gbs": achieved, "frac": achieved / self.peaks["hbm_gbs"]}
 
-    main = decode_point(args.batch, args.steps, args.warmup, ClockSampler())
+    def detail(self, point: dict) -> dict:
+        return {"tok_s": round(point["tok_s"], 1), "ms_per_step": round(point["ms"], 4), "step_ms": point["step_ms"],
+                "hbm_gbs": round(point["gbs"], 1), "hbm_frac": round(point["frac"], 4)}
+
+    def serve(self, n_requests: int, new_tokens: int, lo: int, hi: int) -> dict:
+        """`n_requests` with prompt lengths uniform in [lo, hi] and `new_tokens`
+        new tokens each through Engine.generate, scheduler included; run once
+        untimed (records the graphs), then timed by the wall clock."""
+        engine = self.engine
+        prompts = [self.prompt(int(n)) for n in self.rng.integers(lo, hi + 1, size=n_requests)]
+        engine.generate(prompts, max_new_tokens=new_tokens)
+        engine.marks.clear()
+        before = dict(engine.counters)
+        for key in engine.timings:
+            engine.timings[key].clear()
+        t0 = time.perf_counter()
+        outs = engine.generate(prompts, max_new_tokens=new_tokens)
+        wall = time.perf_counter() - t0
+        made = sum(len(o) for o in outs)
+        by_rows = {}
+        for _, kind, rows in engine.marks:
+            bucket = kind + ":" + ("1-16" if rows <= 16 else "17-64" if rows <= 64 else "65-512" if rows <= 512 else "513+")
+            by_rows[bucket] = by_rows.get(bucket, 0) + 1
+        stats = engine.stats()
+        return {"tok_s": round(made / wall, 1), "wall_s": round(wall, 3), "requests": n_requests, "new_tokens": made,
+                "prompt_tokens": sum(len(p) for p in prompts), "ticks": stats["ticks"] - before["ticks"],
+                "preemptions": stats["preempt_total"], "steps_by_rows": by_rows,
+                "decode_step_ms_median": round(statistics.median(engine.timings["decode_ms"]), 4) if engine.timings["decode_ms"] else None}
+
+    def close(self) -> None:
+        import gc
+
+        import torch
+
+        self.engine.close()
+        self.engine = self.runner = None
+        gc.collect()
+        torch.cuda.empty_cache()
+
+
+def extra_points(args, first: Bench) -> tuple:
+    """The measurements beside the headline; each guarded, so that a failure of
+    one is reported under its own name and costs nothing else."""
+    points, detail = {}, {}
+
+    def guarded(name, fn):
+        try:
+            fn()
+        except Exception as err:  # noqa: BLE001 - reported in the line, never fatal to the headline
+            detail[name] = {"error": f"{type(err).__name__}: {err}"[:300]}
+
+    steps = max(64, args.steps // 2)
+
+    def long_context():
+        fill = CONTEXT - steps - args.warmup - 8  # prompts that leave room for the timed steps only
+        for batch in (8, 64):
+            point = first.decode(batch, steps, args.warmup, prompt_len=fill)
+            points[f"decode_b{batch}_ctx4096"] = round(point["tok_s"], 1)
+            detail[f"decode_b{batch}_ctx4096"] = dict(first.detail(point), prompt_len=fill)
+
+    guarded("decode_ctx4096", long_context)
+    first.close()
+
+    def shape_15b():
+        bench = Bench("1.5b", 0, 64)
+        try:
+            served = bench.serve(64, 256, 128, 2048)
+            points["qwen2.5-1.5b_serve64_tok_s"] = served["tok_s"]
+            detail["qwen2.5-1.5b_serve64"] = served
+            point = bench.decode(8, steps, args.warmup)
+            points["qwen2.5-1.5b_decode_b8"] = round(point["tok_s"], 1)
+            detail["qwen2.5-1.5b_decode_b8"] = bench.detail(point)
+        finally:
+            bench.close()
+
+    def shape_7b():
+        bench = Bench("7b", 0, 64)
+        try:
+            for batch in (1, 8, 64):
+                point = bench.decode(batch, steps, args.warmup)
+                points[f"qwen2.5-7b_decode_b{batch}"] = round(point["tok_s"], 1)
+                detail[f"qwen2.5-7b_decode_b{batch}"] = bench.detail(point)
+            pre = bench.prefill(args.warmup)
+            points["qwen2.5-7b_prefill_tok_s"] = pre["value"]
+            detail["qwen2.5-7b_prefill"] = pre
+        finally:
+            bench.close()
+
+    guarded("qwen2.5-1.5b", shape_15b)
+    guarded("qwen2.5-7b", shape_7b)
+    return points, detail
+
+
+def run(args) -> dict:
+    from alofa_b200.engine.context import Layout
+
+    bench = Bench(args.shape, args.layers, max(64, args.batch))
+    cfg, layers, engine, runner = bench.cfg, bench.layers, bench.engine, bench.runner
+
     if args.phase == "decode":
-        print(json.dumps({"phase": "decode", "batch": args.batch, "ms_per_step": main["ms"], "tok_s": main["tok_s"], "launches": main["launches"]}))
+        prefill = None
+    else:
+        prefill = bench.prefill(args.warmup)
+    if args.phase == "prefill":
+        print(json.dumps({"phase": "prefill", "ms": prefill["ms"], "tok_s": prefill["value"], "reps": prefill["reps"]}))
         raise SystemExit(0)
-    b1 = decode_point(1, max(8, args.steps // 2), args.warmup)
-    b64 = decode_point(64, max(8, args.steps // 2), args.warmup)
-    achieved = main["bytes"] / (main["ms"] * 1e-3) / 1e9
+
+    main = bench.decode(args.batch, args.steps, args.warmup, clocks=ClockSampler())
+    if args.phase == "decode":
+        print(json.dumps({"phase": "decode", "batch": args.batch, "ms_per_step": main["ms"], "tok_s": main["tok_s"], "launches": main["launches"], "step_ms": main["step_ms"]}))
+        raise SystemExit(0)
+    b1 = bench.decode(1, max(8, args.steps // 2), args.warmup)
+    b64 = bench.decode(64, max(8, args.steps // 2), args.warmup)
 
     # -- end to end: Engine.generate, host tokens in and out --------------------
     # as many new tokens as timed steps: the requests start and end a tick apart each, so a short
     # run is mostly steps with fewer rows than the batch
     e2e_new = max(8, min(256, args.steps))
-    prompts = [prompt(PROMPT_LEN) for _ in range(args.batch)]
+    prompts = [bench.prompt(PROMPT_LEN) for _ in range(args.batch)]
     engine.generate(prompts, max_new_tokens=e2e_new)  # the same run once untimed: records the CUDA graphs it uses
     engine.marks.clear()
     rows_before = engine.counters["decode_rows"]
@@ -271,25 +417,34 @@ def run(args) -> dict:
     decode_rows = sum(rows for t, kind, rows in engine.marks if kind == "decode" and t > last_prefill)
     assert decode_rows <= engine.counters["decode_rows"] - rows_before
     e2e_value = decode_rows / decode_wall if decode_wall > 0 else None
-    from alofa_b200.engine.context import Layout
 
     h2d = Layout.make(args.batch, args.batch, args.batch, runner._group_shapes).total * 4
+    points = {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1)}
+    detail = {"decode_b1": bench.detail(b1), f"decode_b{args.batch}": bench.detail(main), "decode_b64": bench.detail(b64)}
+    if args.extra and args.shape == "0.5b" and not args.layers:
+        more_points, more_detail = extra_points(args, bench)
+        points.update(more_points)
+        detail.update(more_detail)
+    metric = METRIC if args.shape == "0.5b" else METRIC.replace("Qwen2.5-0.5B shape", bench.label)
     result = {
-        "metric": METRIC, "value": round(main["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "metric": metric, "value": round(main["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights, uniform random token ids", "impl": "alofa_b200",
         "config": {
-            "model": "Qwen2.5-0.5B shape", "layers": layers, "layers_full": full_layers, "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+            "model": bench.label, "layers": layers, "layers_full": bench.full_layers, "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
             "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "global_batch": args.batch, "prompt_len": PROMPT_LEN, "seq_len": CONTEXT, "block_size": 64, "parallelism": "single GPU",
-            "l2": "inputs>L2 (each step reads >1 GB)", "peaks": pk_kind,
+            "l2": "inputs>L2 (each step reads >1 GB)", "peaks": bench.peaks_kind,
         },
-        "e2e": {"value": round(e2e_value, 1) if e2e_value else None, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch,
+        "e2e": {"value": round(e2e_value, 1) if e2e_value else None, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch + 4,
                 "new_tokens": e2e_new, "wall_s_with_prefill": round(wall, 3), "outputs": len(outs)},
         "gpu_launches": main["launches"],
-        "prefill": prefill,
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": {"decode_b1": round(b1["tok_s"], 1), "decode_b64": round(b64["tok_s"], 1)},
+        "prefill": {k: v for k, v in prefill.items() if k != "reps"},
+        "roofline": {"bound": "hbm", "achieved": round(main["gbs"], 1), "peak": bench.peaks["hbm_gbs"], "unit": "GB/s", "frac": round(main["frac"], 4)},
+        "points": points,
+        "step_ms": main["step_ms"],
+        "prefill_reps": prefill["reps"],
+        "points_detail": detail,
         "clocks": main["clocks"],
     }
     return result
@@ -310,6 +465,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the full shape (named in config)")
     ap.add_argument("--phase", choices=["all", "decode", "prefill"], default="all", help="profiling aid: run only one part; the JSON line then lacks the others")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="whose layer sizes the headline run has")
+    ap.add_argument("--no-extra", dest="extra", action="store_false", help="leave out the measurements beside the headline (long contexts, the 1.5B and 7B shapes)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps(reference_arm()))

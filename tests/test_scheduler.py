@@ -204,3 +204,105 @@ def test_no_cache_group_means_admission_by_slots_alone():
         assert 3 in seen and s.counts()["live"] == 0
         text = format_config(cfg)
         assert text.endswith("G=-") and parse_config(text).groups == []
+
+
+# -- the reference's recorded runs ---------------------------------------------------
+def replay_reference_fixture(fixture: dict, admission: str):
+    """Feed a recorded run of the reference's scheduler to ours.  The reference
+    keeps a block count of its own (finished requests' blocks stay held as its
+    prefix cache until the engine reports them freed, `R=`); ours is told the
+    free pages each tick, so the harness keeps that book: pages of live
+    requests from our own decisions, plus the blocks the reference would hold
+    cached.  `max_new` is translated: the reference counts decode ticks, ours
+    counts tokens and the step that ends a prompt yields the first, so the
+    reference's max_new is ours plus one.  Returns per tick (ours, reference)
+    as (prompt portions, decoded, preempted, finished by the scheduler)."""
+    cfg = fixture["cfg"]
+    bs, cap = cfg["s"], cfg["k"]
+    blocks = lambda n: 0 if n <= 0 else -(-n // bs)
+    sched = Scheduler(SchedConfig(token_budget=cfg["b"], max_chunk=cfg["c"], max_batch=32, max_tokens=1 << 20, watermark_permille=cfg["w"],
+                                  max_wait_ticks=cfg["t"], admission=admission, groups=[(bs, 0, cap)]))
+    live, sizes, cached, deferred, out = {}, {}, 0, [], []
+    for tick in fixture["ticks"]:
+        cached -= tick["R"]
+        for rid in tick["C"]:
+            live.pop(rid, None)
+        for rid in tick["F"]:
+            if rid in live:
+                cached += blocks(sum(sizes[rid]))
+                live.pop(rid)
+        arrivals = deferred + [(i, p, m + 1) for i, p, m in tick["A"] if i not in tick["C"]]
+        sizes.update({i: (p, m) for i, p, m in tick["A"]})
+        held = sum(blocks(n) for n in live.values())
+        act = sched.step(SchedInput(arrivals, tick["C"], tick["F"], [cap - held - cached]))
+        deferred = [a for a, status in zip(arrivals, act.arrival_status) if status == 0]
+        for rid in act.preempted:
+            live[rid] = 0
+        for rid, _, end in act.prefill:
+            live[rid] = end
+        for rid in act.decode:
+            live[rid] = live.get(rid, 0) + 1
+        for rid in act.finished:
+            cached += blocks(sum(sizes[rid]))
+            live.pop(rid, None)
+        ours = ([list(p) for p in act.prefill], list(act.decode), list(act.preempted), list(act.finished))
+        ref = (tick["P"], tick["D"], tick["X"], [f for f in tick["Fout"] if f not in tick["F"]])  # the reference echoes engine-reported completions
+        out.append((ours, ref))
+    return out, sched
+
+
+def reference_fixtures():
+    import json
+    from pathlib import Path
+
+    return json.loads((Path(__file__).parent / "golden" / "scheduler_fixtures.json").read_text())
+
+
+@pytest.mark.parametrize("admission", ["committed", "optimistic"])
+@pytest.mark.parametrize("name", ["s01_long_prompt", "s03_budget_exhausted", "s04_zero_budget", "s05_cancel_race"])
+def test_reference_runs_that_ours_decides_the_same(name, admission):
+    """Chunked prefill under one token budget, decode before prefill, one
+    portion per request per tick, the first token with the last portion, a zero
+    budget, cancels that block a same-tick arrival, completions the engine
+    reports: every tick's portions, decoded requests, preemptions and finishes
+    are the reference's."""
+    ticks, _ = replay_reference_fixture(reference_fixtures()[name], admission)
+    for t, (ours, ref) in enumerate(ticks, 1):
+        assert ours == ref, f"{name} tick {t}: ours {ours} reference {ref}"
+
+
+def test_reference_run_where_waiting_order_differs_on_purpose():
+    """s07_cache_freed: the reference walks waiting requests in slot order, and
+    a new arrival takes the lowest free slot, so at tick 3 request 3 (new, in
+    the slot request 1 left) goes before request 2, which still owes one prompt
+    token.  Ours walks them in admission order: 2 ends its prompt first.  Ticks
+    3 to 5 differ by exactly that exchange; every other tick is the same, and
+    both finish every request."""
+    ticks, sched = replay_reference_fixture(reference_fixtures()["s07_cache_freed"], "committed")
+    differ = [t for t, (ours, ref) in enumerate(ticks, 1) if ours != ref]
+    assert differ == [3, 4, 5]
+    assert ticks[2][0][0] == [[2, 15, 16], [3, 0, 15]] and ticks[2][1][0] == [[3, 0, 16]]
+    finished = lambda side: sorted(r for tick in ticks for r in tick[side][3])
+    assert finished(0) == finished(1) == [1, 2, 3, 4, 5, 6, 7, 8]
+    assert sched.counts()["live"] == 0
+
+
+@pytest.mark.parametrize("name, first", [("s02_preempt_storm", 9), ("s06_kv_watermark", 13)])
+def test_reference_runs_that_storm_where_ours_defers(name, first):
+    """Three requests arrive that fit under the watermark only if the blocks of
+    earlier, finished requests (still held as the reference's prefix cache) are
+    not counted.  The reference admits by the live requests' lengths alone,
+    prefills all three and then preempts tick after tick, dozens of times (its
+    scenario is named for that).  Ours counts every held page (one book):
+    with optimistic admission the arrival that does not fit is deferred at that
+    tick, nothing is ever preempted, and every request finishes.  Every tick
+    before the arrival is the reference's."""
+    fixture = reference_fixtures()[name]
+    ticks, sched = replay_reference_fixture(fixture, "optimistic")
+    differ = [t for t, (ours, ref) in enumerate(ticks, 1) if ours != ref]
+    assert differ[0] == first and all(ours == ref for ours, ref in ticks[: first - 1])
+    ours_first, ref_first = ticks[first - 1]
+    assert len(ours_first[0]) == 1 and len(ref_first[0]) == 2  # one prompt started where the reference starts two
+    assert fixture["ticks"][-1]["preempt_total"] > 30 and all(not ours[2] for ours, _ in ticks)
+    arrived = sorted(a[0] for tick in fixture["ticks"] for a in tick["A"])
+    assert sorted(r for ours, _ in ticks for r in ours[3]) == arrived and sched.counts()["live"] == 0
