@@ -14,11 +14,14 @@ import tiny
 pytestmark = pytest.mark.gpu
 
 # Largest |engine - plain| allowed on logits, times max(1, max|plain|).
-# float32: fp32 sums against the plain implementation's float64.
-# bfloat16: activations and cache entries are rounded to 8 bits of mantissa.
-TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+# float32: fp32 sums against the plain implementation's float64 (worst seen over all runs of
+# this file: 7.9e-7).  bfloat16: activations and cache entries are rounded to 8 bits of
+# mantissa; the bound is about twice the worst seen (4.5e-3 against plain, 3.2e-3 between
+# cuts), and the reference's own gate for reduced precision (cosine and largest logit, see
+# check) is applied beside it.
+TOL = {"float32": 1e-5, "bfloat16": 1e-2}
 # between two cuts of the same request inside one dtype
-TOL_CUT = {"float32": 2e-6, "bfloat16": 2e-2}
+TOL_CUT = {"float32": 2e-6, "bfloat16": 7e-3}
 
 LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 9, 64, 127, 143], "C": [3, 40, 75, 130]}
 
@@ -50,15 +53,39 @@ def runner_for(folder, dtype, block, pages):
     return StepRunner(model, block_size=block, num_pages=pages, max_requests=8, max_tokens=model.spec.max_position, max_step_tokens=512)
 
 
-def check(got, want, tol, what):
+def check(got, want, tol, what, gate=False):
+    """Largest absolute difference against ``tol * max(1, max|ref|)``.  With
+    ``gate`` (bfloat16 against plain) also the reference's own gate for reduced
+    precision (tests/unit/test_model_parity.mojo:49-51): every row's cosine
+    with the plain row at least 0.999, and the same largest logit - or, where
+    plain has a near-tie at the top, one of the tied."""
     for rid, ref in want.items():
         assert rid in got, f"{what}: request {rid} has no output"
         assert got[rid].shape == ref.shape, f"{what}: {rid} shape {got[rid].shape} vs {ref.shape}"
         diff = np.abs(got[rid] - ref)
         bound = tol * max(1.0, float(np.abs(ref).max()))
+        record_worst(what, float(diff.max()) / max(1.0, float(np.abs(ref).max())))
         if diff.max() > bound:
             pos = int(np.argmax(diff.max(axis=1) > bound))
             raise AssertionError(f"{what}: request {rid} first differs at position {pos}: {diff[pos].max():.3e} > {bound:.3e}")
+        if gate:
+            mine = got[rid].astype(np.float64)
+            cosine = (mine * ref).sum(axis=1) / (np.linalg.norm(mine, axis=1) * np.linalg.norm(ref, axis=1))
+            assert cosine.min() >= 0.999, f"{what}: request {rid} position {int(cosine.argmin())}: cosine {cosine.min():.5f}"
+            picked = mine.argmax(axis=1)
+            short = ref.max(axis=1) - ref[np.arange(len(ref)), picked]
+            assert short.max() <= 2 * bound, f"{what}: request {rid} position {int(short.argmax())}: picks a logit {short.max():.3e} below the plain maximum"
+
+
+def record_worst(what, ratio):
+    """ALOFA_RECORD_WORST=FILE appends every comparison's worst difference (as a
+    fraction of max(1, max|ref|)): the bounds above were set from such a run."""
+    import os
+
+    path = os.environ.get("ALOFA_RECORD_WORST")
+    if path:
+        with open(path, "a") as fh:
+            fh.write(f"{what}\t{ratio:.6e}\n")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -73,7 +100,7 @@ def test_every_cut_matches_plain(model_folders, plain_logits, name, dtype, block
     results = {}
     for what, steps in (("whole", replay.whole(reqs)), ("tail", replay.tail_decoded(reqs)), ("portions", replay.portions(reqs))):
         results[what] = replay.collect(steps, replay.run_inprocess(runner, steps), vocab)
-        check(results[what], ref, TOL[dtype], f"{name}/{dtype}/{what}")
+        check(results[what], ref, TOL[dtype], f"{name}/{dtype}/{what}", gate=dtype == "bfloat16")
     # so few pages that they are used again: room for about two and a half requests
     pool = longest + max(block * 3, longest // 2)
     runner = runner_for(model_folders[name], dtype, block, pages=pool // block)
@@ -82,7 +109,7 @@ def test_every_cut_matches_plain(model_folders, plain_logits, name, dtype, block
         assert max(len(s["entries"]) for s in steps) > 1
         out = replay.run_inprocess(runner, steps)
         results["mixed"] = replay.collect(steps, out, vocab)
-        check(results["mixed"], ref, TOL[dtype], f"{name}/{dtype}/mixed{seed}")
+        check(results["mixed"], ref, TOL[dtype], f"{name}/{dtype}/mixed{seed}", gate=dtype == "bfloat16")
     counters = runner.manager.counters(0)
     assert counters["allocs"] > runner.group_specs[0].num_pages, "the pool was never reused"
     assert runner.manager.free_pages(0) == runner.group_specs[0].num_pages
