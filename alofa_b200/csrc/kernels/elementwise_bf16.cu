@@ -6,6 +6,8 @@
 //   alofa_norm_fused        h += bias + sum_z partial[z]  (optional), then
 //                           x = h / sqrt(mean(h^2) + eps) * w      (RMSNorm,
 //                           src/alofa/kernels/cpu/scalar.mojo:93-129)
+//   alofa_stream_settle     h = base + accumulator: the residual stream of a small decode
+//                           step brought back to one fp32 tensor (see STREAM_SCALE)
 //   alofa_rope_store_fused  qkv = bias + sum_z partial[z] (or a bf16 tensor),
 //                           NeoX rotation of q and k, k and v written to
 //                           their cache slots (scalar.mojo:283-344,
@@ -31,10 +33,45 @@ __device__ __forceinline__ void add_splits(float4& v, const float4* p, int z0, i
   }
 }
 
+// The residual stream of a decode step of a few tokens may stand as a base tensor plus a
+// 64-bit fixed-point accumulator (units of 2^-32) into which the products that add to the
+// stream sent their split sums with atomic adds: integer addition does not depend on the
+// order of arrival, so the sum is the same every run, and it is rounded to fp32 once, here
+// or in the product that reads the stream next (gemm_tc.cu, B_NORMED).
+constexpr float STREAM_SCALE = 4294967296.0f;
+__device__ __forceinline__ float4 stream_value(float4 v, const longlong2* acc2) {
+  const longlong2 a = acc2[0], b = acc2[1];
+  // base and accumulator are added in double (exact for sums below 2^21) and rounded to fp32 once
+  v.x = (float)((double)v.x + (double)a.x * (1.0 / 4294967296.0));
+  v.y = (float)((double)v.y + (double)a.y * (1.0 / 4294967296.0));
+  v.z = (float)((double)v.z + (double)b.x * (1.0 / 4294967296.0));
+  v.w = (float)((double)v.w + (double)b.y * (1.0 / 4294967296.0));
+  return v;
+}
+
+// h[t] = base[t] + acc[t] for every row, and both accumulators left zero.
+__global__ void stream_settle_kernel(float* __restrict__ h, const float* __restrict__ base, long long* __restrict__ acc,
+                                     long long* __restrict__ other, int count4) {
+  pdl_begin();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count4) return;
+  float4 v = reinterpret_cast<const float4*>(base)[i];
+  longlong2* a2 = reinterpret_cast<longlong2*>(acc) + 2 * (size_t)i;
+  v = stream_value(v, a2);
+  reinterpret_cast<float4*>(h)[i] = v;
+  a2[0] = a2[1] = make_longlong2(0, 0);
+  if (other) {
+    longlong2* o2 = reinterpret_cast<longlong2*>(other) + 2 * (size_t)i;
+    o2[0] = o2[1] = make_longlong2(0, 0);
+  }
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, float* __restrict__ h, const float* __restrict__ w,
                                                          const float* __restrict__ partial, const float* __restrict__ bias,
-                                                         const int* __restrict__ rows, int n_tokens, int hidden, int splits, float eps) {
+                                                         const int* __restrict__ rows, int n_tokens, int hidden, int splits, float eps,
+                                                         const float* __restrict__ base, long long* __restrict__ acc,
+                                                         long long* __restrict__ other) {
   extern __shared__ float row_buf[];  // hidden floats
   __shared__ float scratch[32];
   const int n4 = hidden >> 2;
@@ -45,10 +82,25 @@ __global__ void __launch_bounds__(256) norm_fused_kernel(TO* __restrict__ out, f
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float4* hr = reinterpret_cast<float4*>(h + (size_t)src * hidden);
+  const float4* br = base ? reinterpret_cast<const float4*>(base + (size_t)src * hidden) : hr;
   const size_t plane4 = ((size_t)n_tokens * hidden) >> 2;
   float ss = 0.f;
   for (int c = threadIdx.x; c < n4; c += blockDim.x) {
-    float4 v = hr[c];
+    float4 v = br[c];
+    if (acc) {
+      // the stream stands as base + accumulator: this row is brought back to one tensor and its
+      // share of both accumulators left zero (rows == nullptr here: every row has its block)
+      longlong2* a2 = reinterpret_cast<longlong2*>(acc + (size_t)src * hidden) + 2 * c;
+      v = stream_value(v, a2);
+      a2[0] = a2[1] = make_longlong2(0, 0);
+      if (other) {
+        longlong2* o2 = reinterpret_cast<longlong2*>(other + (size_t)src * hidden) + 2 * c;
+        o2[0] = o2[1] = make_longlong2(0, 0);
+      }
+      if (!partial) hr[c] = v;
+    } else if (base && !partial) {
+      hr[c] = v;
+    }
     if (partial) {
       // up to 24 splits in one round of loads (a round is a trip to L2), more in rounds of 8
       const float4* p = reinterpret_cast<const float4*>(partial) + (size_t)src * n4 + c;
@@ -179,11 +231,16 @@ static void dispatch_norm_rows(TO* out, float* h, const float* w, const float* p
   else launch_norm_rows<TO, 32>(out, h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps, stream);
 }
 
+// base (optional): the rows are read from `base` instead of h (h is written, complete).  acc
+// (optional, with rows == nullptr only): a fixed-point accumulator [n_tokens, hidden] added on
+// top and left zero, as is `other`.
 ALOFA_API int alofa_norm_fused(void* out, void* h, const float* w, const float* partial, const float* bias, const int* rows, int n_rows,
-                               int n_tokens, int hidden, int splits, float eps, int out_bf16, cudaStream_t stream) {
+                               int n_tokens, int hidden, int splits, float eps, int out_bf16, const float* base, long long* acc,
+                               long long* other, cudaStream_t stream) {
   if (n_rows <= 0) return ALOFA_OK;
   if (hidden % 4 != 0 || hidden > 12288) return ALOFA_ERR_ARGUMENT;
-  if (n_rows >= 256 && hidden <= 4096) {  // many rows: a warp each, the row in registers
+  if ((acc || base) && (rows || n_rows != n_tokens)) return ALOFA_ERR_ARGUMENT;
+  if (n_rows >= 256 && hidden <= 4096 && !acc && !base) {  // many rows: a warp each, the row in registers
     if (out_bf16)
       dispatch_norm_rows<bf16>((bf16*)out, (float*)h, w, partial, bias, rows, n_rows, n_tokens, hidden, splits, eps, stream);
     else
@@ -194,9 +251,18 @@ ALOFA_API int alofa_norm_fused(void* out, void* h, const float* w, const float* 
   ALOFA_PREFER_MAX_SHARED(norm_fused_kernel<bf16>);
   ALOFA_PREFER_MAX_SHARED(norm_fused_kernel<float>);
   if (out_bf16)
-    launch_dep(norm_fused_kernel<bf16>, n_rows, 256, smem, stream, (bf16*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps);
+    launch_dep(norm_fused_kernel<bf16>, n_rows, 256, smem, stream, (bf16*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps, base, acc, other);
   else
-    launch_dep(norm_fused_kernel<float>, n_rows, 256, smem, stream, (float*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps);
+    launch_dep(norm_fused_kernel<float>, n_rows, 256, smem, stream, (float*)out, (float*)h, w, partial, bias, rows, n_tokens, hidden, splits, eps, base, acc, other);
+  return launch_status();
+}
+
+// h = base + acc for all `count` values (a multiple of 4), both accumulators left zero.
+ALOFA_API int alofa_stream_settle(float* h, const float* base, long long* acc, long long* other, int count, cudaStream_t stream) {
+  if (count <= 0) return ALOFA_OK;
+  if ((count & 3) || !h || !base || !acc) return ALOFA_ERR_ARGUMENT;
+  const int count4 = count >> 2;
+  launch_dep(stream_settle_kernel, (count4 + 255) / 256, 256, 0, stream, h, base, acc, other, count4);
   return launch_status();
 }
 

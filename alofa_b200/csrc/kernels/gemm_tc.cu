@@ -23,6 +23,15 @@
 // that a small token count still pulls weights through every SM; the partial
 // sums are added in a fixed order by alofa_splitk_reduce.
 //
+// Small decode steps (up to 16 tokens) keep the residual stream as a base tensor plus a 64-bit
+// fixed-point accumulator (units of 2^-32): residual products add their split sums into the
+// accumulator with atomic integer adds - the sum does not depend on the order of arrival - and the
+// product that reads the stream next (q/k/v, gate/up) makes its token operand from base +
+// accumulator itself, with the RMSNorm folded in (B_NORMED): the operand is (base + acc) * gamma,
+// the row's 1/sqrt(mean square + eps) is a per-token factor and is applied to the accumulator in
+// the epilogue (src/alofa/kernels/cpu/scalar.mojo:93-129 for the norm).  No norm kernel, no split
+// sums in memory.
+//
 // Every wait on an mbarrier is bounded: after the limit the CTA raises the
 // status word, skips its remaining work, frees its tensor memory and returns.
 #include "common.cuh"
@@ -32,7 +41,8 @@
 #include "tma.cuh"
 
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED = 2, EPI_ROPE = 3 };  // EPI_ROPE: weights-on-M tiles of 16 tokens only
-enum { B_ROWS = 0, B_MERGED_SPLITS = 1 };
+enum { B_ROWS = 0, B_MERGED_SPLITS = 1, B_NORMED = 2 };
+constexpr float STREAM_SCALE = 4294967296.0f;  // units of the residual accumulator: 2^-32
 
 constexpr int BM = 128;        // features per CTA (UMMA M)
 constexpr int BK = 64;         // k-slice: 64 bf16 = one 128-byte swizzle row
@@ -57,6 +67,18 @@ struct GemmArgs {
   const int* b_positions;   // merged splits: position of each token
   int b_heads, b_head_dim, b_window, b_split_keys;
   int cluster;              // the splits of a tile are a thread-block cluster and add their sums up themselves (MODE_CLUSTER)
+  // EPI_RESIDUAL into a stream kept as base + accumulator: every CTA adds its sums (the first split
+  // the bias too) into acc [T, N] with atomic 64-bit integer adds, in units of 2^-32
+  long long* acc;
+  // B_NORMED (cluster kernels of 16 tokens): the token operand is RMSNorm(base + n_acc) made by the
+  // epilogue warps; the CTAs of the first feature tile also write base + n_acc to n_out (the
+  // stream's new base) and zero n_zero (the accumulator the next residual product adds into)
+  const float* n_base;       // [T, K] fp32
+  const long long* n_acc;    // [T, K] or null
+  const float* n_gamma;      // [K]
+  float* n_out;              // [T, K]
+  long long* n_zero;         // [T, K] or null
+  float n_eps;
   // EPI_ROPE: the weight is [q heads | k heads | v heads] stacked; the epilogue adds the bias, rotates q and k
   // (NeoX halves, cos/sin from a table by position) and writes q to its buffer, k and v to their cache slots
   bf16* rope_q;             // [T, heads * head_dim]
@@ -142,7 +164,8 @@ __device__ __forceinline__ uint4 merged_splits8(const GemmArgs& a, int t, int k0
 // MODE_CLUSTER: the CTAs that split the depth of a tile form a thread-block cluster along z; the
 // others push their accumulators into the shared memory of the first, which adds them in split
 // order and runs the epilogue - no partial sums in global memory, no second kernel.
-enum { MODE_PLAIN = 0, MODE_COMPUTED = 1, MODE_CLUSTER = 2 };
+// MODE_NORMED: MODE_CLUSTER with the token operand made from the residual stream (B_NORMED).
+enum { MODE_PLAIN = 0, MODE_COMPUTED = 1, MODE_CLUSTER = 2, MODE_NORMED = 3 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -184,8 +207,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int slice_end = min(total_slices, slice_begin + args.k_slices_per_split);
   const int n_slices = slice_end - slice_begin;
 
-  constexpr bool COMPUTED = MODE == MODE_COMPUTED, CLUSTER = MODE == MODE_CLUSTER;
-  constexpr bool computed_b = COMPUTED;
+  constexpr bool COMPUTED = MODE == MODE_COMPUTED, NORMED = MODE == MODE_NORMED, CLUSTER = MODE == MODE_CLUSTER || NORMED;
+  constexpr bool computed_b = COMPUTED || NORMED;
   const uint32_t rank = CLUSTER ? cluster_rank() : 0;  // this CTA's split of the depth, within its cluster
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -232,6 +255,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   }
+  // B_NORMED: this thread's chunks of the norm's weight (a constant of the model), ahead of the wait
+  constexpr int NORM_BATCH = 3;  // k-slices whose loads are in flight together (a batch is one trip to L2)
+  float4 gamma_lo[NORMED ? NORM_BATCH : 1], gamma_hi[NORMED ? NORM_BATCH : 1];
+  if constexpr (NORMED) {
+    if (warp >= 2) {
+      const int c = (threadIdx.x - 64) & 7;
+#pragma unroll
+      for (int b = 0; b < NORM_BATCH; ++b) {
+        const int k = (slice_begin + b) * BK + c * 8;
+        gamma_lo[b] = gamma_hi[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b < n_slices && k < args.K) {
+          gamma_lo[b] = *reinterpret_cast<const float4*>(args.n_gamma + k);
+          gamma_hi[b] = *reinterpret_cast<const float4*>(args.n_gamma + k + 4);
+        }
+      }
+    }
+  }
   // The weights depend on no earlier kernel: the producer asks for the first ring of weight tiles
   // before it waits for the kernel before this one; only the token operand comes after the wait.
   // The kernel after this one is let in after the wait (see pdl_launch).
@@ -258,12 +298,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   bool epilogue_ok = false;
   float* pushed = reinterpret_cast<float*>(tiles + (size_t)stages * STAGE_BYTES);
   float* rope_xchg = pushed + (CLUSTER ? (size_t)(gridDim.z - 1) * N_ACC * BN * 128 : 0);  // EPI_ROPE: [16 tokens][128 features]
+  float* row_ss = rope_xchg + (EPI == EPI_ROPE ? 16 * 128 : 0);  // MODE_NORMED: [8 ranks][16 tokens] sums of squares, in the first CTA
   auto epilogue = [&](bool with_remote) {
     const int q = warp & 3;
     const int f = f0 + q * 32 + lane;
     const bool f_ok = f < args.N;
     const bool split = gridDim.z > 1 && !CLUSTER;
     const bool push = CLUSTER && rank != 0;
+    // MODE_NORMED: the accumulator holds sums over (base + acc) * gamma; the row's factor 1 / sqrt(mean
+    // square + eps) comes from the sums of squares all CTAs of the cluster sent to the first
+    float rstd[NORMED ? 16 : 1];
+    if constexpr (NORMED) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (push) break;
+        float ss = 0.f;
+        for (uint32_t z = 0; z < gridDim.z; ++z) ss += row_ss[z * 16 + j];
+        rstd[j] = 1.0f / sqrtf(ss / (float)args.K + args.n_eps);
+      }
+    }
     float bias0 = 0.f, bias1 = 0.f;
     if (EPI == EPI_ROPE) {
       bias0 = rope_bias;
@@ -316,6 +369,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
         }
       }
+      if constexpr (NORMED) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          r0[j] = __float_as_uint(__uint_as_float(r0[j]) * rstd[j]);
+          if (N_ACC == 2) r1[j] = __float_as_uint(__uint_as_float(r1[j]) * rstd[j]);
+        }
+      }
       if constexpr (EPI == EPI_ROPE) {
         // Rotate-and-store.  A thread holds one feature of 16 tokens; its rotation partner, half a
         // head away, is another thread of this CTA (a tile of 128 features holds whole heads): the
@@ -354,6 +414,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       if (!f_ok) continue;
       const int t_base = t0 + c0;
+      if (EPI == EPI_RESIDUAL && args.acc) {
+        // the stream stands as base + accumulator: integer adds, whose sum does not depend on their order
+        unsigned long long* a = reinterpret_cast<unsigned long long*>(args.acc) + (size_t)t_base * args.N + f;
+        const float b = blockIdx.z == 0 && args.bias ? args.bias[f] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (t_base + j < args.T) atomicAdd(a + (size_t)j * args.N, (unsigned long long)__float2ll_rn((__uint_as_float(r0[j]) + b) * STREAM_SCALE));
+        continue;
+      }
       if (!split && EPI == EPI_RESIDUAL) {
         // read the 16 residual values first, then write: the loads overlap
         float* o = (float*)args.out + (size_t)t_base * args.N + f;
@@ -445,6 +514,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive(&full_bar[s]);
       }
+    }
+    if constexpr (NORMED) {
+      // The token operand from the residual stream, a batch of k-slices per trip to L2: this thread's
+      // eight values of token r are base + accumulator (rounded to fp32 once), times the norm's weight;
+      // their squares are summed for the row's factor.  Rows of 128 bytes, chunk c of row r at c ^ (r & 7).
+      const int tid = threadIdx.x - 64;
+      const int r = tid >> 3, c = tid & 7, t = t0 + r;
+      const uint32_t at = r * 128 + ((c ^ (r & 7)) << 4);
+      const bool writes_stream = blockIdx.x == 0;  // one feature tile brings the stream's new base to memory
+      float ss = 0.f;
+      for (int i0 = 0; i0 < n_slices; i0 += NORM_BATCH) {
+        float4 lo[NORM_BATCH], hi[NORM_BATCH];
+        longlong2 a[NORM_BATCH][4];
+#pragma unroll
+        for (int b = 0; b < NORM_BATCH; ++b) {
+          const int k = (slice_begin + i0 + b) * BK + c * 8;
+          const bool live = i0 + b < n_slices && t < args.T && k < args.K;
+          lo[b] = hi[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) a[b][q] = make_longlong2(0, 0);
+          if (live) {
+            const size_t e = (size_t)t * args.K + k;
+            lo[b] = *reinterpret_cast<const float4*>(args.n_base + e);
+            hi[b] = *reinterpret_cast<const float4*>(args.n_base + e + 4);
+            if (args.n_acc) {
+              const longlong2* p = reinterpret_cast<const longlong2*>(args.n_acc + e);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) a[b][q] = p[q];
+            }
+            if (i0 > 0) {  // the first batch's weights were read ahead of the wait
+              gamma_lo[b] = *reinterpret_cast<const float4*>(args.n_gamma + k);
+              gamma_hi[b] = *reinterpret_cast<const float4*>(args.n_gamma + k + 4);
+            }
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < NORM_BATCH; ++b) {
+          const int i = i0 + b;
+          if (i >= n_slices) break;
+          const int s = i % stages;
+          const int k = (slice_begin + i) * BK + c * 8;
+          const bool live = t < args.T && k < args.K;
+          float v[8] = {lo[b].x, lo[b].y, lo[b].z, lo[b].w, hi[b].x, hi[b].y, hi[b].z, hi[b].w};
+          if (live && args.n_acc) {
+            const long long w8[8] = {a[b][0].x, a[b][0].y, a[b][1].x, a[b][1].y, a[b][2].x, a[b][2].y, a[b][3].x, a[b][3].y};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = (float)((double)v[j] + (double)w8[j] * (1.0 / 4294967296.0));
+          }
+          if (live && writes_stream) {
+            const size_t e = (size_t)t * args.K + k;
+            *reinterpret_cast<float4*>(args.n_out + e) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(args.n_out + e + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            if (args.n_zero) {
+              longlong2* z = reinterpret_cast<longlong2*>(args.n_zero + e);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) z[q] = make_longlong2(0, 0);
+            }
+          }
+          const float g[8] = {gamma_lo[b].x, gamma_lo[b].y, gamma_lo[b].z, gamma_lo[b].w, gamma_hi[b].x, gamma_hi[b].y, gamma_hi[b].z, gamma_hi[b].w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            ss = fmaf(v[j], v[j], ss);
+            v[j] *= g[j];
+          }
+          if (i >= stages && !mbar_wait(&empty_bar[s], ((i / stages) - 1) & 1, &abort_flag)) break;
+          *reinterpret_cast<uint4*>(tiles + (size_t)s * STAGE_BYTES + N_ACC * A_BYTES + at) = pack8(v);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive(&full_bar[s]);
+        }
+      }
+      // the row's sum of squares over this CTA's share of the depth, to the first CTA of the cluster
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      if (c == 0) store_remote_f32(smem_u32(row_ss + rank * 16 + r), 0, ss);
     }
     bool ok = n_slices > 0 ? mbar_wait(&acc_bar, 0, &abort_flag) : true;
     ok = __all_sync(0xffffffffu, ok);
@@ -978,7 +1122,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
     configured = true;
   }
   dim3 grid((args.N + BM - 1) / BM, (args.T + BN - 1) / BN, splits);
-  if (args.b_kind != B_ROWS) {
+  if (args.b_kind == B_MERGED_SPLITS) {
     if constexpr (BN == 16 && EPI == EPI_RESIDUAL) {
       static bool configured_c = false;
       if (!configured_c) {
@@ -993,20 +1137,15 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
       return ALOFA_ERR_ARGUMENT;  // a computed operand feeds residual products of up to 16 tokens
     }
   }
-  if (args.cluster) {
+  if (args.cluster || args.b_kind == B_NORMED) {
     if constexpr (((BN == 16 || BN == 32) && EPI == EPI_GATED) || (BN == 16 && EPI == EPI_ROPE)) {
-      // room behind the ring for the accumulators the other CTAs of a cluster push
-      const size_t pushed = (size_t)(splits - 1) * N_ACC * BN * 128 * sizeof(float) + XCHG;
+      const bool normed = args.b_kind == B_NORMED;
+      if (normed && (BN != 16 || grid.y != 1 || splits > 8)) return ALOFA_ERR_ARGUMENT;
+      // room behind the ring for the accumulators the other CTAs of a cluster push, and the rows' sums of squares
+      const size_t pushed = (size_t)(splits - 1) * N_ACC * BN * 128 * sizeof(float) + XCHG + (normed ? 8 * 16 * sizeof(float) : 0);
       int cstages = (int)((200 * 1024 - pushed) / STAGE);
       if (cstages > 12) cstages = 12;
       if (cstages < 2) return ALOFA_ERR_ARGUMENT;
-      static bool configured_k = false;
-      if (!configured_k) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, MODE_CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
-          return ALOFA_ERR_LAUNCH;
-        prefer_max_shared(gemm_tc_kernel<BN, EPI, MODE_CLUSTER>);
-        configured_k = true;
-      }
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = grid;
       cfg.blockDim = dim3(NUM_THREADS);
@@ -1021,6 +1160,26 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
       attr[1].val.clusterDim.z = (unsigned)splits;
       cfg.attrs = attr;
       cfg.numAttrs = 2;
+      if (normed) {
+        if constexpr (BN == 16) {
+          static bool configured_n = false;
+          if (!configured_n) {
+            if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, MODE_NORMED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
+              return ALOFA_ERR_LAUNCH;
+            prefer_max_shared(gemm_tc_kernel<BN, EPI, MODE_NORMED>);
+            configured_n = true;
+          }
+          cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, MODE_NORMED>, mw, mx, args, cstages);
+        }
+        return launch_status();
+      }
+      static bool configured_k = false;
+      if (!configured_k) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, MODE_CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
+          return ALOFA_ERR_LAUNCH;
+        prefer_max_shared(gemm_tc_kernel<BN, EPI, MODE_CLUSTER>);
+        configured_k = true;
+      }
       cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, MODE_CLUSTER>, mw, mx, args, cstages);
       return launch_status();
     } else {
@@ -1126,11 +1285,23 @@ ALOFA_API int alofa_gemm_tc_reduces_in_cluster(int epi, int bn, int splits) {
 // b_kind = B_MERGED_SPLITS (residual products of up to 16 tokens only): x is ignored and the
 // token operand is computed in the kernel from the attention output of decode tokens still in
 // key splits (b_src partial outputs, b_ml maxima and sums, b_positions; heads * head_dim == K).
+// acc (EPI_RESIDUAL, weights on M): the product's sums go into this fixed-point accumulator
+// [T, N] with atomic adds instead of into `out` or `partial` (see GemmArgs::acc).
+// b_kind = B_NORMED (gated products of up to 16 tokens, split up to 8 ways over a cluster): the token
+// operand is RMSNorm(b_src + n_acc) with weight n_gamma, made in the kernel; b_src + n_acc is also
+// written to n_out and n_zero is zeroed (GemmArgs::n_*).
 ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float* bias, float* partial, int T, int N, int K, int epi, int out_bf16,
                             int bn, int splits, int do_reduce, int* status, int b_kind, const float* b_src, const float* b_ml,
-                            const int* b_positions, int b_heads, int b_head_dim, int b_window, int b_split_keys, cudaStream_t stream) {
+                            const int* b_positions, int b_heads, int b_head_dim, int b_window, int b_split_keys, long long* acc,
+                            const long long* n_acc, const float* n_gamma, float n_eps, float* n_out, long long* n_zero, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return ALOFA_OK;
-  if (b_kind != B_ROWS) {
+  if (acc && (epi != EPI_RESIDUAL || bn <= 0)) return ALOFA_ERR_ARGUMENT;
+  if (b_kind == B_NORMED) {
+    if (bn != 16 || T > 16 || epi != EPI_GATED || !b_src || !n_gamma || !n_out || n_out == b_src || (K % 8) != 0 || !do_reduce) return ALOFA_ERR_ARGUMENT;
+    if (((uintptr_t)b_src & 15) || ((uintptr_t)n_gamma & 15) || ((uintptr_t)n_out & 15) || ((uintptr_t)n_acc & 15) || ((uintptr_t)n_zero & 15)) return ALOFA_ERR_ARGUMENT;
+    if (splits > 8) splits = 8;
+    x = w;  // any mapped address: the map of x is made but never used
+  } else if (b_kind != B_ROWS) {
     if (bn <= 0 || !b_src || ((uintptr_t)b_src & 15) || (K % 8) != 0) return ALOFA_ERR_ARGUMENT;
     if (b_kind != B_MERGED_SPLITS || !b_ml || !b_positions || b_heads * b_head_dim != K || b_head_dim % 8 || b_split_keys <= 0) return ALOFA_ERR_ARGUMENT;
     if (bn != 16 || epi != EPI_RESIDUAL) return ALOFA_ERR_ARGUMENT;  // one 16-byte chunk of a k-slice per epilogue thread
@@ -1141,7 +1312,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   const int total_slices = (K + BK - 1) / BK;
   if (splits < 1) splits = 1;
   if (splits > total_slices) splits = total_slices;
-  if (splits > 1 && !partial) return ALOFA_ERR_ARGUMENT;
+  if (splits > 1 && !partial && !acc && b_kind != B_NORMED) return ALOFA_ERR_ARGUMENT;
   const int w_rows = (epi == EPI_GATED) ? 2 * N : N;
   // bn > 0: weights on the M side, bn tokens per CTA.  bn < 0: tokens on the M
   // side (128 per CTA), -bn weight rows per MMA (for GATED half gate, half up).
@@ -1155,6 +1326,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
     return ALOFA_ERR_ARGUMENT;
   }
   GemmArgs args;
+  memset(&args, 0, sizeof(args));
   args.out = out;
   args.partial = partial;
   args.bias = bias;
@@ -1173,7 +1345,14 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   args.b_head_dim = b_head_dim;
   args.b_window = b_window;
   args.b_split_keys = b_split_keys;
-  args.cluster = alofa_gemm_tc_reduces_in_cluster(epi, bn, splits) && do_reduce && b_kind == B_ROWS;
+  args.cluster = (alofa_gemm_tc_reduces_in_cluster(epi, bn, splits) && do_reduce && b_kind == B_ROWS) || b_kind == B_NORMED;
+  args.acc = acc;
+  args.n_base = b_kind == B_NORMED ? b_src : nullptr;
+  args.n_acc = n_acc;
+  args.n_gamma = n_gamma;
+  args.n_eps = n_eps;
+  args.n_out = n_out;
+  args.n_zero = n_zero;
   int rc;
   if (tokens_on_m) {
     if (epi == EPI_STORE) rc = dispatch_tokens<EPI_STORE>(bnf, mw, mx, args, splits, stream);
@@ -1184,7 +1363,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   else if (epi == EPI_RESIDUAL) rc = dispatch_bn<EPI_RESIDUAL>(bn, mw, mx, args, splits, stream);
   else if (epi == EPI_GATED) rc = dispatch_bn<EPI_GATED>(bn, mw, mx, args, splits, stream);
   else return ALOFA_ERR_ARGUMENT;
-  if (rc != ALOFA_OK || splits == 1 || !do_reduce || args.cluster) return rc;
+  if (rc != ALOFA_OK || splits == 1 || !do_reduce || args.cluster || acc) return rc;
   const size_t plane = (size_t)T * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)((plane + threads - 1) / threads);
@@ -1216,10 +1395,18 @@ ALOFA_API int alofa_splitk_reduce(void* out, const float* partial, const float* 
 // [positions, head_dim / 2, 2] at `positions`, q to q_out [T, heads * head_dim], k and v to
 // their cache slots.  The depth is split over a cluster of up to 8 CTAs that add their sums up
 // themselves.  head_dim must divide 128 (a tile of 128 weight rows then holds whole heads).
+// With n_base the token operand is not x but RMSNorm(n_base + n_acc) with weight n_gamma, made in
+// the kernel (B_NORMED); n_base + n_acc is written to n_out and n_zero is zeroed.
 ALOFA_API int alofa_gemm_tc_rope(const void* x, const void* w, const float* bias, int T, int K, void* q_out, void* k_cache, void* v_cache,
                                  const int* slots, const int* positions, const float* table, int heads, int kv_heads, int head_dim,
-                                 int splits, int* status, cudaStream_t stream) {
+                                 int splits, int* status, const float* n_base, const long long* n_acc, const float* n_gamma, float n_eps,
+                                 float* n_out, long long* n_zero, cudaStream_t stream) {
   if (T <= 0) return ALOFA_OK;
+  if (n_base) {
+    if (!n_gamma || !n_out || n_out == n_base) return ALOFA_ERR_ARGUMENT;
+    if (((uintptr_t)n_base & 15) || ((uintptr_t)n_gamma & 15) || ((uintptr_t)n_out & 15) || ((uintptr_t)n_acc & 15) || ((uintptr_t)n_zero & 15)) return ALOFA_ERR_ARGUMENT;
+    x = w;  // the map of x is made but never used
+  }
   const int N = (heads + 2 * kv_heads) * head_dim;
   if (T > 16 || K <= 0 || (K % 8) != 0 || head_dim <= 0 || 128 % head_dim || head_dim % 2 || heads <= 0) return ALOFA_ERR_ARGUMENT;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || !q_out || !positions || !table || (kv_heads > 0 && (!k_cache || !v_cache || !slots))) return ALOFA_ERR_ARGUMENT;
@@ -1238,8 +1425,14 @@ ALOFA_API int alofa_gemm_tc_rope(const void* x, const void* w, const float* bias
   args.k_slices_per_split = (total_slices + splits - 1) / splits;
   splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;
   args.status = status;
-  args.b_kind = B_ROWS;
-  args.cluster = splits > 1;
+  args.b_kind = n_base ? B_NORMED : B_ROWS;
+  args.cluster = splits > 1 || n_base;
+  args.n_base = n_base;
+  args.n_acc = n_acc;
+  args.n_gamma = n_gamma;
+  args.n_eps = n_eps;
+  args.n_out = n_out;
+  args.n_zero = n_zero;
   args.rope_q = (bf16*)q_out;
   args.rope_k = (bf16*)k_cache;
   args.rope_v = (bf16*)v_cache;

@@ -71,13 +71,13 @@ def _gemm_tc():
     if lib is None:
         lib = load_library("alofa_gemm_tc", ["kernels/gemm_tc.cu"])
         lib.alofa_gemm_tc.restype = _I
-        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P]
+        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P]
         lib.alofa_splitk_reduce.restype = _I
         lib.alofa_splitk_reduce.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _P]
         lib.alofa_gemm_tc_reduces_in_cluster.restype = _I
         lib.alofa_gemm_tc_reduces_in_cluster.argtypes = [_I, _I, _I]
         lib.alofa_gemm_tc_rope.restype = _I
-        lib.alofa_gemm_tc_rope.argtypes = [_P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P]
+        lib.alofa_gemm_tc_rope.argtypes = [_P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _F, _P, _P, _P]
         lib.alofa_gemm_tc_splits.restype = _I
         lib.alofa_gemm_tc_splits.argtypes = [_I, _I]
         _libs["gemm_tc"] = lib
@@ -107,7 +107,9 @@ def _elementwise():
     if lib is None:
         lib = load_library("alofa_elementwise_bf16", ["kernels/elementwise_bf16.cu"])
         lib.alofa_norm_fused.restype = _I
-        lib.alofa_norm_fused.argtypes = [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P]
+        lib.alofa_norm_fused.argtypes = [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P, _P, _P]
+        lib.alofa_stream_settle.restype = _I
+        lib.alofa_stream_settle.argtypes = [_P, _P, _P, _P, _I, _P]
         lib.alofa_rope_store_fused.restype = _I
         lib.alofa_rope_store_fused.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]
         _libs["elementwise"] = lib
@@ -294,10 +296,10 @@ def gemm_tc_splits(k: int, splits: int) -> int:
     return _gemm_tc().alofa_gemm_tc_splits(k, splits)
 
 
-B_ROWS, B_MERGED_SPLITS = 0, 1
+B_ROWS, B_MERGED_SPLITS, B_NORMED = 0, 1, 2
 
 
-def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True, computed=None) -> bool:
+def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True, computed=None, acc=None) -> bool:
     """Tensor-core product ``out = x @ w.T`` (bf16 operands, fp32 sums) with
     the epilogue fused.  Returns False, having launched nothing, when the
     kernel does not take these sizes (depth not a multiple of 8, unaligned).
@@ -305,16 +307,32 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
     ``computed`` (residual products with ``bn`` = 16 only) replaces ``x`` by
     rows the kernel makes as it goes: ``(B_MERGED_SPLITS, partial_o,
     partial_ml, positions, heads, head_dim, window, split_keys)``, the
-    attention output of decode tokens whose key splits are not merged yet."""
+    attention output of decode tokens whose key splits are not merged yet; or,
+    for gated products, ``(B_NORMED, base, acc or None, gamma, eps, new_base,
+    zero or None)``: the RMSNorm of the residual stream ``base + acc``, which
+    is also written to ``new_base`` while ``zero`` is cleared.
+
+    ``acc`` (residual products, weights on M): the sums are added into this
+    int64 accumulator ``[tokens, features]`` (units of 2^-32) with atomic adds
+    instead of into ``out``; nothing else is written."""
     n = out.shape[1]
     rows_w = 2 * n if epi == EPI_GATED else n
     k = w.shape[1]
     m = out.shape[0]
     if w.shape[0] != rows_w or (x is not None and tuple(x.shape) != (m, k)) or (bias is not None and bias.shape[0] != rows_w):
         raise AlofaError("invalid_argument", "gemm sizes disagree", f"out={tuple(out.shape)} w={tuple(w.shape)} epi={epi}")
-    f32 = torch.float32
+    f32, i64 = torch.float32, torch.int64
     b_kind, b_src, b_ml, b_pos, heads, hd, window, split_keys = B_ROWS, None, None, None, 0, 0, 0, 0
-    if computed is not None:
+    n_acc = n_gamma = n_out = n_zero = None
+    n_eps = 0.0
+    if computed is not None and computed[0] == B_NORMED:
+        b_kind, base, acc_in, gamma, n_eps, new_base, zero = computed
+        if tuple(base.shape) != (m, k) or tuple(new_base.shape) != (m, k) or gamma.shape[0] != k:
+            raise AlofaError("invalid_argument", "normed operand sizes disagree", f"base={tuple(base.shape)} gamma={tuple(gamma.shape)} k={k}")
+        b_src, n_gamma, n_out = _dev(base, "base", f32), _dev(gamma, "gamma", f32), _dev(new_base, "new_base", f32)
+        n_acc = _dev(acc_in, "acc", i64) if acc_in is not None else None
+        n_zero = _dev(zero, "zero", i64) if zero is not None else None
+    elif computed is not None:
         b_kind, po, pml, positions, heads, hd, window, split_keys = computed
         b_src, b_ml, b_pos, window = _dev(po, "partial_o", f32), _dev(pml, "partial_ml", f32), _dev(positions, "positions", torch.int32), int(window or 0)
     elif x is None:
@@ -325,30 +343,44 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
         _dev(partial, "partial", f32) if partial is not None else None,
         m, n, k, epi, _is_bf16(out, "out"), bn, splits, 1 if reduce else 0,
         _dev(status, "status", torch.int32) if status is not None else None,
-        b_kind, b_src, b_ml, b_pos, heads, hd, window, split_keys, _stream(),
+        b_kind, b_src, b_ml, b_pos, heads, hd, window, split_keys,
+        _dev(acc, "acc", i64) if acc is not None else None, n_acc, n_gamma, float(n_eps), n_out, n_zero, _stream(),
     )
     if rc == 1:
         return False
     _done(rc, "gemm_tc", f"M={m} N={n} K={k} epi={epi} bn={bn} splits={splits}")
-    if splits > 1 and reduce and not _gemm_tc().alofa_gemm_tc_reduces_in_cluster(epi, bn, splits):
+    if splits > 1 and reduce and acc is None and b_kind != B_NORMED and not _gemm_tc().alofa_gemm_tc_reduces_in_cluster(epi, bn, splits):
         count_launches(1)  # the kernel that adds the split sums up
     return True
 
 
-def gemm_tc_rope(x, w, bias, q_out, k_cache, v_cache, slot_map, positions, cos_sin, nh: int, nkv: int, hd: int, splits: int, status=None) -> bool:
+def gemm_tc_rope(x, w, bias, q_out, k_cache, v_cache, slot_map, positions, cos_sin, nh: int, nkv: int, hd: int, splits: int, status=None, normed=None) -> bool:
     """q/k/v of up to 16 tokens in one kernel: ``x @ w.T + bias`` for the
     stacked weight [q; k; v] (``nkv`` = 0: q only), q and k rotated, q to
-    ``q_out``, k and v to their cache slots.  False, having launched nothing,
-    when the kernel does not take these sizes."""
-    bf, f32 = torch.bfloat16, torch.float32
-    t, k = x.shape
+    ``q_out``, k and v to their cache slots.  With ``normed`` = ``(base, acc or
+    None, gamma, eps, new_base, zero or None)`` the operand is not ``x`` (None
+    then) but the RMSNorm of the residual stream ``base + acc``, made in the
+    kernel; the stream is also written to ``new_base`` and ``zero`` cleared.
+    False, having launched nothing, when the kernel does not take these sizes."""
+    bf, f32, i64 = torch.bfloat16, torch.float32, torch.int64
+    t, k = (x.shape if normed is None else normed[0].shape)
     if t > 16 or 128 % hd or w.shape != ((nh + 2 * nkv) * hd, k):
         return False
+    n_base = n_acc = n_gamma = n_out = n_zero = None
+    n_eps = 0.0
+    if normed is not None:
+        base, acc_in, gamma, n_eps, new_base, zero = normed
+        if tuple(new_base.shape) != (t, k) or gamma.shape[0] != k:
+            raise AlofaError("invalid_argument", "normed operand sizes disagree", f"base={tuple(base.shape)} gamma={tuple(gamma.shape)}")
+        n_base, n_gamma, n_out = _dev(base, "base", f32), _dev(gamma, "gamma", f32), _dev(new_base, "new_base", f32)
+        n_acc = _dev(acc_in, "acc", i64) if acc_in is not None else None
+        n_zero = _dev(zero, "zero", i64) if zero is not None else None
     rc = _gemm_tc().alofa_gemm_tc_rope(
-        _dev(x, "x", bf), _dev(w, "w", bf), _dev(bias, "bias", f32) if bias is not None else None, t, k, _dev(q_out, "q_out", bf),
+        _dev(x, "x", bf) if x is not None else None, _dev(w, "w", bf), _dev(bias, "bias", f32) if bias is not None else None, t, k, _dev(q_out, "q_out", bf),
         _dev(k_cache, "k_cache", bf) if nkv else None, _dev(v_cache, "v_cache", bf) if nkv else None,
         _dev(slot_map, "slot_map", torch.int32) if nkv else None, _dev(positions, "positions", torch.int32), _dev(cos_sin, "cos_sin", f32),
-        nh, nkv, hd, splits, _dev(status, "status", torch.int32) if status is not None else None, _stream(),
+        nh, nkv, hd, splits, _dev(status, "status", torch.int32) if status is not None else None,
+        n_base, n_acc, n_gamma, float(n_eps), n_out, n_zero, _stream(),
     )
     if rc == 1:
         return False
@@ -391,23 +423,40 @@ def attention_combine(out, partial_o, partial_ml, positions, nh: int, hd: int, w
     _done(rc, "attention_combine")
 
 
-def norm_fused(out, h, weight, eps: float, rows=None, partial=None, splits: int = 0, bias=None) -> bool:
+def norm_fused(out, h, weight, eps: float, rows=None, partial=None, splits: int = 0, bias=None, base=None, acc=None, other=None) -> bool:
     """RMSNorm of rows of the fp32 stream ``h`` (vectorised; hidden % 4 == 0).
     With ``partial`` [splits, T, hidden] the pending partial sums (and bias)
-    are first added into ``h``.  Returns False when the size is not taken."""
+    are first added into ``h``.  With ``base`` the stream's values are read
+    from there (``h`` is written, complete), with ``acc`` (int64, units of
+    2^-32; every row, ``rows`` None) that accumulator is added on top and left
+    zero, as is ``other``.  Returns False when the size is not taken."""
     n, hidden = out.shape
     if hidden % 4:
         return False
-    f32 = torch.float32
+    f32, i64 = torch.float32, torch.int64
     rc = _elementwise().alofa_norm_fused(
         _dev(out, "out"), _dev(h, "h", f32), _dev(weight, "weight", f32), _dev(partial, "partial", f32) if partial is not None else None,
         _dev(bias, "bias", f32) if bias is not None else None, _dev(rows, "rows", torch.int32) if rows is not None else None,
-        n, h.shape[0], hidden, splits, float(eps), _is_bf16(out, "out"), _stream(),
+        n, h.shape[0], hidden, splits, float(eps), _is_bf16(out, "out"),
+        _dev(base, "base", f32) if base is not None else None, _dev(acc, "acc", i64) if acc is not None else None,
+        _dev(other, "other", i64) if other is not None else None, _stream(),
     )
     if rc == 1:
         return False
     _done(rc, "norm_fused")
     return True
+
+
+def stream_settle(h, base, acc, other=None) -> None:
+    """``h = base + acc`` (the residual stream of a small decode step brought
+    back to one fp32 tensor); ``acc`` and ``other`` (int64, units of 2^-32) are
+    left zero."""
+    f32, i64 = torch.float32, torch.int64
+    _done(
+        _elementwise().alofa_stream_settle(_dev(h, "h", f32), _dev(base, "base", f32), _dev(acc, "acc", i64),
+                                           _dev(other, "other", i64) if other is not None else None, h.numel(), _stream()),
+        "stream_settle",
+    )
 
 
 def rope_store_fused(q_out, k_cache, v_cache, qkv, partial, splits, bias, cos_sin, positions, slot_map, nh, nkv, hd, write_cache=True) -> None:

@@ -64,6 +64,19 @@ class Layout:
         return lay
 
 
+@dataclass
+class Pending:
+    """The residual stream ``h`` is not up to date in its own tensor: its last
+    complete value lies in ``base`` (``h`` itself or its alternate buffer), and
+    on top of it come the split sums a product left as planes (``partial``) or
+    the fixed-point accumulator number ``acc`` that products added into."""
+
+    h: torch.Tensor
+    base: torch.Tensor
+    partial: object = None
+    acc: int = None
+
+
 class StepContext:
     """Per-step batch description plus scratch allocation."""
 
@@ -104,30 +117,110 @@ class StepContext:
         self.capturing = False  # the step is being recorded as a CUDA graph: launch shapes must not depend on this step's lengths
 
         self.any_hot = True  # some wanted row samples with a positive temperature
-        self.pending = None  # (residual stream, Partial): sums a deferred product still owes it
+        self.pending = None  # a Pending: what the residual stream's own tensor still lacks
+        # Small decode steps keep the stream as base + fixed-point accumulator (see open_stream)
+        self.stream_acc = None  # int64 [2, rows, hidden], given by the step runner; both zero between steps
+        self._stream = None
+
+    # -- the residual stream ---------------------------------------------------------------------
+    # A product that adds into the stream may leave its split sums for the next reader to add
+    # (planes, ``set_pending``), and in decode steps of a few tokens it adds them into one of two
+    # 64-bit fixed-point accumulators instead (``accumulator_for`` / ``owe_accumulator``): integer
+    # adds give the same sum in any order.  The product that reads the stream next (q/k/v, gate/up)
+    # then makes its operand from base + accumulator, norm included, writes the sum to the stream's
+    # other buffer (which becomes the base) and clears the accumulator that was not read; readers
+    # that cannot do that get the stream settled in its own tensor first.
+    def open_stream(self, h) -> None:
+        """Called by the model once ``h`` exists: decode steps of up to 16
+        tokens in bfloat16 keep ``h`` as base + accumulator."""
+        acc = self.stream_acc
+        if acc is None or self.n_tokens > acc.shape[1] or h.shape[1] != acc.shape[2] or h.shape[1] % 8 or self.rt.dtype != torch.bfloat16:
+            return
+        self._stream = {"h": h, "alt": self.buf(tuple(h.shape), torch.float32), "acc": [acc[0, : self.n_tokens], acc[1, : self.n_tokens]], "next": 0, "unclean": set()}
+
+    def stream_of(self, h):
+        return self._stream if self._stream is not None and self._stream["h"] is h else None
+
+    def accumulator_for(self, h):
+        """The accumulator a product that adds into ``h`` should add into, or
+        None when the stream is kept whole (the product then adds in place or
+        leaves planes)."""
+        st = self.stream_of(h)
+        if st is None or (self.pending is not None and (self.pending.partial is not None or self.pending.acc is not None)):
+            return None
+        return st["acc"][st["next"]]
+
+    def owe_accumulator(self, h) -> None:
+        """A product has added into ``accumulator_for(h)``."""
+        st = self.stream_of(h)
+        base = self.pending.base if self.pending is not None else h
+        self.pending = Pending(h, base, None, st["next"])
+        st["unclean"].add(st["next"])
+
+    def stream_read(self, h, new_base, pend) -> None:
+        """A product has read the stream as base + accumulator and written the
+        sum to ``new_base``; it cleared the accumulator it did not read."""
+        st = self.stream_of(h)
+        if pend is not None and pend.acc is not None:
+            st["next"] = 1 - pend.acc
+            st["unclean"].discard(1 - pend.acc)
+        self.pending = Pending(h, new_base) if new_base is not h else None
+
+    def other_base(self, h, base):
+        st = self.stream_of(h)
+        return st["alt"] if base is h else h
 
     def set_pending(self, h, partial) -> None:
         """A product into the residual stream ``h`` left partial sums behind;
         the next reader of ``h`` adds them (norms do it while they read)."""
+        if self.pending is not None and self.pending.h is h and self.pending.partial is None and self.pending.acc is None:
+            self.pending = Pending(h, self.pending.base, partial)  # the base had moved, nothing else was owed
+            return
         self.flush_pending()
-        self.pending = (h, partial)
+        self.pending = Pending(h, h, partial)
 
     def take_pending(self, h):
-        """The partial sums owed to ``h``, handing over the duty to add them."""
-        if self.pending is not None and self.pending[0] is h:
-            partial = self.pending[1]
+        """What ``h`` still lacks (a :class:`Pending`), handing over the duty
+        to bring it up to date; None when it is complete."""
+        if self.pending is not None and self.pending.h is h:
+            pend = self.pending
             self.pending = None
-            return partial
+            return pend
         return None
 
-    def flush_pending(self) -> None:
-        """Add any owed partial sums into their residual stream now."""
-        if self.pending is not None:
-            from ..csrc import ops
+    def accumulators(self, h, pend):
+        """(the accumulator ``pend`` owes, the other one) as tensors, for a
+        reader that adds the first to the stream and leaves both zero."""
+        st = self.stream_of(h)
+        st["unclean"].clear()
+        return st["acc"][pend.acc], st["acc"][1 - pend.acc]
 
-            h, partial = self.pending
-            self.pending = None
-            ops.splitk_reduce(h, partial.sums, partial.bias, partial.splits, ops.EPI_RESIDUAL)
+    def flush_pending(self) -> None:
+        """Bring the residual stream up to date in its own tensor now."""
+        if self.pending is None:
+            return
+        from ..csrc import ops
+
+        pend = self.pending
+        self.pending = None
+        h = pend.h
+        if pend.acc is not None:
+            acc, other = self.accumulators(h, pend)
+            ops.stream_settle(h, pend.base, acc, other)
+        elif pend.base is not h:
+            h.copy_(pend.base)
+        if pend.partial is not None:
+            ops.splitk_reduce(h, pend.partial.sums, pend.partial.bias, pend.partial.splits, ops.EPI_RESIDUAL)
+
+    def close_stream(self) -> None:
+        """The step's last reader of the stream is done: what is still owed is
+        dropped, and an accumulator that nobody left zero is cleared (both are
+        zero between steps)."""
+        self.pending = None
+        if self._stream is not None:
+            for i in sorted(self._stream["unclean"]):
+                self._stream["acc"][i].zero_()
+            self._stream["unclean"].clear()
 
     def host_field(self, name: str) -> np.ndarray:
         at, count = self.layout.fields[name]

@@ -92,6 +92,12 @@ class StepRunner:
         vocab_bytes = 4 * model.spec.vocab_size
         self.arena = Arena(self.rt.device, max_step_tokens * step_row + max_requests * vocab_bytes * 5 // 4 + (1 << 20),
                            max_step_tokens * layer_row * 5 // 4 + (4 << 20))
+        # Decode steps of up to 16 tokens keep the residual stream as a base tensor plus one of two
+        # fixed-point accumulators that the products add into (see StepContext.open_stream); both are
+        # zero between steps.  ALOFA_STREAM_ACC=0 keeps the stream in one tensor, as larger steps do.
+        self._stream_acc = None
+        if on_gpu and self.rt.dtype == torch.bfloat16 and os.environ.get("ALOFA_STREAM_ACC", "1") != "0":
+            self._stream_acc = torch.zeros((2, 16, model.spec.hidden_size), dtype=torch.int64, device=self.rt.device)
         self._layouts = {}
         self.cuda_graphs = cuda_graphs and on_gpu and model.graph_safe()
         self._graphs = {}  # decode steps by batch size; steps with prompt portions by (tokens, requests, wanted rows)
@@ -191,6 +197,7 @@ class StepRunner:
         ctx = StepContext(self.rt, layout, self._dev_meta, host, self._group_shapes, self._status, self.arena)
         self.arena.begin_step()
         ctx.fed_tokens = self._fed if self.feeds_tokens else None
+        ctx.stream_acc = self._stream_acc
         ctx.max_q_len, ctx.max_kv_len = max_q, max_kv
         ctx.decode_only = max_q == 1
         ctx.max_context = self.max_tokens
@@ -335,6 +342,8 @@ class StepRunner:
         if code == 0:
             return
         self._status.zero_()
+        if self._stream_acc is not None:
+            self._stream_acc.zero_()  # a kernel that gave up may have left the step half done
         if code == 2:
             raise AlofaError("state", "a kernel gave up waiting on its own pipeline")
         raise AlofaError("out_of_range", "a kernel met a token id outside the vocabulary")

@@ -21,7 +21,7 @@ from ..csrc import ops
 from ..errors import AlofaError
 from . import fast_linear
 from .base import PagedKV, Part, TensorSpec, as_float32_vector, build_part, register_part
-from .linear import RESIDUAL, STORE, Linear, MergedSplits
+from .linear import RESIDUAL, STORE, Linear, MergedSplits, add_into_stream
 
 
 class GQAttention(Part):
@@ -87,13 +87,14 @@ class GQAttention(Part):
         self.out = Linear(state[pre + "o_proj.weight"], ob, RESIDUAL)
         self.position.load(state)
 
+    takes_normed_rows = True  # ``x`` may be rows still to be made: the q/k/v kernel of a few tokens folds the norm in
+
     def forward(self, ctx, x, h, cache, writes=True):
         """h += Attention(x).  ``cache`` is the layer cache (k, v, group)."""
         n = x.shape[0]
         dt = self.rt.dtype
         group = ctx.groups[cache.group]
         nkv_in = self.nkv if writes else 0
-        qkv = ctx.buf((n, (self.nh + 2 * nkv_in) * self.hd), dt)
         table, rot = self.position.rotary_table()
         custom = getattr(self.position, "apply", None)
         # the vectorised rotate-and-store: bf16, the whole head rotated, head size a multiple of 16
@@ -105,17 +106,29 @@ class GQAttention(Part):
         # and only while a CTA then has a few k-slices: on deep products (3,584 wide) the cluster measured slower
         depth_splits = max(1, min(8, fast_linear.SMS // -(-lin.weight.shape[0] // 128)))
         shallow = -(-(-(-self.hidden // fast_linear.K_SLICE)) // depth_splits) <= 4
-        if vectorised and shallow and n <= 16 and lin.weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and ops.gemm_tc_rope(
-            x, lin.weight, lin.bias, q, cache.k, cache.v, group.slot_map, ctx.positions, table, self.nh, nkv_in, self.hd, depth_splits, ctx.status
-        ):
-            owed = None
-        else:
+        one_kernel = vectorised and shallow and n <= 16 and lin.weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+        lazy = None if isinstance(x, torch.Tensor) else x
+        done = False
+        if lazy is not None:
+            if one_kernel and lazy.fits_kernel():
+                normed = lazy.computed()  # the norm folded into the q/k/v kernel
+                done = ops.gemm_tc_rope(None, lin.weight, lin.bias, q, cache.k, cache.v, group.slot_map, ctx.positions, table, self.nh, nkv_in, self.hd,
+                                        depth_splits, ctx.status, normed=normed[1:])
+                if done:
+                    lazy.done(normed)
+                else:
+                    lazy.undo()
+            if not done:
+                x = lazy.rows()
+        if not done and one_kernel:
+            done = ops.gemm_tc_rope(x, lin.weight, lin.bias, q, cache.k, cache.v, group.slot_map, ctx.positions, table, self.nh, nkv_in, self.hd,
+                                    depth_splits, ctx.status)
+        if not done:
+            qkv = ctx.buf((n, (self.nh + 2 * nkv_in) * self.hd), dt)
             owed = lin(qkv, x, defer=vectorised, buf=ctx.buf)
             self._rotate_and_store(ctx, q, qkv, owed, cache, group, table, rot, custom, vectorised, nkv_in, writes)
         attn = self.attend(ctx, q, cache, group)
-        owed = self.out(h, attn, defer=True, buf=ctx.buf)
-        if owed is not None:
-            ctx.set_pending(h, owed)
+        add_into_stream(ctx, self.out, h, attn)
 
     def _rotate_and_store(self, ctx, q, qkv, owed, cache, group, table, rot, custom, vectorised, nkv_in, writes):
         n = q.shape[0]

@@ -43,15 +43,19 @@ class PrenormResidual(Part):
 
     absorbs_pending = True  # its norms add partial sums owed to h; other readers get them flushed first
 
-    def _norm(self, norm, ctx, h):
+    def _norm(self, norm, ctx, h, reader):
         if not getattr(norm, "absorbs_pending", False):
             ctx.flush_pending()
+            return norm.forward(ctx, h)
+        # a reader that says so may get rows still to be made (the norm folded into its own product)
+        if getattr(reader, "takes_normed_rows", False) and getattr(norm, "gives_normed_rows", False):
+            return norm.forward(ctx, h, lazy=True)
         return norm.forward(ctx, h)
 
     def forward(self, ctx, h, cache, writes=True):
-        x = self._norm(self.mixer_norm, ctx, h)
+        x = self._norm(self.mixer_norm, ctx, h, self.mixer)
         self.mixer.forward(ctx, x, h, cache, writes)
-        x = self._norm(self.feed_forward_norm, ctx, h)
+        x = self._norm(self.feed_forward_norm, ctx, h, self.feed_forward)
         self.feed_forward.forward(ctx, x, h)
 
 

@@ -68,7 +68,9 @@ def plan(linear):
     gated = linear.epi == ops.EPI_GATED
     n_acc = 2 if gated else 1
 
-    def run(out, x, defer: bool = False, buf=None):
+    def run(out, x, defer: bool = False, buf=None, acc=None):
+        from .linear import ACCUMULATED
+
         tokens = x.shape[0]
         if tokens == 0:
             return True
@@ -80,24 +82,36 @@ def plan(linear):
         computed = None
         if lazy is not None:
             # Rows still to be made.  The weights-on-M kernel makes them as it loads, a k-slice at a
-            # time and each a trip to L2: worth it while a CTA has a slice or two, else they are made first.
+            # time and each a trip to L2: worth it while a CTA has a few slices, else they are made first.
             per_cta = -(-(-(-depth // K_SLICE)) // splits)
-            if bn == 16 and linear.epi == ops.EPI_RESIDUAL and depth % 8 == 0 and per_cta <= 2 and lazy.fits_kernel():
+            kind = getattr(lazy, "kind", "merged")
+            if kind == "merged" and bn == 16 and linear.epi == ops.EPI_RESIDUAL and per_cta <= 2 and lazy.fits_kernel():
                 computed = lazy.computed()
+            elif kind == "normed" and bn == 16 and gated and splits <= 8 and per_cta <= 6 and lazy.fits_kernel():
+                computed = lazy.computed()  # the norm folded into a gated product whose splits are one cluster
             else:
                 x = lazy.rows()
         if x is not None and (x.data_ptr() % 16 or not x.is_contiguous()):
             return False
+        normed = computed is not None and computed[0] == ops.B_NORMED
         partial = None
-        if splits > 1:
+        if splits > 1 and acc is None and not normed:
             shape = (splits * n_acc, tokens, linear.out_features)
             partial = buf(shape, torch.float32) if buf is not None else torch.empty(shape, dtype=torch.float32, device=w.device)
-        deferred = defer and splits > 1 and n_acc == 1
+        deferred = defer and splits > 1 and n_acc == 1 and acc is None
         dst = partial[0] if deferred else out  # a deferred product writes partial sums only
-        if not ops.gemm_tc(dst, x, w, linear.bias, linear.epi, bn, splits, partial, reduce=not deferred, computed=computed):
-            if computed is not None:
+        if not ops.gemm_tc(dst, x, w, linear.bias, linear.epi, bn, splits, partial, reduce=not deferred, computed=computed, acc=acc):
+            if normed:
+                lazy.undo()
+                return run(out, lazy.rows(), defer, buf)
+            if computed is not None or acc is not None:
                 raise AlofaError("state", "the tensor-core product refused an operand it had accepted")
             return False
+        if normed:
+            lazy.done(computed)
+        if acc is not None:
+            return ACCUMULATED
         return Partial(partial, splits, linear.bias) if deferred else True
 
+    run.weights_on_m = lambda tokens: _tile(tokens, linear.out_features, gated) > 0
     return run

@@ -9,7 +9,7 @@ import torch
 
 from ..errors import AlofaError
 from .base import Part, TensorSpec, register_part
-from .linear import GATED, RESIDUAL, Linear
+from .linear import GATED, RESIDUAL, Linear, add_into_stream
 
 
 class GatedMLP(Part):
@@ -41,12 +41,12 @@ class GatedMLP(Part):
     def scratch_row_bytes(self) -> int:
         return 4 * self.inter + 2 * 4 * self.hidden  # the activation, and the down product's depth split in two
 
+    takes_normed_rows = True  # ``x`` may be rows still to be made: the gate/up product folds the norm in
+
     def forward(self, ctx, x, h):
         act = ctx.buf((x.shape[0], self.inter), self.rt.dtype)
         self.gate_up(act, x, buf=ctx.buf)
-        owed = self.down(h, act, defer=True, buf=ctx.buf)
-        if owed is not None:
-            ctx.set_pending(h, owed)
+        add_into_stream(ctx, self.down, h, act)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

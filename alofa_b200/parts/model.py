@@ -56,6 +56,7 @@ class Model:
         """Logits (fp32) at ``ctx.logit_rows`` for the step's tokens (None when
         no row is wanted; the final norm and the head run on wanted rows only)."""
         h = ctx.buf((ctx.n_tokens, self.spec.hidden_size), torch.float32)
+        ctx.open_stream(h)
         self.embedding.forward(ctx, h)
         for i, (layer, cache) in enumerate(self.run):
             block = self.layers[layer]
@@ -65,12 +66,12 @@ class Model:
             block.forward(ctx, h, caches.get(cache), writes=(cache == i))
         ctx.end_layers()
         if ctx.n_out == 0:  # a prompt portion whose logits nobody wants
-            ctx.pending = None
+            ctx.close_stream()
             return None
         if not getattr(self.final_norm, "absorbs_pending", False):
             ctx.flush_pending()
         x = self.final_norm.forward(ctx, h, ctx.logit_rows)
-        ctx.pending = None
+        ctx.close_stream()
         return self.head.forward(ctx, x)
 
 def expected_tensors(spec: ModelSpec) -> dict:
