@@ -298,7 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   bool epilogue_ok = false;
   float* pushed = reinterpret_cast<float*>(tiles + (size_t)stages * STAGE_BYTES);
   float* rope_xchg = pushed + (CLUSTER ? (size_t)(gridDim.z - 1) * N_ACC * BN * 128 : 0);  // EPI_ROPE: [16 tokens][128 features]
-  float* row_ss = rope_xchg + (EPI == EPI_ROPE ? 16 * 128 : 0);  // MODE_NORMED: [8 ranks][16 tokens] sums of squares, in the first CTA
+  float* row_ss = rope_xchg + (EPI == EPI_ROPE ? 16 * 128 : 0);  // MODE_NORMED: [8 ranks][16 tokens] sums of squares, then the 16 factors, in the first CTA
   auto epilogue = [&](bool with_remote) {
     const int q = warp & 3;
     const int f = f0 + q * 32 + lane;
@@ -309,12 +309,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // square + eps) comes from the sums of squares all CTAs of the cluster sent to the first
     float rstd[NORMED ? 16 : 1];
     if constexpr (NORMED) {
+      if (!push) {
+        // one thread per token adds the CTAs' sums up (in rank order) and takes the root; the others read the 16 factors
+        // (every thread adding them up for itself cost 5 us: 16 x 7 dependent reads of shared memory)
+        const int et = threadIdx.x - 64;
+        if (et < 16) {
+          float part[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        if (push) break;
-        float ss = 0.f;
-        for (uint32_t z = 0; z < gridDim.z; ++z) ss += row_ss[z * 16 + j];
-        rstd[j] = 1.0f / sqrtf(ss / (float)args.K + args.n_eps);
+          for (int z = 0; z < 8; ++z) part[z] = z < (int)gridDim.z ? row_ss[z * 16 + et] : 0.f;
+          float ss = 0.f;
+#pragma unroll
+          for (int z = 0; z < 8; ++z) ss += part[z];
+          row_ss[8 * 16 + et] = 1.0f / sqrtf(ss / (float)args.K + args.n_eps);
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");  // the four epilogue warps
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const float4 f = *reinterpret_cast<const float4*>(row_ss + 8 * 16 + j);
+          rstd[j] = f.x, rstd[j + 1] = f.y, rstd[j + 2] = f.z, rstd[j + 3] = f.w;
+        }
       }
     }
     float bias0 = 0.f, bias1 = 0.f;
@@ -351,11 +364,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       if constexpr (CLUSTER) {
         const int row = q * 32 + lane;
+        const int live = min(16, args.T - (t0 + c0));  // tokens of this group that exist: the others are neither sent nor added
         if (push) {  // this CTA's sums into the first CTA's shared memory; nothing goes to global memory
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            store_remote_f32(smem_u32(pushed + (((rank - 1) * N_ACC + 0) * BN + c0 + j) * 128 + row), 0, __uint_as_float(r0[j]));
-            if (N_ACC == 2) store_remote_f32(smem_u32(pushed + (((rank - 1) * N_ACC + 1) * BN + c0 + j) * 128 + row), 0, __uint_as_float(r1[j]));
+            if (j < live) {
+              store_remote_f32(smem_u32(pushed + (((rank - 1) * N_ACC + 0) * BN + c0 + j) * 128 + row), 0, __uint_as_float(r0[j]));
+              if (N_ACC == 2) store_remote_f32(smem_u32(pushed + (((rank - 1) * N_ACC + 1) * BN + c0 + j) * 128 + row), 0, __uint_as_float(r1[j]));
+            }
           }
           continue;
         }
@@ -363,8 +379,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           for (uint32_t z = 1; z < gridDim.z; ++z) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + pushed[(((z - 1) * N_ACC + 0) * BN + c0 + j) * 128 + row]);
-              if (N_ACC == 2) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + pushed[(((z - 1) * N_ACC + 1) * BN + c0 + j) * 128 + row]);
+              if (j < live) {
+                r0[j] = __float_as_uint(__uint_as_float(r0[j]) + pushed[(((z - 1) * N_ACC + 0) * BN + c0 + j) * 128 + row]);
+                if (N_ACC == 2) r1[j] = __float_as_uint(__uint_as_float(r1[j]) + pushed[(((z - 1) * N_ACC + 1) * BN + c0 + j) * 128 + row]);
+              }
             }
           }
         }
@@ -1142,7 +1160,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
       const bool normed = args.b_kind == B_NORMED;
       if (normed && (BN != 16 || grid.y != 1 || splits > 8)) return ALOFA_ERR_ARGUMENT;
       // room behind the ring for the accumulators the other CTAs of a cluster push, and the rows' sums of squares
-      const size_t pushed = (size_t)(splits - 1) * N_ACC * BN * 128 * sizeof(float) + XCHG + (normed ? 8 * 16 * sizeof(float) : 0);
+      const size_t pushed = (size_t)(splits - 1) * N_ACC * BN * 128 * sizeof(float) + XCHG + (normed ? 9 * 16 * sizeof(float) : 0);
       int cstages = (int)((200 * 1024 - pushed) / STAGE);
       if (cstages > 12) cstages = 12;
       if (cstages < 2) return ALOFA_ERR_ARGUMENT;
