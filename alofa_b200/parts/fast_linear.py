@@ -17,8 +17,18 @@ import torch
 from ..csrc import ops
 from ..errors import AlofaError
 
-SMS = 148
+SMS = 148  # streaming multiprocessors the grids are sized for: a B200's, replaced by the device's own count at first use
 K_SLICE = 64
+_asked_device = False
+
+
+def _sms_of_device(device) -> None:
+    """The tile and split choices below fill the GPU once: they go by the
+    number of SMs the device reports."""
+    global SMS, _asked_device
+    if not _asked_device and device.type == "cuda":
+        _asked_device = True
+        SMS = torch.cuda.get_device_properties(device).multi_processor_count
 
 
 def _tile(tokens: int, features: int, gated: bool) -> int:
@@ -65,6 +75,7 @@ def plan(linear):
     depth = linear.in_features
     if depth % 8 or w.data_ptr() % 16:
         return None
+    _sms_of_device(w.device)
     gated = linear.epi == ops.EPI_GATED
     n_acc = 2 if gated else 1
 

@@ -8,7 +8,10 @@ import pytest
 from alofa_b200.parts import fast_linear as fl
 
 
-SIZES = [(896, 896), (1152, 896), (9728 // 2, 896), (896, 4864), (151936, 896), (3584, 3584), (18944, 3584), (3584, 18944), (379, 96), (131, 512)]
+SIZES = [(896, 896), (1152, 896), (9728 // 2, 896), (896, 4864), (151936, 896),  # the 0.5B shape
+         (1536, 1536), (2048, 1536), (8960, 1536), (1536, 8960),  # the 1.5B shape
+         (3584, 3584), (4608, 3584), (18944, 3584), (3584, 18944), (152064, 3584),  # the 7B shape
+         (379, 96), (131, 512)]
 TOKENS = [1, 7, 8, 16, 17, 32, 33, 64, 65, 128, 300, 2048]
 
 

@@ -105,3 +105,42 @@ def test_the_benchmarked_prompt_step_against_plain(shaped, dtype):
     runner.check_status()
     assert np.abs(got - want).max() <= bound, f"{dtype} portions of 512: {np.abs(got - want).max():.3e} > {bound:.3e}"
     assert (got.argmax(axis=1) == want.argmax(axis=1)).all()
+
+
+def test_steps_allocate_nothing(shaped):
+    """Every buffer a step needs comes from the runner's arena: once a step of
+    a shape has run, prompt steps, mixed steps and decode steps leave the
+    device memory the tensor library holds exactly as it was."""
+    from alofa_b200.engine.loading import compute_dtype
+    from alofa_b200.engine.step import StepEntry, StepRunner
+    from alofa_b200.models.qwen2 import build_spec
+    from alofa_b200.parts.base import Runtime
+    from alofa_b200.parts.model import Model
+    from alofa_b200.weights.loader import load_state
+
+    cfg, state, toks, _ = shaped
+    model = Model(build_spec(cfg), Runtime(torch.device("cuda"), compute_dtype("bfloat16")))
+    model.load(load_state(model.tensors(), state, model.rt.dtype, model.rt.device))
+    runner = StepRunner(model, block_size=64, num_pages=16, max_requests=4, max_tokens=512, max_step_tokens=256, cuda_graphs=False)
+    a, b = toks["a"], toks["b"]
+
+    def steps():
+        sa, sb = runner.admit(1), runner.admit(2)
+        runner.forward([StepEntry(sa, a[:130], [129])])
+        runner.forward([StepEntry(sa, a[130:131], [0]), StepEntry(sb, b[:67], [66])])
+        for i in range(131, 136):
+            runner.forward([StepEntry(sa, a[i : i + 1], [0]), StepEntry(sb, b[i - 64 : i - 63], [0])])
+        runner.release(sa)
+        runner.release(sb)
+
+    steps()  # kernels loaded, the arena grown to what these shapes need
+    torch.cuda.synchronize()
+    grown = runner.arena.grown
+    before = torch.cuda.memory_allocated()
+    peak = torch.cuda.max_memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
+    steps()
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before and torch.cuda.max_memory_allocated() == before
+    assert runner.arena.grown == grown
+    runner.check_status()
