@@ -128,8 +128,8 @@ def test_steps_allocate_nothing(shaped):
         sa, sb = runner.admit(1), runner.admit(2)
         runner.forward([StepEntry(sa, a[:130], [129])])
         runner.forward([StepEntry(sa, a[130:131], [0]), StepEntry(sb, b[:67], [66])])
-        for i in range(131, 136):
-            runner.forward([StepEntry(sa, a[i : i + 1], [0]), StepEntry(sb, b[i - 64 : i - 63], [0])])
+        for k in range(3):  # both decode, three steps
+            runner.forward([StepEntry(sa, a[131 + k : 132 + k], [0]), StepEntry(sb, b[67 + k : 68 + k], [0])])
         runner.release(sa)
         runner.release(sb)
 
