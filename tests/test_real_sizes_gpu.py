@@ -144,3 +144,38 @@ def test_steps_allocate_nothing(shaped):
     assert torch.cuda.memory_allocated() == before and torch.cuda.max_memory_allocated() == before
     assert runner.arena.grown == grown
     runner.check_status()
+
+
+def test_small_decode_steps_give_the_same_bits_every_run(shaped):
+    """Eight requests decoded together through the five-kernel layer, whose
+    residual products add their split sums with atomic integer adds in
+    whatever order their CTAs finish: two runs from the same state must give
+    the same logits bit for bit, and the accumulators are zero between steps."""
+    from alofa_b200.engine.loading import compute_dtype
+    from alofa_b200.engine.step import StepEntry, StepRunner
+    from alofa_b200.models.qwen2 import build_spec
+    from alofa_b200.parts.base import Runtime
+    from alofa_b200.parts.model import Model
+    from alofa_b200.weights.loader import load_state
+
+    cfg, state, _, _ = shaped
+    model = Model(build_spec(cfg), Runtime(torch.device("cuda"), compute_dtype("bfloat16")))
+    model.load(load_state(model.tensors(), state, model.rt.dtype, model.rt.device))
+    rng = np.random.default_rng(11)
+    prompts = [[int(t) for t in rng.integers(0, 151936, int(n))] for n in rng.integers(20, 200, 8)]
+    feed = rng.integers(0, 151936, size=(6, 8))
+    runs = []
+    for graphs in (True, True, False):
+        runner = StepRunner(model, block_size=64, num_pages=40, max_requests=8, max_tokens=512, max_step_tokens=256, cuda_graphs=graphs)
+        assert runner._stream_acc is not None
+        slots = [runner.admit(i) for i in range(8)]
+        for s, p in zip(slots, prompts):
+            runner.forward([StepEntry(s, p, [])])
+        rows = []
+        for step in feed:
+            rows.append(runner.forward([StepEntry(s, [int(t)], [0]) for s, t in zip(slots, step)]).clone())
+            assert int(runner._stream_acc.abs().sum()) == 0, "an accumulator was left with a value after the step"
+        runner.check_status()
+        runs.append(torch.stack(rows))
+    assert torch.equal(runs[0], runs[1]), "two runs of the same steps differ"
+    assert torch.equal(runs[0], runs[2]), "graph replay and plain launches differ"
