@@ -1217,7 +1217,16 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
   // other keeps the tensor cores busy.  One token tile (decode): the CTAs are
   // few and each streams its weights once, so the ring is made as deep as
   // shared memory allows to keep many loads in flight.
-  const size_t budget = args.T > 128 ? 108 * 1024 : 200 * 1024;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sm_count = 1;
+  }
+  dim3 grid((args.N + FEATS - 1) / FEATS, (args.T + 127) / 128, splits);
+  // A grid that does not fill the GPU once (the narrow q/k/v and output products of a prompt portion) has an SM
+  // to each CTA anyway: the deep ring then, or the CTA waits on the latency of three stages in flight.
+  const bool one_wave = (long long)grid.x * grid.y * grid.z <= sm_count;
+  const size_t budget = (args.T > 128 && !one_wave) ? 108 * 1024 : 200 * 1024;
   int stages = (int)(budget / STAGE);
   if (stages > 12) stages = 12;
   if (stages < 2) stages = 2;
@@ -1229,7 +1238,6 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
     prefer_max_shared(gemm_tc_tokens_kernel<BNF, EPI>);
     configured = true;
   }
-  dim3 grid((args.N + FEATS - 1) / FEATS, (args.T + 127) / 128, splits);
   if (BNF == 256 && splits == 1 && (args.N & 3) == 0 && args.K <= 2048) {
     // More tiles than SMs and a shallow depth, where a tile's epilogue is a large share of its
     // time: one resident CTA per SM works through the tiles, epilogues beside MMAs.  (Deep
