@@ -21,6 +21,23 @@ template <typename T> __device__ __forceinline__ T from_f(float x);
 template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
 template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16_rn(x); }
 
+// The residual stream of a small decode step may stand as an fp32 base plus a 64-bit fixed-point
+// accumulator in units of 2^-32 (products add their split sums into it with atomic integer adds, whose
+// result does not depend on their order).  base + acc in fp32: the accumulator is split into the
+// nearest whole number (exact in fp32 below 2^24) and a signed fraction in [-1/2, 1/2); the whole part
+// is added to the base first, the fraction after.  While the accumulator is below 1/2 in size (the
+// usual case) the whole part is zero and the sum is rounded once, up to the fraction's own 2^-26;
+// otherwise twice, which keeps it within two units in the last place of max(1, |sum|).  The result
+// is the same for the same inputs wherever it is computed.  (Double arithmetic would round once, but
+// 64-bit conversions and adds run at a few per clock per SM here and cost the product that reads
+// the stream 0.3 us per k-slice.)
+constexpr float STREAM_SCALE = 4294967296.0f;  // 2^32
+__device__ __forceinline__ float stream_add(float base, long long acc) {
+  const int whole = (int)((acc + 0x80000000ll) >> 32);
+  const int fraction = (int)(unsigned)(acc & 0xffffffffll);  // acc == whole * 2^32 + fraction
+  return (base + (float)whole) + (float)fraction * (1.0f / 4294967296.0f);
+}
+
 // Sum over a warp in a fixed butterfly order; every lane gets the result.
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

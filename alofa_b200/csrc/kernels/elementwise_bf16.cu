@@ -36,16 +36,15 @@ __device__ __forceinline__ void add_splits(float4& v, const float4* p, int z0, i
 // The residual stream of a decode step of a few tokens may stand as a base tensor plus a
 // 64-bit fixed-point accumulator (units of 2^-32) into which the products that add to the
 // stream sent their split sums with atomic adds: integer addition does not depend on the
-// order of arrival, so the sum is the same every run, and it is rounded to fp32 once, here
-// or in the product that reads the stream next (gemm_tc.cu, B_NORMED).
-constexpr float STREAM_SCALE = 4294967296.0f;
+// order of arrival, so the sum is the same every run; base + accumulator is taken in fp32
+// (stream_add in common.cuh), here or in the product that reads the stream next (gemm_tc.cu,
+// B_NORMED).
 __device__ __forceinline__ float4 stream_value(float4 v, const longlong2* acc2) {
   const longlong2 a = acc2[0], b = acc2[1];
-  // base and accumulator are added in double (exact for sums below 2^21) and rounded to fp32 once
-  v.x = (float)((double)v.x + (double)a.x * (1.0 / 4294967296.0));
-  v.y = (float)((double)v.y + (double)a.y * (1.0 / 4294967296.0));
-  v.z = (float)((double)v.z + (double)b.x * (1.0 / 4294967296.0));
-  v.w = (float)((double)v.w + (double)b.y * (1.0 / 4294967296.0));
+  v.x = stream_add(v.x, a.x);
+  v.y = stream_add(v.y, a.y);
+  v.z = stream_add(v.z, b.x);
+  v.w = stream_add(v.w, b.y);
   return v;
 }
 

@@ -42,7 +42,6 @@
 
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED = 2, EPI_ROPE = 3 };  // EPI_ROPE: weights-on-M tiles of 16 tokens only
 enum { B_ROWS = 0, B_MERGED_SPLITS = 1, B_NORMED = 2 };
-constexpr float STREAM_SCALE = 4294967296.0f;  // units of the residual accumulator: 2^-32
 
 constexpr int BM = 128;        // features per CTA (UMMA M)
 constexpr int BK = 64;         // k-slice: 64 bf16 = one 128-byte swizzle row
@@ -578,7 +577,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (live && args.n_acc) {
             const long long w8[8] = {a[b][0].x, a[b][0].y, a[b][1].x, a[b][1].y, a[b][2].x, a[b][2].y, a[b][3].x, a[b][3].y};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = (float)((double)v[j] + (double)w8[j] * (1.0 / 4294967296.0));
+            for (int j = 0; j < 8; ++j) v[j] = stream_add(v[j], w8[j]);
           }
           if (live && writes_stream) {
             const size_t e = (size_t)t * args.K + k;

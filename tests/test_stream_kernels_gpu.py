@@ -74,11 +74,26 @@ def test_output_product_merges_key_splits_into_the_accumulator(ops):
     assert_close(acc.cpu().numpy() / SCALE, plain.linear(rounded(merged, BF16), w), 6e-3, "merged splits into the accumulator")
 
 
+def stream_sum(base, owed):
+    """base + accumulator as the kernels take it (common.cuh, stream_add): the
+    accumulator split into the nearest whole number and a signed fraction, the
+    whole part added to the base first, the fraction after, all in fp32; the
+    result as float64."""
+    acc = np.rint(np.asarray(owed, dtype=np.float64) * SCALE).astype(np.int64)
+    whole = (acc + (1 << 31)) >> 32
+    fraction = (acc - (whole << 32)).astype(np.int32).astype(np.float32) * np.float32(1.0 / SCALE)
+    return ((np.asarray(base, dtype=np.float32) + whole.astype(np.float32)) + fraction).astype(np.float64)
+
+
 def stream_inputs(rng, t, k, with_acc):
     base = rng.normal(size=(t, k)).astype(np.float32)
     owed = rng.normal(size=(t, k)) * 0.3 if with_acc else np.zeros((t, k))
     gamma = (1 + 0.1 * rng.normal(size=k)).astype(np.float32)
-    stream = (base.astype(np.float64) + np.rint(owed * SCALE) / SCALE).astype(np.float32).astype(np.float64)
+    stream = stream_sum(base, owed)
+    exact = base.astype(np.float64) + np.rint(owed * SCALE) / SCALE
+    small = np.abs(owed) < 0.49
+    assert (np.abs(stream - exact)[small] <= (2.0 ** -24 * np.maximum(1.0, np.abs(exact)) + 2.0 ** -26)[small]).all()  # rounded once, and the fraction's own rounding
+    assert (np.abs(stream - exact) <= 2.0 ** -22 * np.maximum(1.0, np.abs(exact))).all()  # two roundings where the accumulator has a whole part
     return base, owed, gamma, stream
 
 
@@ -103,7 +118,7 @@ def test_gated_product_folds_the_norm_in(ops, t, n, k, splits, with_acc):
     assert ops.gemm_tc(out, None, dev(w, BF16), None, ops.EPI_GATED, 16, splits, None, computed=computed)
     assert_close(out.float().cpu(), want, 6e-3, "gated product of the normed stream")
     assert_close(out.float().cpu(), want_exact, 2e-2, "against the norm applied before rounding")
-    assert np.array_equal(new_base.cpu().numpy().astype(np.float64), stream), "the stream's new base is base + accumulator, rounded once"
+    assert np.array_equal(new_base.cpu().numpy().astype(np.float64), stream), "the stream's new base is base + accumulator"
     assert int(other.abs().sum()) == 0, "the accumulator that was not read is cleared"
     if with_acc:
         assert torch.equal(acc, acc_of(owed)), "the accumulator that was read is left as it was"
