@@ -321,24 +321,30 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
 
 // ---------------------------------------------------------------------------
 // Decode tokens, keys spread over the warps.  One CTA owns one (request, KV
-// head, split of 256 keys); its four warps each take one 64-key block of the
-// split, all against the same 16 query rows (the g <= 16 heads of the group,
-// padded), so the four blocks are fetched and processed side by side instead
-// of one after the other.  The warps' (output, maximum, sum) triples are merged
-// through shared memory in warp order, and the split's triple goes to the
-// partial buffers for attention_combine_kernel (or, with a single split,
-// straight to the output).
+// head, split of split_keys keys); the split's 64-key blocks are dealt to its
+// warps in turn (block b of the split to warp b % WARPS), all against the same
+// 16 query rows (the g <= 16 heads of the group, padded), so that WARPS blocks
+// are fetched and processed side by side.  A warp that has more than one block
+// keeps one key tile and one value tile: the next block's keys are asked for as
+// soon as the scores of this one are taken, its values as soon as this block's
+// have been multiplied in, so the copies run behind the softmax and the
+// products and the warps of an SM fall out of step with one another instead of
+// all loading, then all computing.  The warps' (output, maximum, sum) triples
+// are merged through shared memory in warp order, and the split's triple goes
+// to the partial buffers for attention_combine_kernel (or, with a single
+// split, straight to the output).
 // ---------------------------------------------------------------------------
-// WARPS warps, one 64-key block each: a split is WARPS * 64 keys.  With TMA (pages
-// that hold whole 64-key blocks, head size 64 or 128) a warp's block arrives by two
-// bulk tensor copies - keys and values, 128-byte swizzled - issued by one lane and
-// awaited on an mbarrier; else by 16-byte cp.async copies into padded tiles.
+// With TMA (pages that hold whole 64-key blocks, head size 64 or 128) a block
+// arrives by bulk tensor copies - keys and values, 128-byte swizzled, each on
+// its own mbarrier of the warp - issued by one lane; else by 16-byte cp.async
+// copies into padded tiles, one block after the other.
 constexpr int TILE_BYTES_TMA = BLOCK_N * HD * 2;  // one dense tile
 
-template <int WARPS, bool TMA>
+// LONG: splits of more than one block per warp; without it a warp's keys and values come on one
+// barrier and nothing is refilled.
+template <int WARPS, bool TMA, bool LONG>
 __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const AttnParams p, const __grid_constant__ CUtensorMap map_k,
                                                                       const __grid_constant__ CUtensorMap map_v) {
-  constexpr int DECODE_SPLIT_KEYS = WARPS * BLOCK_N;
   constexpr int THREADS = WARPS * 32;
   constexpr int TILE_ELEMS = TMA ? BLOCK_N * HD : BLOCK_N * ROW;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -349,11 +355,12 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   // the merge buffers reuse the key tiles once every warp is done with them
   float* merge_o = reinterpret_cast<float*>(k_tiles);     // [WARPS][16][MERGE_ROW]
   float* merge_ml = merge_o + WARPS * 16 * MERGE_ROW;     // [WARPS][16][2]
-  __shared__ uint64_t tile_bar[WARPS];
+  __shared__ uint64_t k_bar[WARPS], v_bar[WARPS];
   __shared__ int abort_flag;
   if (TMA && (threadIdx.x & 31) == 0) {
     if (threadIdx.x == 0) abort_flag = 0;
-    mbar_init(&tile_bar[threadIdx.x >> 5], 1);
+    mbar_init(&k_bar[threadIdx.x >> 5], 1);
+    mbar_init(&v_bar[threadIdx.x >> 5], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // Lengths and block tables came with the step's metadata, before any kernel of the step ran,
@@ -363,50 +370,40 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
   const int pos = p.kv_len[seq] - 1;  // the one query position of this request
   int k_lo = 0;
   if (p.window > 0) k_lo = max(0, pos - p.window + 1);
-  k_lo = max(k_lo, split * DECODE_SPLIT_KEYS);
-  const int k_hi = min(pos, (split + 1) * DECODE_SPLIT_KEYS - 1);
+  k_lo = max(k_lo, split * p.split_keys);
+  const int k_hi = min(pos, (split + 1) * p.split_keys - 1);
   if (k_lo > k_hi) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // this warp's block of keys
-  const int j0 = (split * WARPS + warp) * BLOCK_N;
-  const bool has_keys = j0 <= k_hi && j0 + BLOCK_N - 1 >= k_lo;
+  // this warp's blocks of keys: first, first + WARPS, ... up to last (block numbers within the request)
+  const int b_lo = k_lo / BLOCK_N, b_hi = k_hi / BLOCK_N;
+  const int mine = split * (p.split_keys / BLOCK_N) + warp;
+  const int first = mine >= b_lo ? mine : mine + (b_lo - mine + WARPS - 1) / WARPS * WARPS;
+  const bool has_keys = first <= b_hi;
+  const int last = !has_keys ? first - WARPS : LONG ? first + (b_hi - first) / WARPS * WARPS : first;
   bf16* kt = k_tiles + warp * TILE_ELEMS;
   bf16* vt = v_tiles + warp * TILE_ELEMS;
-  // the block lies inside one page, its 64 rows are consecutive cache slots
-  int row0 = 0;
-  if (TMA && has_keys && lane == 0) {
-    const int e = j0 / p.page_size;
-    row0 = p.block_table[(size_t)seq * p.max_blocks + e] * p.page_size + (j0 - e * p.page_size);
-  }
-  const int token = p.q_start[seq];
-  auto fetch_block = [&]() {  // one lane
-    mbar_expect_tx(&tile_bar[warp], 2 * TILE_BYTES_TMA);
-#pragma unroll
-    for (int sub = 0; sub < HD / 64; ++sub) {
-      tma_load_2d(reinterpret_cast<uint8_t*>(kt) + sub * BLOCK_N * 128, &map_k, &tile_bar[warp], kvh * HD + sub * 64, row0);
-      tma_load_2d(reinterpret_cast<uint8_t*>(vt) + sub * BLOCK_N * 128, &map_v, &tile_bar[warp], kvh * HD + sub * 64, row0);
-    }
+  // a block lies inside one page, its 64 rows are consecutive cache slots
+  auto block_row = [&](int block) {
+    const int j = block * BLOCK_N, e = j / p.page_size;
+    return p.block_table[(size_t)seq * p.max_blocks + e] * p.page_size + (j - e * p.page_size);
   };
-  // A block that ends before the query's own position holds only keys of earlier steps: its copy
-  // need not wait for the kernel that writes this step's key and may start at once.
-  const bool early = TMA && has_keys && j0 + BLOCK_N - 1 < pos;
-  if (early && lane == 0) fetch_block();
-  pdl_wait();
-
-  // the query rows: head kvh * g + r for r < g, zero rows above
-  for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += THREADS) {
-    const int r = idx / CHUNKS, c = idx % CHUNKS;
-    const bool ok = r < g;
-    const bf16* src = ok ? p.q + ((size_t)token * p.nh + kvh * g + r) * HD + c * 8 : p.q;
-    cp_async16((uint32_t)__cvta_generic_to_shared(q_tile + r * ROW + c * 8), src, ok);
-  }
-  if (TMA) {
-    if (lane == 0 && has_keys && !early) fetch_block();
-  } else if (has_keys) {
+  auto fetch_keys = [&](int row) {  // one lane
+    mbar_expect_tx(&k_bar[warp], TILE_BYTES_TMA);
+#pragma unroll
+    for (int sub = 0; sub < HD / 64; ++sub)
+      tma_load_2d(reinterpret_cast<uint8_t*>(kt) + sub * BLOCK_N * 128, &map_k, &k_bar[warp], kvh * HD + sub * 64, row);
+  };
+  auto fetch_values = [&](int row) {  // one lane
+    mbar_expect_tx(&v_bar[warp], TILE_BYTES_TMA);
+#pragma unroll
+    for (int sub = 0; sub < HD / 64; ++sub)
+      tma_load_2d(reinterpret_cast<uint8_t*>(vt) + sub * BLOCK_N * 128, &map_v, &v_bar[warp], kvh * HD + sub * 64, row);
+  };
+  auto fetch_padded = [&](int block) {  // the whole warp
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
     for (int idx = lane; idx < BLOCK_N * CHUNKS; idx += 32) {
       const int r = idx / CHUNKS, c = idx % CHUNKS;
-      const int j = j0 + r;
+      const int j = block * BLOCK_N + r;
       const bool ok = j >= k_lo && j <= k_hi;
       size_t offset = 0;
       if (ok) {
@@ -417,28 +414,99 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
       cp_async16((uint32_t)__cvta_generic_to_shared(kt + r * ROW + c * 8), p.k_cache + offset, ok);
       cp_async16((uint32_t)__cvta_generic_to_shared(vt + r * ROW + c * 8), p.v_cache + offset, ok);
     }
+  };
+  auto fetch_first = [&](int row) {  // one lane
+    if (LONG) {
+      fetch_keys(row);
+      fetch_values(row);
+    } else {
+      mbar_expect_tx(&k_bar[warp], 2 * TILE_BYTES_TMA);
+#pragma unroll
+      for (int sub = 0; sub < HD / 64; ++sub) {
+        tma_load_2d(reinterpret_cast<uint8_t*>(kt) + sub * BLOCK_N * 128, &map_k, &k_bar[warp], kvh * HD + sub * 64, row);
+        tma_load_2d(reinterpret_cast<uint8_t*>(vt) + sub * BLOCK_N * 128, &map_v, &k_bar[warp], kvh * HD + sub * 64, row);
+      }
+    }
+  };
+  int row_first = 0, row_next = 0;  // lane 0: cache rows of the first block and of the one after it
+  if (TMA && has_keys && lane == 0) {
+    row_first = block_row(first);
+    if (LONG && first < last) row_next = block_row(first + WARPS);
+  }
+  const int token = p.q_start[seq];
+  // A block that ends before the query's own position holds only keys of earlier steps: its copy
+  // need not wait for the kernel that writes this step's key and may start at once.
+  const bool early = TMA && has_keys && first * BLOCK_N + BLOCK_N - 1 < pos;
+  if (early && lane == 0) fetch_first(row_first);
+  pdl_wait();
+
+  // the query rows: head kvh * g + r for r < g, zero rows above
+  for (int idx = threadIdx.x; idx < 16 * CHUNKS; idx += THREADS) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool ok = r < g;
+    const bf16* src = ok ? p.q + ((size_t)token * p.nh + kvh * g + r) * HD + c * 8 : p.q;
+    cp_async16((uint32_t)__cvta_generic_to_shared(q_tile + r * ROW + c * 8), src, ok);
+  }
+  if (TMA) {
+    if (lane == 0 && has_keys && !early) fetch_first(row_first);
+  } else if (has_keys) {
+    fetch_padded(first);
   }
   pdl_launch();
   cp_async_commit();
   cp_async_wait<0>();
   __syncthreads();  // the query tile was copied by all threads (and the barriers are initialised)
-  bool arrived = true;
-  if (TMA && has_keys) arrived = mbar_wait(&tile_bar[warp], 0, &abort_flag);
 
   RowState st;
   st.m_lo = st.m_hi = -INFINITY;
   st.l_lo = st.l_hi = 0.f;
 #pragma unroll
   for (int d = 0; d < DTILES; ++d) st.o[d][0] = st.o[d][1] = st.o[d][2] = st.o[d][3] = 0.f;
-  if (has_keys && arrived) {
+  if (has_keys) {
     uint32_t qf[KSTEPS][4];
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
       const bf16* src = q_tile + (lane & 15) * ROW + ks * 16 + (lane >> 4) * 8;
       ldmatrix_x4(qf[ks], (uint32_t)__cvta_generic_to_shared(src));
     }
-    attend_block<TMA>(st, qf, (uint32_t)__cvta_generic_to_shared(kt), (uint32_t)__cvta_generic_to_shared(vt), j0, lane, pos, k_lo, k_hi,
-                      p.window, p.scale_log2);
+    const uint32_t kt_s = (uint32_t)__cvta_generic_to_shared(kt), vt_s = (uint32_t)__cvta_generic_to_shared(vt);
+    uint32_t parity = 0;
+    for (int block = first; block <= last; block += WARPS, parity ^= 1) {
+      const bool more = LONG && block < last;
+      if (TMA) {
+        if (!mbar_wait(&k_bar[warp], parity, &abort_flag)) break;
+        const int row_more = row_next;
+        int row_after = 0;  // looked up two blocks ahead, so that the copy does not wait for the table
+        if (LONG && lane == 0 && block + 2 * WARPS <= last) row_after = block_row(block + 2 * WARPS);
+        bool values_here = true;
+        attend_block<true>(
+            st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, p.window, p.scale_log2,
+            [&] {
+              if (more) {
+                __syncwarp();  // every lane has taken its scores from the key tile
+                if (lane == 0) fetch_keys(row_more);
+              }
+            },
+            [&] {
+              if (LONG) values_here = mbar_wait(&v_bar[warp], parity, &abort_flag);
+            });
+        if (!values_here) break;
+        if (more) {
+          __syncwarp();  // every lane has multiplied the value tile in
+          if (lane == 0) fetch_values(row_more);
+        }
+        row_next = row_after;
+      } else {
+        attend_block<false>(st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, p.window, p.scale_log2);
+        if (more) {
+          __syncwarp();
+          fetch_padded(block + WARPS);
+          cp_async_commit();
+          cp_async_wait<0>();
+          __syncwarp();
+        }
+      }
+    }
   }
   // ---- merge the warps in warp order ---------------------------------------------------
   __syncthreads();  // every warp is done with the key tiles the merge buffers overlay
@@ -499,19 +567,27 @@ static size_t decode_smem_bytes(int warps, bool tma) {
   return 1024 + (tiles > merge ? tiles : merge) + (size_t)16 * ROW * sizeof(bf16);
 }
 
+template <int WARPS, bool TMA, bool LONG>
+static int launch_decode_as(const AttnParams& p, const CUtensorMap& map_k, const CUtensorMap& map_v, int n_splits, int nkv, int n_seqs,
+                            cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_decode_kernel<WARPS, TMA, LONG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)decode_smem_bytes(WARPS, TMA)) != cudaSuccess)
+      return ALOFA_ERR_LAUNCH;
+    prefer_max_shared(attention_decode_kernel<WARPS, TMA, LONG>);
+    configured = true;
+  }
+  launch_dep(attention_decode_kernel<WARPS, TMA, LONG>, dim3(n_splits, nkv, n_seqs), WARPS * 32, decode_smem_bytes(WARPS, TMA), stream, p, map_k,
+             map_v);
+  return cudaGetLastError() == cudaSuccess ? ALOFA_OK : ALOFA_ERR_LAUNCH;
+}
+
 template <int WARPS, bool TMA>
 static int launch_decode(const AttnParams& p, const CUtensorMap& map_k, const CUtensorMap& map_v, int n_splits, int nkv, int n_seqs,
                          cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_decode_kernel<WARPS, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)decode_smem_bytes(WARPS, TMA)) != cudaSuccess)
-      return ALOFA_ERR_LAUNCH;
-    prefer_max_shared(attention_decode_kernel<WARPS, TMA>);
-    configured = true;
-  }
-  launch_dep(attention_decode_kernel<WARPS, TMA>, dim3(n_splits, nkv, n_seqs), WARPS * 32, decode_smem_bytes(WARPS, TMA), stream, p, map_k, map_v);
-  return cudaGetLastError() == cudaSuccess ? ALOFA_OK : ALOFA_ERR_LAUNCH;
+  if (p.split_keys > WARPS * BLOCK_N) return launch_decode_as<WARPS, TMA, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
+  return launch_decode_as<WARPS, TMA, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
 }
 
 // Merge the splits of every (token, head) row in split order.  One block of HD
@@ -543,6 +619,28 @@ static size_t attention_smem_bytes(int stages, int table_entries) {
 }
 
 ALOFA_API int alofa_attention_head_dim() { return HD; }
+
+// How many CTAs of the decode kernel (four warps) the device holds at a time: what a caller
+// sizes the key splits by, so that a step's CTAs are resident together.  0 when it cannot be asked.
+ALOFA_API int alofa_attention_decode_slots(int page_size) {
+  const bool tma = (HD == 64 || HD == 128) && page_size % BLOCK_N == 0;
+  int device = 0, sms = 0, per_sm = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+  const size_t smem = decode_smem_bytes(4, tma);
+  cudaError_t rc;
+  if (tma) {
+    cudaFuncSetAttribute(attention_decode_kernel<4, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<4, true, true>, 128, smem);
+  } else {
+    cudaFuncSetAttribute(attention_decode_kernel<4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<4, false, true>, 128, smem);
+  }
+  if (rc != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return sms * per_sm;
+}
 
 // Merge the splits a launch with do_combine = 0 left behind: out [T, nh, HD] bf16.
 ALOFA_API int alofa_attention_combine(void* out, const float* partial_o, const float* partial_ml, const int* positions, int n_tokens, int nh,
@@ -610,7 +708,7 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
     prefer_max_shared(attention_combine_kernel);
     configured = true;
   }
-  if (n_splits > 0 && decode_only && nh / nkv <= 16 && (split_keys == 4 * BLOCK_N || split_keys == 2 * BLOCK_N)) {
+  if (n_splits > 0 && decode_only && nh / nkv <= 16 && (split_keys % (4 * BLOCK_N) == 0 || split_keys == 2 * BLOCK_N)) {
     // decode tokens of small head groups: the key blocks of a split side by side on the warps
     // pages that hold whole key blocks and rows of 128 or 256 bytes: bulk tensor copies
     CUtensorMap map_k, map_v;
@@ -623,7 +721,7 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
       memset(&map_v, 0, sizeof(map_v));
     }
     int rc;
-    if (split_keys == 4 * BLOCK_N)
+    if (split_keys % (4 * BLOCK_N) == 0)
       rc = tma ? launch_decode<4, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<4, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
     else
       rc = tma ? launch_decode<2, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<2, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);

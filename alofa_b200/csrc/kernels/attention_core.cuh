@@ -70,9 +70,12 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int col) {
 }
 
 // One warp: 16 query rows against the 64 keys of one block held in shared tiles.
-template <bool SWIZZLED>
+// keys_done() runs when the key tile has been read for the last time (it may be
+// refilled), values_wanted() just before the value tile is read for the first time.
+template <bool SWIZZLED, class KeysDone, class ValuesWanted>
 __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[KSTEPS][4], uint32_t kt, uint32_t vt, int j0, int lane,
-                                             int pos, int k_lo, int k_hi, int window, float scale_log2) {
+                                             int pos, int k_lo, int k_hi, int window, float scale_log2, KeysDone keys_done,
+                                             ValuesWanted values_wanted) {
   float s[BLOCK_N / 8][4];
 #pragma unroll
   for (int n = 0; n < BLOCK_N / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
@@ -86,6 +89,7 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
       mma_16816(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
     }
   }
+  keys_done();
   const bool all_visible = j0 >= k_lo && j0 + BLOCK_N - 1 <= k_hi && (window <= 0 || j0 > pos - window);
   if (!all_visible) {
 #pragma unroll
@@ -135,6 +139,7 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
     st.o[d][2] *= corr_hi;
     st.o[d][3] *= corr_hi;
   }
+  values_wanted();
 #pragma unroll
   for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
 #pragma unroll
@@ -145,6 +150,12 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
       mma_16816(st.o[2 * d2 + 1], pf[kk], vf[2], vf[3]);
     }
   }
+}
+
+template <bool SWIZZLED>
+__device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[KSTEPS][4], uint32_t kt, uint32_t vt, int j0, int lane,
+                                             int pos, int k_lo, int k_hi, int window, float scale_log2) {
+  attend_block<SWIZZLED>(st, qf, kt, vt, j0, lane, pos, k_lo, k_hi, window, scale_log2, [] {}, [] {});
 }
 
 constexpr int MERGE_ROW = HD + 4;  // floats per merged row in shared memory

@@ -93,8 +93,22 @@ def _attention(head_dim: int):
         lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _I, _P]
         lib.alofa_attention_combine.restype = _I
         lib.alofa_attention_combine.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _P]
+        lib.alofa_attention_decode_slots.restype = _I
+        lib.alofa_attention_decode_slots.argtypes = [_I]
         _libs[key] = lib
     return lib
+
+
+_decode_slots = {}
+
+
+def attention_decode_slots(head_dim: int, page_size: int) -> int:
+    """How many CTAs of the decode attention kernel the device holds at a
+    time (asked once per head size and kind of page)."""
+    key = (head_dim, page_size % 64 == 0)
+    if key not in _decode_slots:
+        _decode_slots[key] = max(1, _attention(head_dim).alofa_attention_decode_slots(page_size))
+    return _decode_slots[key]
 
 
 def attention_bf16_supported(head_dim: int) -> bool:

@@ -145,7 +145,13 @@ class GQAttention(Part):
                 custom(ctx, q_view, k_view)
             ops.rope_store(q, cache.k, cache.v, qkv, table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, rot, writes)
 
-    SPLIT_KEYS = 256  # keys per CTA when a decode-only step splits each request's keys (four 64-key blocks, one per warp)
+    # Keys per CTA, at least, when a decode-only step splits each request's keys: four 64-key
+    # blocks, one per warp.  Splits grow in steps of this (a warp then takes several blocks in
+    # turn, fetching the next behind its work on this one) until the step's CTAs are resident
+    # together: CTAs that queue for an SM load, then compute, wave after wave (batch 64 at
+    # 2,048 keys: 1.58 -> 1.47 ms per step for 14 heads of 64 on 2, 5.90 -> 5.08 ms for 28 heads
+    # of 128 on 4).
+    SPLIT_KEYS = 256
     # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.
     # Measured at 2,048-token prompts the round trip of the partial sums costs more than the
     # long tiles' tail saves (4.9 ms against 4.5 ms for the step), so it is off.
@@ -166,6 +172,14 @@ class GQAttention(Part):
             splits, po, pml = 0, None, None
             longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
             per_split = self.SPLIT_KEYS
+            group_size = self.nh // self.nkv
+            if ctx.decode_only and group_size <= 16:
+                resident = ops.attention_decode_slots(self.hd, group.page_size) // max(1, ctx.n_seqs * self.nkv)
+                blocks = -(-longest // self.SPLIT_KEYS)
+                if ctx.n_tokens <= 16 and blocks <= 4 * self.MERGE_IN_PRODUCT_SPLITS:
+                    # few enough splits that the output product merges them, while a warp has at most four blocks
+                    resident = min(resident, self.MERGE_IN_PRODUCT_SPLITS)
+                per_split = self.SPLIT_KEYS * -(-blocks // max(1, resident))
             if not ctx.decode_only:
                 per_split = self.PROMPT_SPLIT_KEYS or (1 << 30)
             if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):

@@ -440,6 +440,32 @@ def test_attention_bf16_split_keys(ops, hd, nh, nkv):
     assert_close(got, want, TOL[BF16], "one split")
 
 
+@pytest.mark.parametrize("hd, nh, nkv", [(64, 14, 2), (128, 7, 1), (32, 6, 2)])
+def test_attention_bf16_long_splits(ops, hd, nh, nkv):
+    """Splits of several blocks per warp (512 to 1,280 keys): a warp refills its
+    key tile and its value tile while it works on the block before.  Lengths
+    either side of every edge: one block, one round of the warps, a split."""
+    lens = [1, 65, 256, 257, 513, 769, 1025, 2049, 2600]
+    for window, cases in ((None, ((512, 64), (768, 128), (1280, 64), (512, 16))), (700, ((1024, 64), (768, 48)))):
+        for split, page in cases:
+            got, want = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=[1] * len(lens), page=page, window=window, rng=np.random.default_rng(hd + split), fast=True, split_keys=split)
+            assert_close(got, want, TOL[BF16], f"split {split} hd={hd} window={window} page={page}")
+    # one far key, in every block of a 1,024-key split in turn, among 2,049
+    for far in range(1024 + 5, 2049, 128 if hd != 64 else 64):
+        rng = np.random.default_rng(far)
+
+        def craft(qs, ks, vs, far=far):
+            direction = rng.normal(size=hd)
+            direction /= np.linalg.norm(direction)
+            qs[0][-1, :] = np.tile(12.0 * direction, nh)
+            ks[0][far, :] = np.tile(12.0 * direction, nkv)
+            vs[0][far, :] = 100.0
+
+        got, want = attention_case(ops, BF16, hd, nh, nkv, lens=[2049], q_lens=[1], page=64, window=None, rng=rng, craft=craft, fast=True, split_keys=1024)
+        assert np.abs(want[0]).min() > 90.0
+        assert_close(got, want, TOL[BF16], f"far key at {far}")
+
+
 def test_attention_bf16_prompt_portions_with_split_keys(ops):
     """Prompt portions (and decode tokens beside them) whose query tiles split
     their keys over several CTAs."""

@@ -82,6 +82,54 @@ def test_decode_graphs_against_plain_and_launches(folders, name):
 
 
 @pytest.mark.parametrize("name", ["P", "Q"])
+def test_decode_with_more_work_than_the_device_holds_at_once(folders, name, monkeypatch):
+    """When a decode step's (request, KV head) pairs times 256-key splits are
+    more than the CTAs the device holds at a time, the splits grow and a warp
+    takes several key blocks in turn.  Made to happen at this size by a device
+    that claims room for few CTAs: twenty requests merged by the combine
+    kernel, then eight whose splits the output product merges."""
+    from alofa_b200.csrc import ops
+    from alofa_b200.engine.step import StepEntry
+    from alofa_b200.parts.attention import GQAttention
+
+    wts, cfg = plain.load(folders[name])
+    vocab = configs()[name][0].vocab_size
+    rng = np.random.default_rng(5)
+    lens = [1, 63, 255, 256, 257, 511, 512, 513, 767, 768, 769, 900] + [int(n) for n in rng.integers(2, 900, 8)]
+    n_new = 3
+    seqs = [[int(t) for t in rng.integers(0, vocab, n + n_new)] for n in lens]
+    want = [plain.forward(s, wts, cfg) for s in seqs]
+    asked = []
+    real = ops.attention_bf16
+
+    def watch(*args, **kwargs):
+        asked.append(args[17])  # split_keys
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(ops, "attention_bf16", watch)
+    for graphs in (True, False):
+        runner = runner_for(folders[name], graphs, pages=20 * 16, max_requests=20, max_tokens=20 * 1024)
+        slots = [runner.admit(i) for i in range(len(seqs))]
+        for i in rng.permutation(len(seqs)):
+            for lo in range(0, lens[i], 700):
+                runner.forward([StepEntry(slots[i], seqs[i][lo : min(lens[i], lo + 700)], [])])
+        got = [[] for _ in seqs]
+        del asked[:]
+        for step, (live, room) in enumerate(((range(20), 40), (range(4, 12), 16), (range(4, 12), 16))):
+            monkeypatch.setattr(ops, "attention_decode_slots", lambda hd, page, room=room: room)
+            logits = runner.forward([StepEntry(slots[i], [seqs[i][lens[i] + len(got[i])]], [0]) for i in live]).float().cpu().numpy()
+            for row, i in zip(logits, live):
+                got[i].append(row)
+        runner.check_status()
+        assert max(asked) >= 512 and GQAttention.SPLIT_KEYS == 256, f"splits asked for: {sorted(set(asked))}"
+        for i, rows in enumerate(got):
+            ref = want[i][lens[i] : lens[i] + len(rows)]
+            bound = 2e-2 * max(1.0, float(np.abs(ref).max()))
+            diff = np.abs(np.stack(rows).astype(np.float64) - ref) if rows else np.zeros(1)
+            assert diff.max() <= bound, f"{name} graphs={graphs} request {i} ({lens[i]} keys): differs from plain by {diff.max():.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("name", ["P", "Q"])
 def test_prompt_steps_of_a_repeated_shape_are_replayed_as_graphs(folders, name):
     """Steps with prompt portions whose shape (tokens, requests, wanted rows)
     repeats are recorded as CUDA graphs at the third occurrence and replayed
