@@ -23,14 +23,15 @@
 // that a small token count still pulls weights through every SM; the partial
 // sums are added in a fixed order by alofa_splitk_reduce.
 //
-// Small decode steps (up to 16 tokens) keep the residual stream as a base tensor plus a 64-bit
+// Decode steps of a few dozen tokens keep the residual stream as a base tensor plus a 64-bit
 // fixed-point accumulator (units of 2^-32): residual products add their split sums into the
-// accumulator with atomic integer adds - the sum does not depend on the order of arrival - and the
-// product that reads the stream next (q/k/v, gate/up) makes its token operand from base +
-// accumulator itself, with the RMSNorm folded in (B_NORMED): the operand is (base + acc) * gamma,
-// the row's 1/sqrt(mean square + eps) is a per-token factor and is applied to the accumulator in
-// the epilogue (src/alofa/kernels/cpu/scalar.mojo:93-129 for the norm).  No norm kernel, no split
-// sums in memory.
+// accumulator with atomic integer adds - the sum does not depend on the order of arrival.  In
+// steps of up to 16 tokens the product that reads the stream next (q/k/v, gate/up) makes its
+// token operand from base + accumulator itself, with the RMSNorm folded in (B_NORMED): the
+// operand is (base + acc) * gamma, the row's 1/sqrt(mean square + eps) is a per-token factor and
+// is applied to the accumulator in the epilogue (src/alofa/kernels/cpu/scalar.mojo:93-129 for the
+// norm).  No norm kernel, no split sums in memory.  In larger steps the norm kernel reads base +
+// accumulator.
 //
 // Every wait on an mbarrier is bounded: after the limit the CTA raises the
 // status word, skips its remaining work, frees its tensor memory and returns.

@@ -131,8 +131,9 @@ class StepContext:
     # other buffer (which becomes the base) and clears the accumulator that was not read; readers
     # that cannot do that get the stream settled in its own tensor first.
     def open_stream(self, h) -> None:
-        """Called by the model once ``h`` exists: decode steps of up to 16
-        tokens in bfloat16 keep ``h`` as base + accumulator."""
+        """Called by the model once ``h`` exists: steps of few enough tokens
+        for the runner's accumulators, in bfloat16, keep ``h`` as base +
+        accumulator."""
         acc = self.stream_acc
         if acc is None or self.n_tokens > acc.shape[1] or h.shape[1] != acc.shape[2] or h.shape[1] % 8 or self.rt.dtype != torch.bfloat16:
             return

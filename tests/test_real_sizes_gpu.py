@@ -146,11 +146,13 @@ def test_steps_allocate_nothing(shaped):
     runner.check_status()
 
 
-def test_small_decode_steps_give_the_same_bits_every_run(shaped):
-    """Eight requests decoded together through the five-kernel layer, whose
-    residual products add their split sums with atomic integer adds in
-    whatever order their CTAs finish: two runs from the same state must give
-    the same logits bit for bit, and the accumulators are zero between steps."""
+@pytest.mark.parametrize("n", [8, 40])
+def test_decode_steps_on_the_accumulator_stream_give_the_same_bits_every_run(shaped, n):
+    """Requests decoded together (eight: the five-kernel layer; forty: the
+    layer of larger steps), whose residual products add their split sums with
+    atomic integer adds in whatever order their CTAs finish: two runs from the
+    same state must give the same logits bit for bit, and the accumulators are
+    zero between steps."""
     from alofa_b200.engine.loading import compute_dtype
     from alofa_b200.engine.step import StepEntry, StepRunner
     from alofa_b200.models.qwen2 import build_spec
@@ -162,13 +164,13 @@ def test_small_decode_steps_give_the_same_bits_every_run(shaped):
     model = Model(build_spec(cfg), Runtime(torch.device("cuda"), compute_dtype("bfloat16")))
     model.load(load_state(model.tensors(), state, model.rt.dtype, model.rt.device))
     rng = np.random.default_rng(11)
-    prompts = [[int(t) for t in rng.integers(0, 151936, int(n))] for n in rng.integers(20, 200, 8)]
-    feed = rng.integers(0, 151936, size=(6, 8))
+    prompts = [[int(t) for t in rng.integers(0, 151936, int(k))] for k in rng.integers(20, 200, n)]
+    feed = rng.integers(0, 151936, size=(4, n))
     runs = []
     for graphs in (True, True, False):
-        runner = StepRunner(model, block_size=64, num_pages=40, max_requests=8, max_tokens=512, max_step_tokens=256, cuda_graphs=graphs)
-        assert runner._stream_acc is not None
-        slots = [runner.admit(i) for i in range(8)]
+        runner = StepRunner(model, block_size=64, num_pages=5 * n, max_requests=n, max_tokens=512, max_step_tokens=256, cuda_graphs=graphs)
+        assert runner._stream_acc is not None and n <= runner.STREAM_TOKENS
+        slots = [runner.admit(i) for i in range(n)]
         for s, p in zip(slots, prompts):
             runner.forward([StepEntry(s, p, [])])
         rows = []
