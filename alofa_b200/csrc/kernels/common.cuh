@@ -38,6 +38,18 @@ __device__ __forceinline__ float stream_add(float base, long long acc) {
   return (base + (float)whole) + (float)fraction * (1.0f / 4294967296.0f);
 }
 
+// silu(g) * u = g / (1 + e^-g) * u in the bfloat16 kernels: the exponential and the reciprocal by
+// the hardware approximations (2 ulp and 1 ulp), denormals flushed.  One function for every kernel
+// that has a gated epilogue, so that a token's value does not depend on which of them ran; the
+// library forms (__expf, a division) cost the prompt kernels' epilogue a fifth of its time.
+// (src/alofa/kernels/cpu/scalar.mojo:208-232 for the formula.)
+__device__ __forceinline__ float silu_times(float g, float u) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return g * r * u;
+}
+
 // Sum over a warp in a fixed butterfly order; every lane gets the result.
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -58,6 +58,7 @@ struct GemmArgs {
   int T, N, K;        // tokens, output features (GATED: per half), depth
   int k_slices_per_split;
   int out_bf16;
+  int pair;           // tokens on M: the wide product runs on pairs of CTAs (the weight map's box is then 128 rows)
   int* status;
   // The token operand of the weights-on-M kernel need not lie in memory as rows: the
   // epilogue warps, idle while the MMAs run, can make each k-slice of it in shared memory.
@@ -464,7 +465,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (N_ACC == 2) p[plane] = __uint_as_float(r1[j]);
         } else if (EPI == EPI_GATED) {
           const float g = a0 + bias0, u = __uint_as_float(r1[j]) + bias1;
-          const float y = g / (1.0f + __expf(-g)) * u;
+          const float y = silu_times(g, u);
           if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
           else ((float*)args.out)[(size_t)t * args.N + f] = y;
         } else {
@@ -629,11 +630,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // The epilogue of a 128-token tile whose width is a multiple of 4: warp q owns
 // rows [32q, 32q + 32) of the accumulator at `tmem_acc`; `staging` holds
-// 4 x 32 rows of 132 floats.  `release` (optional, 128 arrivals) is signalled
+// 4 x 32 rows of 132 floats.  `release` (optional, one arrival per warp) is signalled
 // once the accumulator has been read out.
 template <int BNF, int EPI>
 __device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uint32_t tmem_base, float* staging, int q, int lane, int f0, int t0,
-                                                       int n_splits, int split_index, uint64_t* release) {
+                                                       int n_splits, int split_index, uint64_t* release, uint32_t release_in_cluster = 0) {
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr int FEATS = GATED ? BNF / 2 : BNF;
   // The accumulator rows go through shared memory so
@@ -665,18 +666,20 @@ __device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uin
         if (GATED) {
           float u = __uint_as_float(r1[j]);
           if (args.bias && f + j < N) u += args.bias[N + f + j];
-          a = __fdividef(a, 1.0f + __expf(-a)) * u;
+          a = silu_times(a, u);
         }
         v[j] = a;
       }
 #pragma unroll
       for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(stage + lane * PITCH + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
     }
-    if (release && (cb + 128 >= FEATS || f0 + cb + 128 >= N)) {  // the accumulator is read out: the next tile but one may have it
-      tc_fence_before();
-      mbar_arrive(release);
-    }
+    const bool read_out = (release || release_in_cluster) && (cb + 128 >= FEATS || f0 + cb + 128 >= N);
+    if (read_out) tc_fence_before();  // the accumulator is read out: the next tile but one may have it
     __syncwarp();
+    if (read_out && lane == 0) {  // one arrival per warp: arrivals at a barrier of the other CTA are dear
+      if (release_in_cluster) mbar_arrive_in_cluster(release_in_cluster);
+      else mbar_arrive(release);
+    }
     const int f = f0 + cb + lane * 4;  // this lane's four features of every row
     const bool f_ok = f < N && cb + lane * 4 < FEATS;  // N % 4 == 0: a group is inside or outside as a whole
     const int rows = min(32, args.T - (t0 + q * 32));
@@ -872,7 +875,7 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         }
         if (GATED) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + __expf(-v[j])) * u[j];
+          for (int j = 0; j < 16; ++j) v[j] = silu_times(v[j], u[j]);
         }
         if (EPI == EPI_RESIDUAL) {
           float* o = (float*)args.out + (size_t)t * N + f;
@@ -970,7 +973,7 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_free[b], 128);
+      mbar_init(&acc_free[b], 4);  // the epilogue warps
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1055,7 +1058,8 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
         tokens_epilogue_staged<BNF, EPI>(args, tmem_base + buf * BNF, staging, q, lane, f0, t0, 1, 0, &acc_free[buf]);
       } else {
         tc_fence_before();
-        mbar_arrive(&acc_free[buf]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_free[buf]);
       }
     }
   }
@@ -1064,6 +1068,150 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
+}
+
+// ---------------------------------------------------------------------------
+// The same, on pairs of CTAs (a cluster of two, one CTA per SM): a pair works
+// through tiles of 256 tokens x 256 weight rows with MMAs of M = 256 that the
+// first CTA issues for both.  Each CTA fetches its own 128 tokens and its own
+// half of the weight rows (for EPI_GATED the first CTA the gate rows, the
+// second the matching up rows), 32 KB per k-slice where the single CTA fetches
+// 48 KB for the same MMA time: the product is no longer bound by what an SM can
+// pull out of L2, and the ring is four stages deep.  The first CTA's full
+// barrier counts the bytes of both CTAs' copies; the MMAs' completion is
+// signalled on the barriers of both; both CTAs' epilogue warps free an
+// accumulator on the first CTA's barrier.
+// ---------------------------------------------------------------------------
+constexpr int PAIR_STAGES = 4;
+
+template <int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_tokens_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args) {
+  constexpr int BNF = 256;
+  constexpr bool GATED = EPI == EPI_GATED;
+  constexpr int FEATS = GATED ? BNF / 2 : BNF;
+  constexpr uint32_t A_BYTES = 128 * BK * 2;
+  constexpr uint32_t B_BYTES = (BNF / 2) * BK * 2;  // this CTA's half of the weight rows
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BNF >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  float* staging = reinterpret_cast<float*>(tiles + (size_t)PAIR_STAGES * STAGE_BYTES);
+  __shared__ uint64_t full_bar[PAIR_STAGES], empty_bar[PAIR_STAGES], acc_full[2], acc_free[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool first = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int n_ftiles = (args.N + FEATS - 1) / FEATS, n_ttiles = (args.T + 255) / 256;
+  const int n_tiles = n_ftiles * n_ttiles;
+  const int n_slices = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_free[b], 8);  // the epilogue warps of both CTAs
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) tmem_alloc_pair(&tmem_base_smem, 512);
+  tc_fence_before();
+  cluster_sync_all();  // both CTAs' barriers stand before either signals the other's
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  // this CTA's weight rows of a tile that starts at feature f0
+  auto weight_row = [&](int f0) { return GATED ? (first ? f0 : args.N + f0) : f0 + (int)rank * (BNF / 2); };
+  auto load_weights = [&](int it, int i, int f0) {  // the weight tile of slice i of a tile into the stage of ring position it
+    const int s = it % PAIR_STAGES;
+    if (first) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+    tma_load_2d_pair(tiles + (size_t)s * STAGE_BYTES + A_BYTES, &map_w, in_cluster_cta(&full_bar[s], 0), i * BK, weight_row(f0));
+  };
+  // the weights depend on no earlier kernel: those of the first tile's first ring go ahead of the wait
+  int early_slices = 0;
+  if (threadIdx.x == 0) {
+    asm volatile("griddepcontrol.launch_dependents;");
+    if (pair < n_tiles) {
+      early_slices = min(PAIR_STAGES, n_slices);
+      for (int i = 0; i < early_slices; ++i) load_weights(i, i, (pair % n_ftiles) * FEATS);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+  } else {
+    pdl_begin();
+  }
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;  // slices asked for so far, over all tiles
+      for (int tile = pair; tile < n_tiles; tile += n_pairs) {
+        const int f0 = (tile % n_ftiles) * FEATS, t0 = (tile / n_ftiles) * 256 + (int)rank * 128;
+        for (int i = 0; i < n_slices; ++i, ++it) {
+          const int s = it % PAIR_STAGES;
+          if (it >= PAIR_STAGES && !mbar_wait(&empty_bar[s], ((it / PAIR_STAGES) - 1) & 1, &abort_flag)) break;
+          if (it >= early_slices) load_weights(it, i, f0);
+          tma_load_2d_pair(tiles + (size_t)s * STAGE_BYTES, &map_x, in_cluster_cta(&full_bar[s], 0), i * BK, t0);
+        }
+        if (abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && first) {
+      int it = 0, j = 0;  // slices consumed; tiles of this pair so far
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++j) {
+        const int buf = j & 1;
+        if (j >= 2) ok = mbar_wait(&acc_free[buf], ((j >> 1) - 1) & 1, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        for (int i = 0; i < n_slices; ++i, ++it) {
+          const int s = it % PAIR_STAGES;
+          ok = mbar_wait(&full_bar[s], (it / PAIR_STAGES) & 1, &abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t stage = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const uint64_t desc_a = smem_desc_sw128(stage), desc_b = smem_desc_sw128(stage + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_pair(tmem_base + buf * BNF, desc_a + (uint64_t)(k * 2), desc_b + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
+          umma_commit_pair(&empty_bar[s], 3);
+        }
+        if (ok) umma_commit_pair(&acc_full[buf], 3);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int j = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++j) {
+      const int buf = j & 1;
+      const int f0 = (tile % n_ftiles) * FEATS, t0 = (tile / n_ftiles) * 256 + (int)rank * 128;
+      bool ok = mbar_wait(&acc_full[buf], (j >> 1) & 1, &abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t free_bar = in_cluster_cta(&acc_free[buf], 0);
+      if (t0 + q * 32 < args.T) {
+        tokens_epilogue_staged<BNF, EPI>(args, tmem_base + buf * BNF, staging, q, lane, f0, t0, 1, 0, nullptr, free_bar);
+      } else {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_in_cluster(free_bar);
+      }
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();  // neither CTA leaves, or frees tensor memory, while the other may still signal or read it
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
   }
   if (threadIdx.x == 0 && abort_flag && args.status) atomicExch(args.status, 2);
 }
@@ -1101,7 +1249,7 @@ __global__ void splitk_reduce_kernel(void* __restrict__ out, const float* __rest
     if (N_ACC == 2) a1 += bias[N + f];
   }
   float y = a0;
-  if (EPI == EPI_GATED) y = a0 / (1.0f + __expf(-a0)) * a1;
+  if (EPI == EPI_GATED) y = silu_times(a0, a1);
   if (EPI == EPI_RESIDUAL) {
     ((float*)out)[idx] += y;
   } else if (out_bf16) {
@@ -1208,6 +1356,25 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
   return launch_status();
 }
 
+// Whether a tokens-on-M product runs on pairs of CTAs: a wide product over at least two token
+// tiles with more tiles than SMs, and deep (ALOFA_GEMM_PAIR=0 keeps one CTA per tile).  Measured
+// on 2,048 tokens: depth 3,584 x 37,888 weight rows 477 against 540 us, 18,944 x 3,584 233 against
+// 238 us; at depth 896 the pair's epilogue is not hidden behind its shorter MMA phase and one CTA
+// per tile is faster (33 against 36 us for 9,728 weight rows), so shallow products stay there.
+constexpr int PAIR_MIN_DEPTH = 2048;
+static bool pair_product(int bnf, int splits, int T, int N, int K, int epi) {
+  static int sms = 0, allowed = -1;
+  if (allowed < 0) {
+    const char* env = getenv("ALOFA_GEMM_PAIR");
+    allowed = (env && env[0] == '0') ? 0 : 1;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 0;
+  }
+  if (!allowed || sms < 2 || bnf != 256 || splits != 1 || (N & 3) || T <= 128 || K < PAIR_MIN_DEPTH) return false;
+  const int feats = epi == EPI_GATED ? 128 : 256;
+  return (long long)((N + feats - 1) / feats) * ((T + 127) / 128) > sms;
+}
+
 template <int BNF, int EPI>
 static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& args, int splits, cudaStream_t stream) {
   constexpr size_t STAGE = (size_t)128 * BK * 2 + (size_t)BNF * BK * 2;
@@ -1238,7 +1405,7 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
     prefer_max_shared(gemm_tc_tokens_kernel<BNF, EPI>);
     configured = true;
   }
-  if (BNF == 256 && splits == 1 && (args.N & 3) == 0 && args.K <= 2048) {
+  if (BNF == 256 && splits == 1 && (args.N & 3) == 0 && (args.K <= 2048 || args.pair)) {
     // More tiles than SMs and a shallow depth, where a tile's epilogue is a large share of its
     // time: one resident CTA per SM works through the tiles, epilogues beside MMAs.  (Deep
     // products measured faster as two CTAs per SM, which keep four stages in flight per SM.)
@@ -1250,6 +1417,32 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
       if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 0;
     }
     const int n_tiles = (int)(grid.x * grid.y);
+    if (args.pair) {
+      static bool configured_2 = false;
+      constexpr size_t SMEM_2 = (size_t)PAIR_STAGES * ((size_t)128 * BK * 2 + (size_t)128 * BK * 2) + STAGING_BYTES + 1024;
+      if (!configured_2) {
+        if (cudaFuncSetAttribute(gemm_tc_tokens_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_2) != cudaSuccess)
+          return ALOFA_ERR_LAUNCH;
+        prefer_max_shared(gemm_tc_tokens_pair_kernel<EPI>);
+        configured_2 = true;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(sms / 2 * 2);
+      cfg.blockDim = dim3(NUM_THREADS);
+      cfg.dynamicSmemBytes = SMEM_2;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+      attr[1].id = cudaLaunchAttributeClusterDimension;
+      attr[1].val.clusterDim.x = 2;
+      attr[1].val.clusterDim.y = 1;
+      attr[1].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 2;
+      cudaLaunchKernelEx(&cfg, gemm_tc_tokens_pair_kernel<EPI>, mw, mx, args);
+      return launch_status();
+    }
     if (persistent && sms > 0 && n_tiles > sms) {
       static bool configured_p = false;
       constexpr size_t SMEM_P = (size_t)PERSISTENT_STAGES * STAGE + STAGING_BYTES + 1024;
@@ -1345,8 +1538,9 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   const bool tokens_on_m = bn < 0;
   const int bnf = -bn;
   CUtensorMap mw, mx;
+  const bool pair = tokens_on_m && pair_product(bnf, splits, T, N, K, epi);
   if (tokens_on_m) {
-    const int w_box = (epi == EPI_GATED) ? bnf / 2 : bnf;
+    const int w_box = (epi == EPI_GATED || pair) ? bnf / 2 : bnf;
     if (!make_map(&mw, w, w_rows, K, w_box) || !make_map(&mx, x, T, K, 128)) return ALOFA_ERR_ARGUMENT;
   } else if (!make_map(&mw, w, w_rows, K, BM) || !make_map(&mx, x, T, K, bn)) {
     return ALOFA_ERR_ARGUMENT;
@@ -1362,6 +1556,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   args.k_slices_per_split = (total_slices + splits - 1) / splits;
   splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;  // no empty split
   args.out_bf16 = out_bf16;
+  args.pair = pair ? 1 : 0;
   args.status = status;
   args.b_kind = b_kind;
   args.b_src = b_src;

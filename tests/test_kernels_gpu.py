@@ -246,7 +246,10 @@ def test_qkv_product_rotates_and_stores(ops, hd, nh, nkv, k):
                                    (5, 128, 64, -64, 1), (130, 379, 96, -128, 1), (300, 1152, 896, -256, 3), (513, 650, 320, -256, 2), (257, 200, 240, -128, 1),
                                    (5, 40000, 96, -256, 1), (130, 39996, 64, -256, 1),  # more tiles than SMs: one resident CTA per SM, tiles cut evenly
                                    (8, 2048, 1536, 16, 8), (8, 1536, 8960, 16, 12), (64, 1536, 1536, 64, 6), (300, 8960, 1536, -256, 1),  # widths of the 1.5B shape
-                                   (8, 4608, 3584, 16, 4), (8, 3584, 18944, 16, 5), (33, 3584, 3584, 64, 2), (200, 4608, 3584, -256, 1)])  # and of the 7B shape
+                                   (8, 4608, 3584, 16, 4), (8, 3584, 18944, 16, 5), (33, 3584, 3584, 64, 2), (200, 4608, 3584, -256, 1),  # and of the 7B shape
+                                   # deep and wide over several token tiles: pairs of CTAs with MMAs of M = 256 (ragged depth and width, a pair's
+                                   # second token tile partly or wholly past the end)
+                                   (300, 13000, 2056, -256, 1), (129, 20000, 2048, -256, 1)])
 def test_gemm_tc_epilogues_and_split_depth(ops, shape):
     """The tcgen05 product against fp64: every epilogue, ragged sizes, split
     depth; weights on the M side (tile > 0) and tokens on the M side (tile < 0)."""
