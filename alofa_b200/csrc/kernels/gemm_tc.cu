@@ -47,6 +47,11 @@ enum { B_ROWS = 0, B_MERGED_SPLITS = 1, B_NORMED = 2 };
 constexpr int BM = 128;        // features per CTA (UMMA M)
 constexpr int BK = 64;         // k-slice: 64 bf16 = one 128-byte swizzle row
 constexpr int NUM_THREADS = 192;  // warp 0 producer, warp 1 MMA, warps 2-5 epilogue
+// The kernels with the tokens on the M side have eight epilogue warps, two to each quarter of the
+// accumulator's lanes (a warp reads the lanes 32 (w % 4) ... of tensor memory): each takes half of
+// the columns and half of the rows' stores.  One warp per scheduler left the epilogue waiting on
+// its own instructions' latency for most of its time.
+constexpr int TOKENS_THREADS = 320;  // warp 0 producer, warp 1 MMA, warps 2-9 epilogue
 
 // ---------------------------------------------------------------------------
 // The kernel
@@ -630,11 +635,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // The epilogue of a 128-token tile whose width is a multiple of 4: warp q owns
 // rows [32q, 32q + 32) of the accumulator at `tmem_acc`; `staging` holds
-// 4 x 32 rows of 132 floats.  `release` (optional, one arrival per warp) is signalled
-// once the accumulator has been read out.
+// 4 x 32 rows of 132 floats.  Two warps share a quarter: `half` (0 or 1) takes columns
+// [64 half, 64 half + 64) of every 128 and rows [16 half, 16 half + 16) of the stores; they meet
+// on the named barrier 8 + q.  `release` (optional, one arrival per warp) is signalled once the
+// accumulator has been read out.
+__device__ __forceinline__ void quarter_sync(int q) { asm volatile("bar.sync %0, 64;" ::"r"(8 + q) : "memory"); }
+// All eight epilogue warps: true when every thread brought true (one verdict for all, so that they
+// go on, or give up, together).
+__device__ __forceinline__ bool epilogue_warps_agree(bool ok) {
+  uint32_t any_bad;
+  asm volatile(
+      "{\n\t.reg .pred p, r;\n\t"
+      "setp.eq.u32 p, %1, 0;\n\t"
+      "bar.red.or.pred r, 1, 256, p;\n\t"
+      "selp.u32 %0, 1, 0, r;\n\t}"
+      : "=r"(any_bad)
+      : "r"((uint32_t)ok)
+      : "memory");
+  return any_bad == 0;
+}
+
 template <int BNF, int EPI>
-__device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uint32_t tmem_base, float* staging, int q, int lane, int f0, int t0,
-                                                       int n_splits, int split_index, uint64_t* release, uint32_t release_in_cluster = 0) {
+__device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uint32_t tmem_base, float* staging, int q, int half, int lane, int f0,
+                                                       int t0, int n_splits, int split_index, uint64_t* release, uint32_t release_in_cluster = 0) {
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr int FEATS = GATED ? BNF / 2 : BNF;
   // The accumulator rows go through shared memory so
@@ -650,7 +673,7 @@ __device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uin
   for (int cb = 0; cb < FEATS; cb += 128) {
     if (f0 + cb >= N) break;
 #pragma unroll 1
-    for (int c0 = 0; c0 < 128 && cb + c0 < FEATS; c0 += 16) {
+    for (int c0 = half * 64; c0 < half * 64 + 64 && cb + c0 < FEATS; c0 += 16) {
       const int f = f0 + cb + c0;
       if (f >= N) break;
       uint32_t r0[16], r1[16];
@@ -680,18 +703,20 @@ __device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uin
       if (release_in_cluster) mbar_arrive_in_cluster(release_in_cluster);
       else mbar_arrive(release);
     }
+    quarter_sync(q);  // both halves of the columns are staged
     const int f = f0 + cb + lane * 4;  // this lane's four features of every row
     const bool f_ok = f < N && cb + lane * 4 < FEATS;  // N % 4 == 0: a group is inside or outside as a whole
-    const int rows = min(32, args.T - (t0 + q * 32));
+    const int r_lo = half * 16;
+    const int rows = min(r_lo + 16, args.T - (t0 + q * 32));  // this warp stores rows [r_lo, rows)
     if (f_ok) {
       if (split) {
         float* p = args.partial + (size_t)split_index * plane + (size_t)(t0 + q * 32) * N + f;
 #pragma unroll 4
-        for (int r = 0; r < rows; ++r) *reinterpret_cast<float4*>(p + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
+        for (int r = r_lo; r < rows; ++r) *reinterpret_cast<float4*>(p + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
       } else if (EPI == EPI_RESIDUAL) {
         float* o = (float*)args.out + (size_t)(t0 + q * 32) * N + f;
-#pragma unroll 1
-        for (int rb = 0; rb < 32; rb += 16) {  // sixteen rows at a time: all their loads in flight, then the stores
+        {  // sixteen rows: all their loads in flight, then the stores
+          const int rb = r_lo;
           float4 b[16];
 #pragma unroll
           for (int r = 0; r < 16; ++r)
@@ -706,7 +731,7 @@ __device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uin
       } else if (args.out_bf16) {
         bf16* o = (bf16*)args.out + (size_t)(t0 + q * 32) * N + f;
 #pragma unroll 4
-        for (int r = 0; r < rows; ++r) {
+        for (int r = r_lo; r < rows; ++r) {
           const float4 a = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
           __nv_bfloat162 lo = __floats2bfloat162_rn(a.x, a.y), hi = __floats2bfloat162_rn(a.z, a.w);
           *reinterpret_cast<uint2*>(o + (size_t)r * N) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
@@ -714,10 +739,10 @@ __device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uin
       } else {
         float* o = (float*)args.out + (size_t)(t0 + q * 32) * N + f;
 #pragma unroll 4
-        for (int r = 0; r < rows; ++r) *reinterpret_cast<float4*>(o + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
+        for (int r = r_lo; r < rows; ++r) *reinterpret_cast<float4*>(o + (size_t)r * N) = *reinterpret_cast<const float4*>(stage + r * PITCH + lane * 4);
       }
     }
-    __syncwarp();
+    quarter_sync(q);  // the staged rows are stored: the next 128 columns, or the next tile, may overwrite them
   }
 }
 
@@ -732,7 +757,7 @@ __device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uin
 // and writes runs of 16 consecutive features with 16-byte stores.
 // ---------------------------------------------------------------------------
 template <int BNF, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+__global__ void __launch_bounds__(TOKENS_THREADS, 2)
 gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args, const int stages) {
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr int FEATS = GATED ? BNF / 2 : BNF;  // output features per CTA
@@ -816,14 +841,15 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       umma_commit(&acc_bar);
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3, half = (warp - 2) >> 2;
     const int t = t0 + q * 32 + lane;
     bool ok = mbar_wait(&acc_bar, 0, &abort_flag);
     ok = __all_sync(0xffffffffu, ok);
+    ok = epilogue_warps_agree(ok);  // the quarter's other warp must not be left waiting for this one
     tc_fence_after();
     const bool staged = (args.N & 3) == 0 && !(GATED && gridDim.z > 1);
     if (ok && staged && t0 + q * 32 < args.T) {
-      tokens_epilogue_staged<BNF, EPI>(args, tmem_base, reinterpret_cast<float*>(tiles), q, lane, f0, t0, (int)gridDim.z, (int)blockIdx.z, nullptr);
+      tokens_epilogue_staged<BNF, EPI>(args, tmem_base, reinterpret_cast<float*>(tiles), q, half, lane, f0, t0, (int)gridDim.z, (int)blockIdx.z, nullptr);
     } else if (ok && t0 + q * 32 < args.T) {
       // widths that are no multiple of 4 (or gated partial sums): element-wise, straight from the registers
       const bool split = gridDim.z > 1;
@@ -831,7 +857,7 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       const int N = args.N;
       const size_t plane = (size_t)args.T * N;
 #pragma unroll 1
-      for (int c0 = 0; c0 < FEATS; c0 += 16) {
+      for (int c0 = half * 16; c0 < FEATS; c0 += 32) {  // the quarter's two warps take the runs of 16 columns in turn
         const int f = f0 + c0;
         if (f >= N) break;
         uint32_t r0[16], r1[16];
@@ -943,7 +969,7 @@ constexpr int PERSISTENT_STAGES = 3;
 constexpr int STAGING_BYTES = 4 * 32 * 132 * 4;  // the epilogue's padded rows
 
 template <int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(TOKENS_THREADS, 1)
 gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args) {
   constexpr int BNF = 256;
   constexpr bool GATED = EPI == EPI_GATED;
@@ -973,7 +999,7 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_free[b], 4);  // the epilogue warps
+      mbar_init(&acc_free[b], 8);  // the epilogue warps
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1045,17 +1071,17 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3, half = (warp - 2) >> 2;
     int j = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
       const int buf = j & 1;
       const int f0 = (tile % n_ftiles) * FEATS, t0 = (tile / n_ftiles) * 128;
       bool ok = mbar_wait(&acc_full[buf], (j >> 1) & 1, &abort_flag);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!epilogue_warps_agree(ok)) break;
       tc_fence_after();
       if (t0 + q * 32 < args.T) {
-        tokens_epilogue_staged<BNF, EPI>(args, tmem_base + buf * BNF, staging, q, lane, f0, t0, 1, 0, &acc_free[buf]);
+        tokens_epilogue_staged<BNF, EPI>(args, tmem_base + buf * BNF, staging, q, half, lane, f0, t0, 1, 0, &acc_free[buf]);
       } else {
         tc_fence_before();
         __syncwarp();
@@ -1087,7 +1113,7 @@ gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, cons
 constexpr int PAIR_STAGES = 4;
 
 template <int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(TOKENS_THREADS, 1)
 gemm_tc_tokens_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args) {
   constexpr int BNF = 256;
   constexpr bool GATED = EPI == EPI_GATED;
@@ -1120,7 +1146,7 @@ gemm_tc_tokens_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_free[b], 8);  // the epilogue warps of both CTAs
+      mbar_init(&acc_free[b], 16);  // the epilogue warps of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1188,18 +1214,18 @@ gemm_tc_tokens_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3, half = (warp - 2) >> 2;
     int j = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++j) {
       const int buf = j & 1;
       const int f0 = (tile % n_ftiles) * FEATS, t0 = (tile / n_ftiles) * 256 + (int)rank * 128;
       bool ok = mbar_wait(&acc_full[buf], (j >> 1) & 1, &abort_flag);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!epilogue_warps_agree(ok)) break;
       tc_fence_after();
       const uint32_t free_bar = in_cluster_cta(&acc_free[buf], 0);
       if (t0 + q * 32 < args.T) {
-        tokens_epilogue_staged<BNF, EPI>(args, tmem_base + buf * BNF, staging, q, lane, f0, t0, 1, 0, nullptr, free_bar);
+        tokens_epilogue_staged<BNF, EPI>(args, tmem_base + buf * BNF, staging, q, half, lane, f0, t0, 1, 0, nullptr, free_bar);
       } else {
         tc_fence_before();
         __syncwarp();
@@ -1359,9 +1385,10 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArg
 // Whether a tokens-on-M product runs on pairs of CTAs: a wide product over at least two token
 // tiles with more tiles than SMs, and deep (ALOFA_GEMM_PAIR=0 keeps one CTA per tile).  Measured
 // on 2,048 tokens: depth 3,584 x 37,888 weight rows 477 against 540 us, 18,944 x 3,584 233 against
-// 238 us; at depth 896 the pair's epilogue is not hidden behind its shorter MMA phase and one CTA
-// per tile is faster (33 against 36 us for 9,728 weight rows), so shallow products stay there.
-constexpr int PAIR_MIN_DEPTH = 2048;
+// 238 us, depth 1,536 x 17,920 rows 85 against 92 us; at depth 896 the pair's epilogue is not
+// hidden behind its shorter MMA phase and one CTA per tile is as fast or faster (32.7 against
+// 33.9 us for 9,728 weight rows), so shallow products stay there.
+constexpr int PAIR_MIN_DEPTH = 1024;
 static bool pair_product(int bnf, int splits, int T, int N, int K, int epi) {
   static int sms = 0, allowed = -1;
   if (allowed < 0) {
@@ -1428,7 +1455,7 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
       }
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(sms / 2 * 2);
-      cfg.blockDim = dim3(NUM_THREADS);
+      cfg.blockDim = dim3(TOKENS_THREADS);
       cfg.dynamicSmemBytes = SMEM_2;
       cfg.stream = stream;
       cudaLaunchAttribute attr[2];
@@ -1452,11 +1479,11 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
         prefer_max_shared(gemm_tc_tokens_persistent_kernel<EPI>);
         configured_p = true;
       }
-      launch_dep(gemm_tc_tokens_persistent_kernel<EPI>, dim3(sms), NUM_THREADS, SMEM_P, stream, mw, mx, args);
+      launch_dep(gemm_tc_tokens_persistent_kernel<EPI>, dim3(sms), TOKENS_THREADS, SMEM_P, stream, mw, mx, args);
       return launch_status();
     }
   }
-  launch_dep(gemm_tc_tokens_kernel<BNF, EPI>, grid, NUM_THREADS, smem, stream, mw, mx, args, stages);
+  launch_dep(gemm_tc_tokens_kernel<BNF, EPI>, grid, TOKENS_THREADS, smem, stream, mw, mx, args, stages);
   return launch_status();
 }
 

@@ -249,7 +249,7 @@ def test_qkv_product_rotates_and_stores(ops, hd, nh, nkv, k):
                                    (8, 4608, 3584, 16, 4), (8, 3584, 18944, 16, 5), (33, 3584, 3584, 64, 2), (200, 4608, 3584, -256, 1),  # and of the 7B shape
                                    # deep and wide over several token tiles: pairs of CTAs with MMAs of M = 256 (ragged depth and width, a pair's
                                    # second token tile partly or wholly past the end)
-                                   (300, 13000, 2056, -256, 1), (129, 20000, 2048, -256, 1)])
+                                   (300, 13000, 2056, -256, 1), (129, 20000, 1024, -256, 1)])
 def test_gemm_tc_epilogues_and_split_depth(ops, shape):
     """The tcgen05 product against fp64: every epilogue, ragged sizes, split
     depth; weights on the M side (tile > 0) and tokens on the M side (tile < 0)."""
