@@ -620,18 +620,28 @@ static size_t attention_smem_bytes(int stages, int table_entries) {
 
 ALOFA_API int alofa_attention_head_dim() { return HD; }
 
-// How many CTAs of the decode kernel (four warps) the device holds at a time: what a caller
-// sizes the key splits by, so that a step's CTAs are resident together.  0 when it cannot be asked.
-ALOFA_API int alofa_attention_decode_slots(int page_size) {
+// How many CTAs of the decode kernel with `warps` warps (4, or 8: head size 64 on pages of whole
+// key blocks, taken when a launch has one split of a multiple of 512 keys) the device holds at a
+// time: what a caller sizes the key splits by, so that a step's CTAs are resident together.
+// 0 when that kernel does not exist here or the device cannot be asked.
+ALOFA_API int alofa_attention_decode_slots(int page_size, int warps) {
   const bool tma = (HD == 64 || HD == 128) && page_size % BLOCK_N == 0;
   int device = 0, sms = 0, per_sm = 0;
   if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-  const size_t smem = decode_smem_bytes(4, tma);
   cudaError_t rc;
-  if (tma) {
+  if (warps == 8) {
+    if (!tma || HD != 64) return 0;
+    const size_t smem = decode_smem_bytes(8, true);
+    cudaFuncSetAttribute(attention_decode_kernel<8, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<8, true, true>, 256, smem);
+  } else if (warps != 4) {
+    return 0;
+  } else if (tma) {
+    const size_t smem = decode_smem_bytes(4, true);
     cudaFuncSetAttribute(attention_decode_kernel<4, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<4, true, true>, 128, smem);
   } else {
+    const size_t smem = decode_smem_bytes(4, false);
     cudaFuncSetAttribute(attention_decode_kernel<4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<4, false, true>, 128, smem);
   }
@@ -721,7 +731,10 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
       memset(&map_v, 0, sizeof(map_v));
     }
     int rc;
-    if (split_keys % (4 * BLOCK_N) == 0)
+    if (tma && HD == 64 && n_splits == 1 && split_keys % (8 * BLOCK_N) == 0)
+      // one split per request and KV head, a multiple of 512 keys: eight warps (see alofa_attention_decode_slots)
+      rc = launch_decode<8, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
+    else if (split_keys % (4 * BLOCK_N) == 0)
       rc = tma ? launch_decode<4, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<4, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
     else
       rc = tma ? launch_decode<2, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<2, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);

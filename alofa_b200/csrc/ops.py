@@ -94,7 +94,7 @@ def _attention(head_dim: int):
         lib.alofa_attention_combine.restype = _I
         lib.alofa_attention_combine.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _P]
         lib.alofa_attention_decode_slots.restype = _I
-        lib.alofa_attention_decode_slots.argtypes = [_I]
+        lib.alofa_attention_decode_slots.argtypes = [_I, _I]
         _libs[key] = lib
     return lib
 
@@ -102,12 +102,13 @@ def _attention(head_dim: int):
 _decode_slots = {}
 
 
-def attention_decode_slots(head_dim: int, page_size: int) -> int:
-    """How many CTAs of the decode attention kernel the device holds at a
-    time (asked once per head size and kind of page)."""
-    key = (head_dim, page_size % 64 == 0)
+def attention_decode_slots(head_dim: int, page_size: int, warps: int = 4) -> int:
+    """How many CTAs of the decode attention kernel with ``warps`` warps (4 or
+    8) the device holds at a time, 0 when that kernel is not built for this
+    head size and kind of page (asked once each)."""
+    key = (head_dim, page_size % 64 == 0, warps)
     if key not in _decode_slots:
-        _decode_slots[key] = max(1, _attention(head_dim).alofa_attention_decode_slots(page_size))
+        _decode_slots[key] = max(0, _attention(head_dim).alofa_attention_decode_slots(page_size, warps))
     return _decode_slots[key]
 
 

@@ -152,6 +152,11 @@ class GQAttention(Part):
     # 2,048 keys: 1.58 -> 1.47 ms per step for 14 heads of 64 on 2, 5.90 -> 5.08 ms for 28 heads
     # of 128 on 4).
     SPLIT_KEYS = 256
+    # With three tenths as many (request, KV head) pairs as SMs or more, in steps of more than 16
+    # tokens, and where the kernel has its eight-warp form (head size 64, pages of whole key blocks):
+    # one split per pair, a multiple of the eight warps' 512 keys (batch 64: 1.40 -> 1.34 ms; batch 32:
+    # 1.065 -> 1.027; the merge kernel and the partial sums go; below that the shorter splits win).
+    WIDE_SPLIT_KEYS = 512
     # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.
     # Measured at 2,048-token prompts the round trip of the partial sums costs more than the
     # long tiles' tail saves (4.9 ms against 4.5 ms for the step), so it is off.
@@ -174,12 +179,19 @@ class GQAttention(Part):
             per_split = self.SPLIT_KEYS
             group_size = self.nh // self.nkv
             if ctx.decode_only and group_size <= 16:
-                resident = ops.attention_decode_slots(self.hd, group.page_size) // max(1, ctx.n_seqs * self.nkv)
+                pairs = max(1, ctx.n_seqs * self.nkv)
+                wide = ops.attention_decode_slots(self.hd, group.page_size, 8)
                 blocks = -(-longest // self.SPLIT_KEYS)
-                if ctx.n_tokens <= 16 and blocks <= 4 * self.MERGE_IN_PRODUCT_SPLITS:
-                    # few enough splits that the output product merges them, while a warp has at most four blocks
-                    resident = min(resident, self.MERGE_IN_PRODUCT_SPLITS)
-                per_split = self.SPLIT_KEYS * -(-blocks // max(1, resident))
+                if ctx.n_tokens > 16 and 10 * pairs >= 3 * wide > 0:
+                    # enough (request, KV head) pairs to keep the SMs busy with one CTA of eight warps each: the
+                    # whole context in one split, no partial sums and no kernel that merges them
+                    per_split = self.WIDE_SPLIT_KEYS * -(-longest // self.WIDE_SPLIT_KEYS)
+                else:
+                    resident = max(1, ops.attention_decode_slots(self.hd, group.page_size) // pairs)
+                    if ctx.n_tokens <= 16 and blocks <= 4 * self.MERGE_IN_PRODUCT_SPLITS:
+                        # few enough splits that the output product merges them, while a warp has at most four blocks
+                        resident = min(resident, self.MERGE_IN_PRODUCT_SPLITS)
+                    per_split = self.SPLIT_KEYS * -(-blocks // resident)
             if not ctx.decode_only:
                 per_split = self.PROMPT_SPLIT_KEYS or (1 << 30)
             if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):

@@ -96,17 +96,20 @@ def test_decode_with_more_work_than_the_device_holds_at_once(folders, name, monk
     vocab = configs()[name][0].vocab_size
     rng = np.random.default_rng(5)
     lens = [1, 63, 255, 256, 257, 511, 512, 513, 767, 768, 769, 900] + [int(n) for n in rng.integers(2, 900, 8)]
-    n_new = 3
+    n_new = 4
     seqs = [[int(t) for t in rng.integers(0, vocab, n + n_new)] for n in lens]
     want = [plain.forward(s, wts, cfg) for s in seqs]
-    asked = []
+    asked, one_wide_split = [], []
     real = ops.attention_bf16
 
     def watch(*args, **kwargs):
         asked.append(args[17])  # split_keys
+        if args[16] == 1 and args[17] % 512 == 0:
+            one_wide_split.append(args[17])
         return real(*args, **kwargs)
 
     monkeypatch.setattr(ops, "attention_bf16", watch)
+    real_slots = ops.attention_decode_slots
     for graphs in (True, False):
         runner = runner_for(folders[name], graphs, pages=20 * 16, max_requests=20, max_tokens=20 * 1024)
         slots = [runner.admit(i) for i in range(len(seqs))]
@@ -115,13 +118,17 @@ def test_decode_with_more_work_than_the_device_holds_at_once(folders, name, monk
                 runner.forward([StepEntry(slots[i], seqs[i][lo : min(lens[i], lo + 700)], [])])
         got = [[] for _ in seqs]
         del asked[:]
-        for step, (live, room) in enumerate(((range(20), 40), (range(4, 12), 16), (range(4, 12), 16))):
-            monkeypatch.setattr(ops, "attention_decode_slots", lambda hd, page, room=room: room)
+        # (requests, room for four-warp CTAs, room for eight-warp CTAs): twenty with splits of 512 merged by the combine
+        # kernel; eight, twice, whose splits the output product merges; twenty with one split each on eight warps (head 64)
+        for step, (live, room, wide) in enumerate(((range(20), 40, 0), (range(4, 12), 16, 0), (range(4, 12), 16, 0), (range(19), 40, 40))):  # nineteen: a graph of its own
+            monkeypatch.setattr(ops, "attention_decode_slots",
+                                lambda hd, page, warps=4, room=room, wide=wide: room if warps == 4 else min(wide, real_slots(hd, page, 8)))
             logits = runner.forward([StepEntry(slots[i], [seqs[i][lens[i] + len(got[i])]], [0]) for i in live]).float().cpu().numpy()
             for row, i in zip(logits, live):
                 got[i].append(row)
         runner.check_status()
         assert max(asked) >= 512 and GQAttention.SPLIT_KEYS == 256, f"splits asked for: {sorted(set(asked))}"
+        assert one_wide_split or name != "P", "head size 64: the last step should have run one split per request on eight warps"
         for i, rows in enumerate(got):
             ref = want[i][lens[i] : lens[i] + len(rows)]
             bound = 2e-2 * max(1.0, float(np.abs(ref).max()))
