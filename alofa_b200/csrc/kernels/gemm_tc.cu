@@ -1693,6 +1693,40 @@ ALOFA_API int alofa_gemm_tc_rope(const void* x, const void* w, const float* bias
   return launch_tc<16, EPI_ROPE>(mw, mx, args, splits, stream);
 }
 
+// How many clusters of `splits` CTAs of the q/k/v kernel (16 tokens, depth split over a cluster
+// along z; `normed`: with the norm folded in) the device holds at a time - a GPC places only whole
+// clusters, so eight-CTA clusters may leave SMs idle that six-CTA clusters fill.  A caller keeps all
+// of a product's clusters in one wave by it.  0 when the device cannot be asked.
+template <int MODE>
+static int resident_rope_clusters(int splits) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<16, EPI_ROPE, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess) return 0;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, 1, (unsigned)splits);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = 200 * 1024 + 1024;  // what a launch asks for at most: the ring and the pushed accumulators
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned)splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<16, EPI_ROPE, MODE>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+ALOFA_API int alofa_gemm_tc_rope_resident_clusters(int splits, int normed) {
+  if (splits < 1 || splits > 8) return 0;
+  return normed ? resident_rope_clusters<MODE_NORMED>(splits) : resident_rope_clusters<MODE_CLUSTER>(splits);
+}
+
 // How many splits alofa_gemm_tc will really use (it never leaves one empty).
 ALOFA_API int alofa_gemm_tc_splits(int K, int splits) {
   const int total = (K + BK - 1) / BK;

@@ -78,6 +78,8 @@ def _gemm_tc():
         lib.alofa_gemm_tc_reduces_in_cluster.argtypes = [_I, _I, _I]
         lib.alofa_gemm_tc_rope.restype = _I
         lib.alofa_gemm_tc_rope.argtypes = [_P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _F, _P, _P, _P]
+        lib.alofa_gemm_tc_rope_resident_clusters.restype = _I
+        lib.alofa_gemm_tc_rope_resident_clusters.argtypes = [_I, _I]
         lib.alofa_gemm_tc_splits.restype = _I
         lib.alofa_gemm_tc_splits.argtypes = [_I, _I]
         _libs["gemm_tc"] = lib
@@ -304,6 +306,23 @@ def sample_chain(tokens, logits, work, fparams, iparams, bias_start, bias_index,
         ),
         "sample_chain", f"vocab={vocab}",
     )
+
+
+_rope_clusters = {}
+
+
+def gemm_tc_rope_splits(m_tiles: int, normed: bool, most: int = 8) -> int:
+    """The largest depth split (a cluster of that many CTAs per 128-row tile)
+    of the q/k/v kernel for which all ``m_tiles`` clusters are resident
+    together: a GPC holds whole clusters only, so the answer comes from the
+    runtime's occupancy of clusters, asked once per size."""
+    for splits in range(most, 1, -1):
+        key = (splits, bool(normed))
+        if key not in _rope_clusters:
+            _rope_clusters[key] = _gemm_tc().alofa_gemm_tc_rope_resident_clusters(splits, 1 if normed else 0)
+        if _rope_clusters[key] >= m_tiles:
+            return splits
+    return 1
 
 
 def gemm_tc_splits(k: int, splits: int) -> int:

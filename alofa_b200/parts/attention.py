@@ -102,12 +102,16 @@ class GQAttention(Part):
         lin = self.qkv if writes else self.q_only
         q = ctx.buf((n, self.q_dim), dt)
         # a handful of tokens: product, bias, rotation and the cache write in one kernel
-        # (its depth split over a cluster of up to eight CTAs, as many as keep all tiles in one wave of the GPU)
-        # and only while a CTA then has a few k-slices: on deep products (3,584 wide) the cluster measured slower
-        depth_splits = max(1, min(8, fast_linear.SMS // -(-lin.weight.shape[0] // 128)))
+        # (its depth split over a cluster of up to eight CTAs: the largest for which every tile's cluster is
+        # resident at once - a GPC holds whole clusters only, 16 clusters of 8 ran in two waves where 16 of 6 run
+        # in one: 1.52 -> 1.41 ms per step at hidden 1,536) and only while a CTA then has a few k-slices: on deep
+        # products (3,584 wide) the cluster measured slower
+        lazy = None if isinstance(x, torch.Tensor) else x
+        depth_splits = 1
+        if vectorised and n <= 16 and x.dtype == torch.bfloat16:
+            depth_splits = ops.gemm_tc_rope_splits(-(-lin.weight.shape[0] // 128), lazy is not None)
         shallow = -(-(-(-self.hidden // fast_linear.K_SLICE)) // depth_splits) <= 4
         one_kernel = vectorised and shallow and n <= 16 and lin.weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
-        lazy = None if isinstance(x, torch.Tensor) else x
         done = False
         if lazy is not None:
             if one_kernel and lazy.fits_kernel():
