@@ -621,7 +621,7 @@ static size_t attention_smem_bytes(int stages, int table_entries) {
 ALOFA_API int alofa_attention_head_dim() { return HD; }
 
 // How many CTAs of the decode kernel with `warps` warps (4, or 8: head size 64 on pages of whole
-// key blocks, taken when a launch has one split of a multiple of 512 keys) the device holds at a
+// key blocks, taken when a launch's splits are a multiple of 512 keys) the device holds at a
 // time: what a caller sizes the key splits by, so that a step's CTAs are resident together.
 // 0 when that kernel does not exist here or the device cannot be asked.
 ALOFA_API int alofa_attention_decode_slots(int page_size, int warps) {
@@ -731,8 +731,8 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
       memset(&map_v, 0, sizeof(map_v));
     }
     int rc;
-    if (tma && HD == 64 && n_splits == 1 && split_keys % (8 * BLOCK_N) == 0)
-      // one split per request and KV head, a multiple of 512 keys: eight warps (see alofa_attention_decode_slots)
+    if (tma && HD == 64 && split_keys % (8 * BLOCK_N) == 0)
+      // splits of a multiple of 512 keys: eight warps, one CTA per SM (see alofa_attention_decode_slots)
       rc = launch_decode<8, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
     else if (split_keys % (4 * BLOCK_N) == 0)
       rc = tma ? launch_decode<4, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<4, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);

@@ -156,10 +156,11 @@ class GQAttention(Part):
     # 2,048 keys: 1.58 -> 1.47 ms per step for 14 heads of 64 on 2, 5.90 -> 5.08 ms for 28 heads
     # of 128 on 4).
     SPLIT_KEYS = 256
-    # With three tenths as many (request, KV head) pairs as SMs or more, in steps of more than 16
-    # tokens, and where the kernel has its eight-warp form (head size 64, pages of whole key blocks):
-    # one split per pair, a multiple of the eight warps' 512 keys (batch 64: 1.40 -> 1.34 ms; batch 32:
-    # 1.065 -> 1.027; the merge kernel and the partial sums go; below that the shorter splits win).
+    # Head size 64 on pages of whole key blocks has an eight-warp form of the kernel, one CTA per SM, whose
+    # splits grow by 512 keys: fewer, larger CTAs and fewer splits to merge (batch 8: nine splits of 256 keys
+    # 0.780 ms per step, five of 512 0.758; batch 12: 0.819 -> 0.788).  With three tenths as many (request, KV
+    # head) pairs as SMs or more, in steps of more than 16 tokens, one split per pair (batch 64: 1.40 -> 1.34 ms;
+    # batch 32: 1.065 -> 1.027; the merge kernel and the partial sums go).
     WIDE_SPLIT_KEYS = 512
     # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.
     # Measured at 2,048-token prompts the round trip of the partial sums costs more than the
@@ -185,17 +186,20 @@ class GQAttention(Part):
             if ctx.decode_only and group_size <= 16:
                 pairs = max(1, ctx.n_seqs * self.nkv)
                 wide = ops.attention_decode_slots(self.hd, group.page_size, 8)
-                blocks = -(-longest // self.SPLIT_KEYS)
-                if ctx.n_tokens > 16 and 10 * pairs >= 3 * wide > 0:
-                    # enough (request, KV head) pairs to keep the SMs busy with one CTA of eight warps each: the
-                    # whole context in one split, no partial sums and no kernel that merges them
-                    per_split = self.WIDE_SPLIT_KEYS * -(-longest // self.WIDE_SPLIT_KEYS)
+                # the unit a split grows by, and how many CTAs of that kernel are resident together
+                unit, room = (self.WIDE_SPLIT_KEYS, wide) if wide > 0 else (self.SPLIT_KEYS, ops.attention_decode_slots(self.hd, group.page_size))
+                if wide > 0 and ctx.n_tokens > 16 and 10 * pairs >= 3 * wide:
+                    # enough (request, KV head) pairs to keep the SMs busy with one CTA each: the whole context in
+                    # one split, no partial sums and no kernel that merges them
+                    per_split = unit * -(-longest // unit)
                 else:
-                    resident = max(1, ops.attention_decode_slots(self.hd, group.page_size) // pairs)
-                    if ctx.n_tokens <= 16 and blocks <= 4 * self.MERGE_IN_PRODUCT_SPLITS:
-                        # few enough splits that the output product merges them, while a warp has at most four blocks
-                        resident = min(resident, self.MERGE_IN_PRODUCT_SPLITS)
-                    per_split = self.SPLIT_KEYS * -(-blocks // resident)
+                    # as many splits as are resident together, by the longest context of this step (a graph keeps
+                    # what the step that recorded it chose; every length its bucket holds is covered either way)
+                    blocks = -(-max(1, ctx.max_kv_len) // unit)
+                    per_split = unit * -(-blocks // max(1, room // pairs))
+                    if ctx.n_tokens <= 16 and longest <= 4 * self.MERGE_IN_PRODUCT_SPLITS * self.SPLIT_KEYS:
+                        # few enough splits that the output product merges them, while a warp has at most a few blocks
+                        per_split = max(per_split, unit * -(-longest // (unit * self.MERGE_IN_PRODUCT_SPLITS)))
             if not ctx.decode_only:
                 per_split = self.PROMPT_SPLIT_KEYS or (1 << 30)
             if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):
