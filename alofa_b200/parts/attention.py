@@ -197,6 +197,8 @@ class GQAttention(Part):
                     # what the step that recorded it chose; every length its bucket holds is covered either way)
                     blocks = -(-max(1, ctx.max_kv_len) // unit)
                     per_split = unit * -(-blocks // max(1, room // pairs))
+                    if per_split >= blocks * unit:
+                        per_split = unit * -(-longest // unit)  # one split: let it reach to the end of the bucket, so that nothing is merged
                     if ctx.n_tokens <= 16 and longest <= 4 * self.MERGE_IN_PRODUCT_SPLITS * self.SPLIT_KEYS:
                         # few enough splits that the output product merges them, while a warp has at most a few blocks
                         per_split = max(per_split, unit * -(-longest // (unit * self.MERGE_IN_PRODUCT_SPLITS)))
