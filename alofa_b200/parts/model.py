@@ -6,6 +6,7 @@ entry whose cache is an earlier entry's reads that cache and writes nothing
 (layer order of the one shipped architecture: src/alofa/model/arch/qwen.mojo:1367-1372)."""
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..config.spec import ModelSpec
@@ -70,7 +71,11 @@ class Model:
             return None
         if not getattr(self.final_norm, "absorbs_pending", False):
             ctx.flush_pending()
-        x = self.final_norm.forward(ctx, h, ctx.logit_rows)
+        # every row wanted, in order (a decode step): no picking, and a norm that reads the stream as base + accumulator may
+        rows = ctx.logit_rows
+        if ctx.n_out == ctx.n_tokens and bool((ctx.host_field("logit_rows") == np.arange(ctx.n_tokens, dtype=np.int32)).all()):
+            rows = None
+        x = self.final_norm.forward(ctx, h, rows)
         ctx.close_stream()
         return self.head.forward(ctx, x)
 
