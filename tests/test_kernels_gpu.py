@@ -241,6 +241,20 @@ def test_qkv_product_rotates_and_stores(ops, hd, nh, nkv, k):
                                 kc, vc, dev(np.zeros(17, dtype=np.int32)), dev(np.zeros(17, dtype=np.int32)), table, nh, nkv, hd, 4), "more than 16 tokens"
 
 
+def test_qkv_cluster_size_is_what_the_device_holds_at_once(ops):
+    """The depth split of the q/k/v kernel: the largest cluster size for which
+    the runtime reports every tile's cluster resident together, so it can only
+    shrink as the tiles grow in number, and one tile gets the largest."""
+    sizes = [ops.gemm_tc_rope_splits(tiles, normed) for normed in (True, False) for tiles in (1, 9, 16, 24, 36, 74, 148, 400)]
+    for half in (sizes[:8], sizes[8:]):
+        assert half[0] == 8 and all(1 <= s <= 8 for s in half)
+        assert all(a >= b for a, b in zip(half, half[1:])), half
+        assert half[-1] == 1  # more tiles than SMs: no cluster of two fits them all
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for tiles, split in zip((1, 9, 16, 24, 36, 74), sizes[:6]):
+        assert tiles * split <= sms
+
+
 @pytest.mark.parametrize("shape", [(5, 128, 64, 16, 1), (33, 379, 96, 64, 1), (300, 1152, 896, 128, 3), (8, 896, 4864, 16, 19), (513, 640, 320, 256, 2),
                                    (8, 512, 896, 16, 3), (13, 200, 320, 16, 5), (16, 131, 512, 16, 8), (29, 640, 896, 32, 3),  # gated: the splits add up inside a cluster
                                    (5, 128, 64, -64, 1), (130, 379, 96, -128, 1), (300, 1152, 896, -256, 3), (513, 650, 320, -256, 2), (257, 200, 240, -128, 1),
