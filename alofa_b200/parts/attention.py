@@ -172,6 +172,32 @@ class GQAttention(Part):
     # the product would re-read too many partial outputs.
     MERGE_IN_PRODUCT_SPLITS = 16
 
+    @classmethod
+    def decode_split_keys(cls, n_tokens: int, pairs: int, longest: int, longest_now: int, wide_slots: int, slots: int) -> int:
+        """Keys per CTA of a decode-only step.  ``pairs``: (request, KV head)
+        pairs; ``longest``: the context the launch must cover (a graph's
+        bucket), ``longest_now``: the longest context of this step;
+        ``wide_slots`` / ``slots``: CTAs of the eight-warp / four-warp kernel
+        the device holds at a time (0: that kernel is not built here)."""
+        pairs = max(1, pairs)
+        # the unit a split grows by, and how many CTAs of that kernel are resident together
+        unit, room = (cls.WIDE_SPLIT_KEYS, wide_slots) if wide_slots > 0 else (cls.SPLIT_KEYS, slots)
+        whole = unit * -(-longest // unit)
+        if wide_slots > 0 and n_tokens > 16 and 10 * pairs >= 3 * wide_slots:
+            # enough pairs to keep the SMs busy with one CTA each: the whole context in one split, no partial
+            # sums and no kernel that merges them
+            return whole
+        # as many splits as are resident together, by the longest context of this step (a graph keeps what the
+        # step that recorded it chose; every length its bucket holds is covered either way)
+        blocks = -(-max(1, longest_now) // unit)
+        per_split = unit * -(-blocks // max(1, room // pairs))
+        if per_split >= blocks * unit:
+            return whole  # one split: let it reach to the end of the bucket, so that nothing is merged
+        if n_tokens <= 16 and longest <= 4 * cls.MERGE_IN_PRODUCT_SPLITS * cls.SPLIT_KEYS:
+            # few enough splits that the output product merges them, while a warp has at most a few blocks
+            per_split = max(per_split, unit * -(-longest // (unit * cls.MERGE_IN_PRODUCT_SPLITS)))
+        return per_split
+
     def attend(self, ctx, q, cache, group):
         """Attention of the step's rows over the cache: the tensor-core kernels
         for bfloat16 and head sizes they are built for, else the generic one.
@@ -184,24 +210,8 @@ class GQAttention(Part):
             per_split = self.SPLIT_KEYS
             group_size = self.nh // self.nkv
             if ctx.decode_only and group_size <= 16:
-                pairs = max(1, ctx.n_seqs * self.nkv)
-                wide = ops.attention_decode_slots(self.hd, group.page_size, 8)
-                # the unit a split grows by, and how many CTAs of that kernel are resident together
-                unit, room = (self.WIDE_SPLIT_KEYS, wide) if wide > 0 else (self.SPLIT_KEYS, ops.attention_decode_slots(self.hd, group.page_size))
-                if wide > 0 and ctx.n_tokens > 16 and 10 * pairs >= 3 * wide:
-                    # enough (request, KV head) pairs to keep the SMs busy with one CTA each: the whole context in
-                    # one split, no partial sums and no kernel that merges them
-                    per_split = unit * -(-longest // unit)
-                else:
-                    # as many splits as are resident together, by the longest context of this step (a graph keeps
-                    # what the step that recorded it chose; every length its bucket holds is covered either way)
-                    blocks = -(-max(1, ctx.max_kv_len) // unit)
-                    per_split = unit * -(-blocks // max(1, room // pairs))
-                    if per_split >= blocks * unit:
-                        per_split = unit * -(-longest // unit)  # one split: let it reach to the end of the bucket, so that nothing is merged
-                    if ctx.n_tokens <= 16 and longest <= 4 * self.MERGE_IN_PRODUCT_SPLITS * self.SPLIT_KEYS:
-                        # few enough splits that the output product merges them, while a warp has at most a few blocks
-                        per_split = max(per_split, unit * -(-longest // (unit * self.MERGE_IN_PRODUCT_SPLITS)))
+                per_split = self.decode_split_keys(ctx.n_tokens, ctx.n_seqs * self.nkv, longest, ctx.max_kv_len,
+                                                   ops.attention_decode_slots(self.hd, group.page_size, 8), ops.attention_decode_slots(self.hd, group.page_size))
             if not ctx.decode_only:
                 per_split = self.PROMPT_SPLIT_KEYS or (1 << 30)
             if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):

@@ -73,3 +73,40 @@ def test_a_deep_product_that_underfills_the_gpu_is_halved_only_for_a_consumer_th
     assert fl._splits(ctas, 4864, deferrable=True) == 2
     assert fl._splits(ctas, 4864, deferrable=False) == 1
     assert fl._splits(ctas, 896, deferrable=True) == 1  # shallow: not worth a second pass
+
+
+def test_decode_attention_splits_keep_a_step_resident_at_once():
+    """Keys per CTA of a decode-only step (GQAttention.decode_split_keys), for
+    a device of 148 SMs: head size 64 has the eight-warp kernel (148 CTAs at a
+    time, splits in multiples of 512), head size 128 the four-warp one only
+    (148 CTAs, multiples of 256)."""
+    from alofa_b200.parts.attention import GQAttention as A
+
+    def keys(n_tokens, pairs, longest, now, wide=148, slots=444):
+        return A.decode_split_keys(n_tokens, pairs, longest, now, wide, slots)
+
+    # 14 heads on 2 (pairs = 2 x requests), contexts of 2,049 in a bucket of 4,096
+    assert keys(1, 2, 4096, 2049) == 512
+    assert keys(8, 16, 4096, 2049) == 512  # five splits x 16 pairs = 80 CTAs, one per SM
+    assert keys(12, 24, 4096, 2049) == 512  # 120 CTAs
+    assert keys(16, 32, 4096, 2049) == 1024  # 96 CTAs where 160 would not be resident together
+    assert keys(17, 34, 4096, 2049) == 1024
+    assert keys(24, 48, 4096, 2049) == 4096  # 0.3 pairs per SM and more, past 16 tokens: one split per pair
+    assert keys(64, 128, 4096, 2049) == 4096
+    assert keys(8, 16, 256, 200) == 512  # one split reaches to the end of the bucket: nothing to merge
+    # few tokens keep at most 16 splits for the output product to merge, up to 16k keys
+    assert keys(1, 2, 16384, 16000) == 1024 and -(-16384 // 1024) == 16
+    assert keys(1, 2, 32768, 32000) == 512  # beyond that the merge kernel takes them, as many as are resident
+    # 28 heads of 128 on 4: no eight-warp kernel, 148 CTAs of four warps at a time
+    assert keys(8, 32, 4096, 2049, wide=0, slots=148) == 768  # three splits x 32 pairs
+    assert keys(64, 256, 4096, 2049, wide=0, slots=148) == 4096  # more pairs than SMs: one split each
+    assert keys(1, 4, 4096, 2049, wide=0, slots=148) == 256
+    # every answer covers the launch in whole units and never asks for an empty split first
+    for n, pairs, longest, now, wide, slots in itertools.product((1, 8, 16, 17, 40, 64), (1, 7, 64, 300), (256, 4096, 65536), (1, 200, 4000), (0, 148), (148, 444)):
+        if now > longest:
+            continue
+        k = A.decode_split_keys(n, pairs, longest, now, wide, slots)
+        unit = 512 if wide else 256
+        assert k % unit == 0 and k >= unit and k <= unit * -(-longest // unit)
+        if n <= 16 and longest <= 16384:
+            assert -(-longest // k) <= 16
