@@ -64,7 +64,7 @@ struct GemmArgs {
   int k_slices_per_split;
   int out_bf16;
   int pair;           // tokens on M: the wide product runs on pairs of CTAs (the weight map's box is then 128 rows)
-  int few;            // tokens on M, persistent, up to 32 tokens: the token map's box is 32 rows
+  int few;            // tokens on M, persistent, up to 64 tokens: the token map's box is this many rows (32 or 64), else 0
   int* status;
   // The token operand of the weights-on-M kernel need not lie in memory as rows: the
   // epilogue warps, idle while the MMAs run, can make each k-slice of it in shared memory.
@@ -967,25 +967,26 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 // that run side by side read the same tokens and neighbouring weights.
 // ---------------------------------------------------------------------------
 constexpr int STAGING_BYTES = 4 * 32 * 132 * 4;  // the epilogue's padded rows
-// FEW (up to 32 tokens: an output head in a decode step): only 32 rows of the token tile are
-// fetched - the MMA reads 128, the other 96 from whatever follows in shared memory, and their
-// accumulator rows are never read - and only one quarter of the epilogue has rows, so a stage is
-// 36 KB instead of 48 and the ring five deep instead of three: more weight bytes in flight per SM.
-template <bool FEW>
+// ROWS (32 or 64 instead of 128: an output head in a decode step of up to that many tokens): only
+// ROWS rows of the token tile are fetched - the MMA reads 128, the rest from whatever follows in
+// shared memory, and their accumulator rows are never read - and only ROWS / 32 quarters of the
+// epilogue have rows, so a stage is 36 or 40 KB instead of 48 and the ring five or four deep
+// instead of three: more weight bytes in flight per SM.
+template <int ROWS>
 struct PersistentRing {
-  static constexpr int STAGES = FEW ? 5 : 3;
-  static constexpr uint32_t A_BYTES = (FEW ? 32 : 128) * BK * 2;
-  static constexpr uint32_t STAGING = FEW ? STAGING_BYTES / 4 : STAGING_BYTES;
+  static constexpr int STAGES = ROWS == 32 ? 5 : ROWS == 64 ? 4 : 3;
+  static constexpr uint32_t A_BYTES = ROWS * BK * 2;
+  static constexpr uint32_t STAGING = STAGING_BYTES / 128 * ROWS;
 };
 
-template <int EPI, bool FEW>
+template <int EPI, int ROWS>
 __global__ void __launch_bounds__(TOKENS_THREADS, 1)
 gemm_tc_tokens_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmArgs args) {
   constexpr int BNF = 256;
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr int FEATS = GATED ? BNF / 2 : BNF;
-  constexpr int PERSISTENT_STAGES = PersistentRing<FEW>::STAGES;
-  constexpr uint32_t A_BYTES = PersistentRing<FEW>::A_BYTES;
+  constexpr int PERSISTENT_STAGES = PersistentRing<ROWS>::STAGES;
+  constexpr uint32_t A_BYTES = PersistentRing<ROWS>::A_BYTES;
   constexpr uint32_t B_BYTES = BNF * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BNF >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -1413,10 +1414,25 @@ static bool pair_product(int bnf, int splits, int T, int N, int K, int epi) {
   return (long long)((N + feats - 1) / feats) * ((T + 127) / 128) > sms;
 }
 
-// Whether a tokens-on-M product of up to 32 tokens runs on the persistent kernel's few-token form
+template <int EPI, int ROWS>
+static int launch_persistent(int sms, const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& args, cudaStream_t stream) {
+  static bool configured = false;
+  constexpr size_t SMEM = (size_t)PersistentRing<ROWS>::STAGES * (PersistentRing<ROWS>::A_BYTES + (size_t)256 * BK * 2) + PersistentRing<ROWS>::STAGING + 1024;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_tokens_persistent_kernel<EPI, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
+      return ALOFA_ERR_LAUNCH;
+    prefer_max_shared(gemm_tc_tokens_persistent_kernel<EPI, ROWS>);
+    configured = true;
+  }
+  launch_dep(gemm_tc_tokens_persistent_kernel<EPI, ROWS>, dim3(sms), TOKENS_THREADS, SMEM, stream, mw, mx, args);
+  return launch_status();
+}
+
+// How many token rows (32 or 64) the persistent kernel's few-token form fetches for a tokens-on-M
+// product of up to 64 tokens, 0 when the product does not run on it
 // (the same conditions as launch_tokens has for the persistent kernel; ALOFA_GEMM_PERSISTENT=0
 // turns both off).
-static bool few_tokens_product(int bnf, int splits, int T, int N, int K, int epi) {
+static int few_tokens_product(int bnf, int splits, int T, int N, int K, int epi) {
   static int sms = 0, allowed = -1;
   if (allowed < 0) {
     const char* env = getenv("ALOFA_GEMM_PERSISTENT");
@@ -1424,9 +1440,10 @@ static bool few_tokens_product(int bnf, int splits, int T, int N, int K, int epi
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 0;
   }
-  if (!allowed || sms <= 0 || bnf != 256 || splits != 1 || (N & 3) || K > 2048 || T > 32) return false;
+  if (!allowed || sms <= 0 || bnf != 256 || splits != 1 || (N & 3) || K > 2048 || T > 64) return 0;
   const int feats = epi == EPI_GATED ? 128 : 256;
-  return (N + feats - 1) / feats > sms;  // one token tile: the feature tiles alone are more than the SMs
+  if ((N + feats - 1) / feats <= sms) return 0;  // one token tile: the feature tiles alone must be more than the SMs
+  return T <= 32 ? 32 : 64;
 }
 
 template <int BNF, int EPI>
@@ -1497,30 +1514,9 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
       cudaLaunchKernelEx(&cfg, gemm_tc_tokens_pair_kernel<EPI>, mw, mx, args);
       return launch_status();
     }
-    if (persistent && sms > 0 && n_tiles > sms && args.few) {
-      static bool configured_f = false;
-      constexpr size_t SMEM_F = (size_t)PersistentRing<true>::STAGES * (PersistentRing<true>::A_BYTES + (size_t)BNF * BK * 2) + PersistentRing<true>::STAGING + 1024;
-      if (!configured_f) {
-        if (cudaFuncSetAttribute(gemm_tc_tokens_persistent_kernel<EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_F) != cudaSuccess)
-          return ALOFA_ERR_LAUNCH;
-        prefer_max_shared(gemm_tc_tokens_persistent_kernel<EPI, true>);
-        configured_f = true;
-      }
-      launch_dep(gemm_tc_tokens_persistent_kernel<EPI, true>, dim3(sms), TOKENS_THREADS, SMEM_F, stream, mw, mx, args);
-      return launch_status();
-    }
-    if (persistent && sms > 0 && n_tiles > sms) {
-      static bool configured_p = false;
-      constexpr size_t SMEM_P = (size_t)PersistentRing<false>::STAGES * STAGE + STAGING_BYTES + 1024;
-      if (!configured_p) {
-        if (cudaFuncSetAttribute(gemm_tc_tokens_persistent_kernel<EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_P) != cudaSuccess)
-          return ALOFA_ERR_LAUNCH;
-        prefer_max_shared(gemm_tc_tokens_persistent_kernel<EPI, false>);
-        configured_p = true;
-      }
-      launch_dep(gemm_tc_tokens_persistent_kernel<EPI, false>, dim3(sms), TOKENS_THREADS, SMEM_P, stream, mw, mx, args);
-      return launch_status();
-    }
+    if (persistent && sms > 0 && n_tiles > sms && args.few == 32) return launch_persistent<EPI, 32>(sms, mw, mx, args, stream);
+    if (persistent && sms > 0 && n_tiles > sms && args.few == 64) return launch_persistent<EPI, 64>(sms, mw, mx, args, stream);
+    if (persistent && sms > 0 && n_tiles > sms) return launch_persistent<EPI, 128>(sms, mw, mx, args, stream);
   }
   if (args.few || args.pair) return ALOFA_ERR_ARGUMENT;  // their maps have other boxes than this kernel's
   launch_dep(gemm_tc_tokens_kernel<BNF, EPI>, grid, TOKENS_THREADS, smem, stream, mw, mx, args, stages);
@@ -1606,10 +1602,10 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   const int bnf = -bn;
   CUtensorMap mw, mx;
   const bool pair = tokens_on_m && pair_product(bnf, splits, T, N, K, epi);
-  const bool few = tokens_on_m && !pair && few_tokens_product(bnf, splits, T, N, K, epi);
+  const int few = (tokens_on_m && !pair) ? few_tokens_product(bnf, splits, T, N, K, epi) : 0;
   if (tokens_on_m) {
     const int w_box = (epi == EPI_GATED || pair) ? bnf / 2 : bnf;
-    if (!make_map(&mw, w, w_rows, K, w_box) || !make_map(&mx, x, T, K, few ? 32 : 128)) return ALOFA_ERR_ARGUMENT;
+    if (!make_map(&mw, w, w_rows, K, w_box) || !make_map(&mx, x, T, K, few ? few : 128)) return ALOFA_ERR_ARGUMENT;
   } else if (!make_map(&mw, w, w_rows, K, BM) || !make_map(&mx, x, T, K, bn)) {
     return ALOFA_ERR_ARGUMENT;
   }
@@ -1625,7 +1621,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;  // no empty split
   args.out_bf16 = out_bf16;
   args.pair = pair ? 1 : 0;
-  args.few = few ? 1 : 0;
+  args.few = few;
   args.status = status;
   args.b_kind = b_kind;
   args.b_src = b_src;

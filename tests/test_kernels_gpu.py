@@ -258,7 +258,7 @@ def test_qkv_cluster_size_is_what_the_device_holds_at_once(ops):
 @pytest.mark.parametrize("shape", [(5, 128, 64, 16, 1), (33, 379, 96, 64, 1), (300, 1152, 896, 128, 3), (8, 896, 4864, 16, 19), (513, 640, 320, 256, 2),
                                    (8, 512, 896, 16, 3), (13, 200, 320, 16, 5), (16, 131, 512, 16, 8), (29, 640, 896, 32, 3),  # gated: the splits add up inside a cluster
                                    (5, 128, 64, -64, 1), (130, 379, 96, -128, 1), (300, 1152, 896, -256, 3), (513, 650, 320, -256, 2), (257, 200, 240, -128, 1),
-                                   (5, 40000, 96, -256, 1), (130, 39996, 64, -256, 1),  # more tiles than SMs: one resident CTA per SM, tiles cut evenly
+                                   (5, 40000, 96, -256, 1), (40, 40000, 96, -256, 1), (130, 39996, 64, -256, 1),  # more tiles than SMs: one resident CTA per SM, tiles cut evenly (5 and 40 tokens: 32 and 64 rows of the token tile fetched)
                                    (8, 2048, 1536, 16, 8), (8, 1536, 8960, 16, 12), (64, 1536, 1536, 64, 6), (300, 8960, 1536, -256, 1),  # widths of the 1.5B shape
                                    (8, 4608, 3584, 16, 4), (8, 3584, 18944, 16, 5), (33, 3584, 3584, 64, 2), (200, 4608, 3584, -256, 1),  # and of the 7B shape
                                    # deep and wide over several token tiles: pairs of CTAs with MMAs of M = 256 (ragged depth and width, a pair's
