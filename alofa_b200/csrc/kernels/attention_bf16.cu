@@ -620,20 +620,26 @@ static size_t attention_smem_bytes(int stages, int table_entries) {
 
 ALOFA_API int alofa_attention_head_dim() { return HD; }
 
-// How many CTAs of the decode kernel with `warps` warps (4, or 8: head size 64 on pages of whole
-// key blocks, taken when a launch's splits are a multiple of 512 keys) the device holds at a
-// time: what a caller sizes the key splits by, so that a step's CTAs are resident together.
+// The decode kernel's wide form: one CTA per SM with as many warps as its shared memory holds
+// key and value tiles for (16 KB a warp at head size 64, 32 KB at 128), on pages of whole key
+// blocks.  Taken when a launch's splits are a multiple of WIDE_WARPS * 64 keys.
+constexpr int WIDE_WARPS = HD == 64 ? 8 : HD == 128 ? 6 : 0;
+ALOFA_API int alofa_attention_decode_wide_warps() { return WIDE_WARPS; }
+
+// How many CTAs of the decode kernel with `warps` warps (4, or the wide form's) the device holds
+// at a time: what a caller sizes the key splits by, so that a step's CTAs are resident together.
 // 0 when that kernel does not exist here or the device cannot be asked.
 ALOFA_API int alofa_attention_decode_slots(int page_size, int warps) {
   const bool tma = (HD == 64 || HD == 128) && page_size % BLOCK_N == 0;
   int device = 0, sms = 0, per_sm = 0;
   if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
   cudaError_t rc;
-  if (warps == 8) {
-    if (!tma || HD != 64) return 0;
-    const size_t smem = decode_smem_bytes(8, true);
-    cudaFuncSetAttribute(attention_decode_kernel<8, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<8, true, true>, 256, smem);
+  if (WIDE_WARPS > 0 && warps == WIDE_WARPS) {
+    if (!tma) return 0;
+    constexpr int W = WIDE_WARPS > 0 ? WIDE_WARPS : 4;
+    const size_t smem = decode_smem_bytes(W, true);
+    cudaFuncSetAttribute(attention_decode_kernel<W, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    rc = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<W, true, true>, W * 32, smem);
   } else if (warps != 4) {
     return 0;
   } else if (tma) {
@@ -718,7 +724,8 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
     prefer_max_shared(attention_combine_kernel);
     configured = true;
   }
-  if (n_splits > 0 && decode_only && nh / nkv <= 16 && (split_keys % (4 * BLOCK_N) == 0 || split_keys == 2 * BLOCK_N)) {
+  if (n_splits > 0 && decode_only && nh / nkv <= 16 &&
+      (split_keys % (4 * BLOCK_N) == 0 || split_keys == 2 * BLOCK_N || (WIDE_WARPS > 0 && split_keys % ((WIDE_WARPS > 0 ? WIDE_WARPS : 4) * BLOCK_N) == 0))) {
     // decode tokens of small head groups: the key blocks of a split side by side on the warps
     // pages that hold whole key blocks and rows of 128 or 256 bytes: bulk tensor copies
     CUtensorMap map_k, map_v;
@@ -731,9 +738,9 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
       memset(&map_v, 0, sizeof(map_v));
     }
     int rc;
-    if (tma && HD == 64 && split_keys % (8 * BLOCK_N) == 0)
-      // splits of a multiple of 512 keys: eight warps, one CTA per SM (see alofa_attention_decode_slots)
-      rc = launch_decode<8, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
+    if (tma && WIDE_WARPS > 0 && split_keys % ((WIDE_WARPS > 0 ? WIDE_WARPS : 4) * BLOCK_N) == 0)
+      // splits of a multiple of the wide form's keys: one CTA per SM (see alofa_attention_decode_slots)
+      rc = launch_decode<(WIDE_WARPS > 0 ? WIDE_WARPS : 4), true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
     else if (split_keys % (4 * BLOCK_N) == 0)
       rc = tma ? launch_decode<4, true>(p, map_k, map_v, n_splits, nkv, n_seqs, stream) : launch_decode<4, false>(p, map_k, map_v, n_splits, nkv, n_seqs, stream);
     else

@@ -95,6 +95,8 @@ def _attention(head_dim: int):
         lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _I, _P]
         lib.alofa_attention_combine.restype = _I
         lib.alofa_attention_combine.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _P]
+        lib.alofa_attention_decode_wide_warps.restype = _I
+        lib.alofa_attention_decode_wide_warps.argtypes = []
         lib.alofa_attention_decode_slots.restype = _I
         lib.alofa_attention_decode_slots.argtypes = [_I, _I]
         _libs[key] = lib
@@ -104,10 +106,16 @@ def _attention(head_dim: int):
 _decode_slots = {}
 
 
+def attention_decode_wide_warps(head_dim: int) -> int:
+    """Warps of the decode attention kernel's wide form at this head size (one
+    CTA per SM; its splits are multiples of 64 keys a warp), 0 when it has none."""
+    return _attention(head_dim).alofa_attention_decode_wide_warps()
+
+
 def attention_decode_slots(head_dim: int, page_size: int, warps: int = 4) -> int:
-    """How many CTAs of the decode attention kernel with ``warps`` warps (4 or
-    8) the device holds at a time, 0 when that kernel is not built for this
-    head size and kind of page (asked once each)."""
+    """How many CTAs of the decode attention kernel with ``warps`` warps (4, or
+    the wide form's) the device holds at a time, 0 when that kernel is not
+    built for this head size and kind of page (asked once each)."""
     key = (head_dim, page_size % 64 == 0, warps)
     if key not in _decode_slots:
         _decode_slots[key] = max(0, _attention(head_dim).alofa_attention_decode_slots(page_size, warps))

@@ -156,12 +156,13 @@ class GQAttention(Part):
     # 2,048 keys: 1.58 -> 1.47 ms per step for 14 heads of 64 on 2, 5.90 -> 5.08 ms for 28 heads
     # of 128 on 4).
     SPLIT_KEYS = 256
-    # Head size 64 on pages of whole key blocks has an eight-warp form of the kernel, one CTA per SM, whose
-    # splits grow by 512 keys: fewer, larger CTAs and fewer splits to merge (batch 8: nine splits of 256 keys
-    # 0.780 ms per step, five of 512 0.758; batch 12: 0.819 -> 0.788).  With three tenths as many (request, KV
-    # head) pairs as SMs or more, in steps of more than 16 tokens, one split per pair (batch 64: 1.40 -> 1.34 ms;
-    # batch 32: 1.065 -> 1.027; the merge kernel and the partial sums go).
-    WIDE_SPLIT_KEYS = 512
+    # On pages of whole key blocks head sizes 64 and 128 have a wide form of the kernel, one CTA per SM with
+    # eight or six warps (what shared memory holds tiles for), whose splits grow by 64 keys a warp: fewer,
+    # larger CTAs and fewer splits to merge (14 heads of 64 on 2, batch 8: nine splits of 256 keys 0.780 ms per
+    # step, five of 512 0.758; batch 12: 0.819 -> 0.788; 28 heads of 128 on 4, batch 64: 5.03 -> 4.90 ms).  With
+    # three tenths as many (request, KV head) pairs as SMs or more, in steps of more than 16 tokens, one split
+    # per pair (14 heads of 64 on 2, batch 64: 1.40 -> 1.34 ms; batch 32: 1.065 -> 1.027; the merge kernel and
+    # the partial sums go).
     # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.
     # Measured at 2,048-token prompts the round trip of the partial sums costs more than the
     # long tiles' tail saves (4.9 ms against 4.5 ms for the step), so it is off.
@@ -173,15 +174,16 @@ class GQAttention(Part):
     MERGE_IN_PRODUCT_SPLITS = 16
 
     @classmethod
-    def decode_split_keys(cls, n_tokens: int, pairs: int, longest: int, longest_now: int, wide_slots: int, slots: int) -> int:
+    def decode_split_keys(cls, n_tokens: int, pairs: int, longest: int, longest_now: int, wide_slots: int, slots: int, wide_unit: int = 512) -> int:
         """Keys per CTA of a decode-only step.  ``pairs``: (request, KV head)
         pairs; ``longest``: the context the launch must cover (a graph's
         bucket), ``longest_now``: the longest context of this step;
-        ``wide_slots`` / ``slots``: CTAs of the eight-warp / four-warp kernel
-        the device holds at a time (0: that kernel is not built here)."""
+        ``wide_slots`` / ``slots``: CTAs of the wide / four-warp kernel the
+        device holds at a time (0: that kernel is not built here);
+        ``wide_unit``: the keys the wide kernel's splits grow by."""
         pairs = max(1, pairs)
         # the unit a split grows by, and how many CTAs of that kernel are resident together
-        unit, room = (cls.WIDE_SPLIT_KEYS, wide_slots) if wide_slots > 0 else (cls.SPLIT_KEYS, slots)
+        unit, room = (wide_unit, wide_slots) if wide_slots > 0 else (cls.SPLIT_KEYS, slots)
         whole = unit * -(-longest // unit)
         if wide_slots > 0 and n_tokens > 16 and 10 * pairs >= 3 * wide_slots:
             # enough pairs to keep the SMs busy with one CTA each: the whole context in one split, no partial
@@ -210,8 +212,10 @@ class GQAttention(Part):
             per_split = self.SPLIT_KEYS
             group_size = self.nh // self.nkv
             if ctx.decode_only and group_size <= 16:
+                wide_warps = ops.attention_decode_wide_warps(self.hd)
                 per_split = self.decode_split_keys(ctx.n_tokens, ctx.n_seqs * self.nkv, longest, ctx.max_kv_len,
-                                                   ops.attention_decode_slots(self.hd, group.page_size, 8), ops.attention_decode_slots(self.hd, group.page_size))
+                                                   ops.attention_decode_slots(self.hd, group.page_size, wide_warps) if wide_warps else 0,
+                                                   ops.attention_decode_slots(self.hd, group.page_size), 64 * wide_warps)
             if not ctx.decode_only:
                 per_split = self.PROMPT_SPLIT_KEYS or (1 << 30)
             if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):

@@ -463,8 +463,9 @@ def test_attention_bf16_long_splits(ops, hd, nh, nkv):
     key tile and its value tile while it works on the block before.  Lengths
     either side of every edge: one block, one round of the warps, a split."""
     lens = [1, 65, 256, 257, 513, 769, 1025, 2049, 2600]
-    # 3,072 keys: one split for every request here, which head size 64 on pages of whole blocks runs with eight warps
-    for window, cases in ((None, ((512, 64), (768, 128), (1280, 64), (512, 16), (3072, 64))), (700, ((1024, 64), (768, 48), (3072, 128)))):
+    # 3,072 keys: one split for every request here; multiples of 512 keys run on eight warps at head size 64, multiples
+    # of 384 on six at head size 128 (384 itself: one block per warp), on pages of whole blocks
+    for window, cases in ((None, ((512, 64), (768, 128), (1280, 64), (512, 16), (3072, 64), (384, 64))), (700, ((1024, 64), (768, 48), (3072, 128)))):
         for split, page in cases:
             got, want = attention_case(ops, BF16, hd, nh, nkv, lens=lens, q_lens=[1] * len(lens), page=page, window=window, rng=np.random.default_rng(hd + split), fast=True, split_keys=split)
             assert_close(got, want, TOL[BF16], f"split {split} hd={hd} window={window} page={page}")

@@ -101,6 +101,11 @@ def test_decode_attention_splits_keep_a_step_resident_at_once():
     assert keys(8, 32, 4096, 2049, wide=0, slots=148) == 768  # three splits x 32 pairs
     assert keys(64, 256, 4096, 2049, wide=0, slots=148) == 4096  # more pairs than SMs: one split each
     assert keys(1, 4, 4096, 2049, wide=0, slots=148) == 256
+    # the same head size with its six-warp form (splits in multiples of 384 keys, 148 CTAs at a time)
+    wide128 = dict(wide_slots=148, slots=148, wide_unit=384)
+    assert A.decode_split_keys(8, 32, 4096, 2049, **wide128) == 768  # six blocks of 384 over four resident splits: two each
+    assert A.decode_split_keys(64, 256, 4096, 2049, **wide128) == 4224  # one split, the bucket rounded up to 384s
+    assert A.decode_split_keys(1, 4, 4096, 2049, **wide128) == 384
     # every answer covers the launch in whole units and never asks for an empty split first
     for n, pairs, longest, now, wide, slots in itertools.product((1, 8, 16, 17, 40, 64), (1, 7, 64, 300), (256, 4096, 65536), (1, 200, 4000), (0, 148), (148, 444)):
         if now > longest:
