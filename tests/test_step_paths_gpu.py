@@ -104,7 +104,7 @@ def test_decode_with_more_work_than_the_device_holds_at_once(folders, name, monk
 
     def watch(*args, **kwargs):
         asked.append(args[17])  # split_keys
-        if args[16] == 1 and args[17] % 512 == 0:
+        if args[16] == 1 and args[17] % (64 * ops.attention_decode_wide_warps(args[13])) == 0:
             one_wide_split.append(args[17])
         return real(*args, **kwargs)
 
@@ -119,16 +119,16 @@ def test_decode_with_more_work_than_the_device_holds_at_once(folders, name, monk
         got = [[] for _ in seqs]
         del asked[:]
         # (requests, room for four-warp CTAs, room for eight-warp CTAs): twenty with splits of 512 merged by the combine
-        # kernel; eight, twice, whose splits the output product merges; twenty with one split each on eight warps (head 64)
+        # kernel; eight, twice, whose splits the output product merges; nineteen with one split each on the wide kernel's eight or six warps
         for step, (live, room, wide) in enumerate(((range(20), 40, 0), (range(4, 12), 16, 0), (range(4, 12), 16, 0), (range(19), 40, 40))):  # nineteen: a graph of its own
             monkeypatch.setattr(ops, "attention_decode_slots",
-                                lambda hd, page, warps=4, room=room, wide=wide: room if warps == 4 else min(wide, real_slots(hd, page, 8)))
+                                lambda hd, page, warps=4, room=room, wide=wide: room if warps == 4 else min(wide, real_slots(hd, page, warps)))
             logits = runner.forward([StepEntry(slots[i], [seqs[i][lens[i] + len(got[i])]], [0]) for i in live]).float().cpu().numpy()
             for row, i in zip(logits, live):
                 got[i].append(row)
         runner.check_status()
         assert max(asked) >= 512 and GQAttention.SPLIT_KEYS == 256, f"splits asked for: {sorted(set(asked))}"
-        assert one_wide_split or name != "P", "head size 64: the last step should have run one split per request on eight warps"
+        assert one_wide_split, "the last step should have run one split per request on the wide kernel"
         for i, rows in enumerate(got):
             ref = want[i][lens[i] : lens[i] + len(rows)]
             bound = 2e-2 * max(1.0, float(np.abs(ref).max()))
